@@ -1,0 +1,139 @@
+/*
+ * nzb.h - C ABI of the B200 (sm_100a) kernel library behind NeuZephyr's dense-contraction path.
+ *
+ * Every entry point is asynchronous on the stream it is given, never synchronises the
+ * host, never resets the device and reports failure through its return code.
+ * Pointers are device pointers to contiguous fp32 storage unless stated otherwise.
+ * File:line citations name the NeuZephyr interface an entry point stands in for.
+ */
+#ifndef NZB_H
+#define NZB_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define NZB_API __declspec(dllexport)
+#else
+#define NZB_API __attribute__((visibility("default")))
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+    NZB_OK = 0,
+    NZB_ERR_BAD_ARG = 1,        /* null pointer, negative extent, inconsistent shapes */
+    NZB_ERR_UNSUPPORTED = 2,    /* shape outside what the kernels handle */
+    NZB_ERR_WORKSPACE = 3,      /* workspace missing or smaller than nzb_*_workspace_bytes() */
+    NZB_ERR_CUDA = 4,           /* a CUDA runtime/driver call failed; see nzb_last_error_string() */
+    NZB_ERR_DEVICE_TIMEOUT = 5, /* a bounded device-side wait expired (reported by nzb_device_status) */
+    NZB_ERR_NO_DEVICE = 6       /* no sm_100 device is current */
+};
+
+enum { NZB_BIAS_NONE = 0, NZB_BIAS_ROW = 1, NZB_BIAS_COL = 2, NZB_BIAS_MATRIX = 3 };
+
+/*
+ * General descriptor: C[b] (op)= op(A[b]) * op(B[b]) over a two-dimensional batch grid
+ * (the N and C extents of NeuZephyr's 4-D tensors). fp32 in memory, operands rounded to
+ * fp16 (round-to-nearest-even) for the tensor cores, fp32 accumulation.
+ *
+ *   op(A) is M x K, op(B) is K x N, C is M x N, all row-major.
+ *   transA = 0: A is stored M x K with leading dimension lda; 1: stored K x M.
+ *   transB = 0: B is stored K x N with leading dimension ldb; 1: stored N x K.
+ *   batch[d]   extent of batch dimension d (>= 1).
+ *   strideX[d] element stride of operand X along batch dimension d. 0 on A or B
+ *              broadcasts that operand; 0 on C with batch[d] > 1 SUMS the products of
+ *              that dimension into one C (the reference's batch-reducing backward).
+ *   accumulate 0: C is overwritten (Cutting, src/OperationKernels.cu:862-871);
+ *              1: the result is added to C (CuttingAndCompress, :873-883).
+ *   bias_mode  NZB_BIAS_ROW: bias[N] added to every row; NZB_BIAS_COL: bias[M] added to
+ *              every column; NZB_BIAS_MATRIX: bias[M x N] with leading dimension bias_ld
+ *              (NeuZephyr's untied conv bias {1,1,Ho*Wo,Cout}). Bias is shared by all batches.
+ *   relu       apply max(x, 0) after bias (and after accumulate).
+ */
+typedef struct nzb_gemm_desc {
+    int64_t M, N, K;
+    int64_t lda, ldb, ldc;
+    int32_t transA, transB;
+    int32_t batch[2];
+    int64_t strideA[2], strideB[2], strideC[2];
+    int32_t accumulate;
+    int32_t bias_mode;
+    int64_t bias_ld;
+    int32_t relu;
+    int32_t reserved;
+} nzb_gemm_desc;
+
+/* Library / device ------------------------------------------------------- */
+
+/* Version of this ABI (major * 100 + minor). */
+NZB_API int nzb_version(void);
+
+/* Human-readable text for the most recent non-OK return on the calling thread. */
+NZB_API const char* nzb_last_error_string(void);
+
+/*
+ * Reads the device-side status word of the current device: 0 when no kernel of this
+ * library gave up on a bounded wait since the last nzb_device_status_reset(). The word
+ * lives in mapped host memory; call after synchronising the stream(s) of interest.
+ * Replaces the reference's CHECK macro policy (cudaDeviceReset + throw,
+ * include/NeuZephyr/NeuZephyrCudaErrorHandling.cuh:101-118) with a queryable status.
+ */
+NZB_API int nzb_device_status(int* status_out);
+NZB_API int nzb_device_status_reset(void);
+
+/* GEMM -------------------------------------------------------------------- */
+
+/* Scratch bytes nzb_gemm needs for this descriptor (fp16 operand copies). */
+NZB_API int nzb_gemm_workspace_bytes(const nzb_gemm_desc* desc, size_t* bytes_out);
+
+/*
+ * The tensor-core GEMM: replaces nz::krnl::TensorCoreGEMM / TensorCoreGEMMParallel /
+ * GEMMBackwardParallel (src/OperationKernels.cu:885-912, :914-1026, :1028-1144; declared
+ * include/NeuZephyr/OperationKernels.cuh:911-921) including their Padding / Cutting /
+ * CuttingAndCompress passes, and optionally the bias add (MatrixAddKernel, :12-37) and
+ * ReLU (:230-240) that follow it in Model::Linear / Model::Conv2d graphs.
+ * workspace must be 256-byte aligned device memory of at least
+ * nzb_gemm_workspace_bytes() bytes, private to this call until the stream reaches its end.
+ */
+NZB_API int nzb_gemm(const nzb_gemm_desc* desc, const float* A, const float* B, float* C, const float* bias,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Same seam as nz::data::iTensorCoreGEMM(float* A, float* B, float* C, const Dimension&
+ * shapeA, shapeB, shapeC) (include/NeuZephyr/TensorOperations.cuh:1021-1024,
+ * src/TensorOperations.cu:112-115): shapes are {N, C, H, W}; M = A.H, K = A.W, N = B.W;
+ * an operand whose N (or C) extent is 1 is broadcast along that dimension; C is overwritten.
+ */
+NZB_API int nzb_tensorcore_gemm_workspace_bytes(const int64_t shapeA[4], const int64_t shapeB[4],
+                                                const int64_t shapeC[4], size_t* bytes_out);
+NZB_API int nzb_tensorcore_gemm(const float* A, const float* B, float* C, const int64_t shapeA[4],
+                                const int64_t shapeB[4], const int64_t shapeC[4], void* workspace,
+                                size_t workspace_bytes, void* stream);
+
+/*
+ * Same seam as nz::data::iGEMMBackward (include/NeuZephyr/TensorOperations.cuh:1026-1031,
+ * src/TensorOperations.cu:117-120): the products of all max(A.N,B.N) x max(A.C,B.C)
+ * batches are ADDED to C; along a dimension where C's extent is 1 they are summed into
+ * the single C matrix (src/OperationKernels.cu:1121-1137).
+ */
+NZB_API int nzb_gemm_backward(const float* A, const float* B, float* C, const int64_t shapeA[4],
+                              const int64_t shapeB[4], const int64_t shapeC[4], void* workspace,
+                              size_t workspace_bytes, void* stream);
+
+/*
+ * fp32 -> fp16 (round to nearest even) copy of `rows` x `cols` with source leading
+ * dimension ld_in into a dense fp16 matrix with leading dimension ld_out (columns
+ * cols..ld_out-1 are zero filled): the Padding kernel (src/OperationKernels.cu:846-860)
+ * as a stand-alone pass. transpose != 0 reads the source as cols x rows.
+ */
+NZB_API int nzb_cast_f32_f16(const float* in, void* out_f16, int64_t rows, int64_t cols, int64_t ld_in,
+                             int64_t ld_out, int transpose, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NZB_H */

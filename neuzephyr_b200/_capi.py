@@ -1,0 +1,76 @@
+"""ctypes binding of libnzb.so (include/nzb.h). No torch types cross this boundary:
+callers pass raw device addresses, sizes and a stream handle."""
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libnzb.so")
+
+OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(7)
+BIAS_NONE, BIAS_ROW, BIAS_COL, BIAS_MATRIX = range(4)
+
+EXPORTS = [
+    "nzb_version", "nzb_last_error_string", "nzb_device_status", "nzb_device_status_reset",
+    "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
+    "nzb_gemm_backward", "nzb_cast_f32_f16",
+]
+
+
+class GemmDesc(ctypes.Structure):
+    """struct nzb_gemm_desc"""
+    _fields_ = [
+        ("M", ctypes.c_int64), ("N", ctypes.c_int64), ("K", ctypes.c_int64),
+        ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldc", ctypes.c_int64),
+        ("transA", ctypes.c_int32), ("transB", ctypes.c_int32),
+        ("batch", ctypes.c_int32 * 2),
+        ("strideA", ctypes.c_int64 * 2), ("strideB", ctypes.c_int64 * 2), ("strideC", ctypes.c_int64 * 2),
+        ("accumulate", ctypes.c_int32), ("bias_mode", ctypes.c_int32),
+        ("bias_ld", ctypes.c_int64),
+        ("relu", ctypes.c_int32), ("reserved", ctypes.c_int32),
+    ]
+
+
+class NzbError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__("nzb error %d: %s" % (code, msg))
+        self.code = code
+
+
+_lib = None
+
+
+def lib():
+    """Loads libnzb.so; raises if it has not been built (there is no fallback path)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError("libnzb.so is missing: run `python -m neuzephyr_b200.build` (needs nvcc)")
+        L = ctypes.CDLL(LIB_PATH)
+        L.nzb_last_error_string.restype = ctypes.c_char_p
+        i64p = ctypes.POINTER(ctypes.c_int64)
+        vp, sz = ctypes.c_void_p, ctypes.c_size_t
+        L.nzb_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc), ctypes.POINTER(sz)]
+        L.nzb_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, sz, vp]
+        L.nzb_tensorcore_gemm_workspace_bytes.argtypes = [i64p, i64p, i64p, ctypes.POINTER(sz)]
+        L.nzb_tensorcore_gemm.argtypes = [vp, vp, vp, i64p, i64p, i64p, vp, sz, vp]
+        L.nzb_gemm_backward.argtypes = [vp, vp, vp, i64p, i64p, i64p, vp, sz, vp]
+        L.nzb_cast_f32_f16.argtypes = [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                       ctypes.c_int, vp]
+        L.nzb_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+        _lib = L
+    return _lib
+
+
+def check(rc):
+    if rc != OK:
+        raise NzbError(rc, lib().nzb_last_error_string().decode())
+
+
+def shape4(s):
+    return (ctypes.c_int64 * 4)(*[int(v) for v in s])
+
+
+def device_status():
+    s = ctypes.c_int(0)
+    check(lib().nzb_device_status(ctypes.byref(s)))
+    return s.value

@@ -1,0 +1,250 @@
+// extern "C" entry points of libnzb: argument validation, workspace carving and the
+// mapping from NeuZephyr's 4-D shapes to the kernel launch description.
+#include <cuda_fp16.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+#include "nzb_internal.h"
+
+namespace nzb {
+
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+static std::mutex g_mu;
+static DeviceState g_states[64];
+
+int get_device_state(DeviceState** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        cudaGetLastError();
+        return fail(NZB_ERR_NO_DEVICE, "no CUDA device is current");
+    }
+    std::lock_guard<std::mutex> lk(g_mu);
+    DeviceState& s = g_states[dev];
+    if (s.device != dev) {
+        cudaDeviceProp prop;
+        NZB_CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+        if (prop.major != 10) return fail(NZB_ERR_NO_DEVICE, "device %d is sm_%d%d; this library holds sm_100a code only", dev, prop.major, prop.minor);
+        int* h = nullptr;
+        NZB_CUDA_TRY(cudaHostAlloc(&h, sizeof(int) * 16, cudaHostAllocMapped));
+        for (int i = 0; i < 16; i++) h[i] = 0;
+        int* d = nullptr;
+        NZB_CUDA_TRY(cudaHostGetDevicePointer(&d, h, 0));
+        s.sm_count = prop.multiProcessorCount;
+        s.cc_major = prop.major;
+        s.status_host = h;
+        s.status_dev = d;
+        s.device = dev;
+    }
+    *out = &s;
+    return NZB_OK;
+}
+
+int get_encode_tiled(EncodeTiledFn* out) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        NZB_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !p) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    *out = fn;
+    return NZB_OK;
+}
+
+// Resolved view of a descriptor.
+struct Plan {
+    int64_t M, N, K, Kp;
+    int64_t nA0, nA1, nB0, nB1;  // matrices in the fp16 copies along each batch dimension
+    size_t a_bytes, b_bytes;
+    GemmLaunch g;
+};
+
+static int make_plan(const nzb_gemm_desc* d, Plan* pl) {
+    if (!d) return fail(NZB_ERR_BAD_ARG, "descriptor is null");
+    if (d->M < 0 || d->N < 0 || d->K < 0) return fail(NZB_ERR_BAD_ARG, "negative extent");
+    if (d->batch[0] < 1 || d->batch[1] < 1) return fail(NZB_ERR_BAD_ARG, "batch extents must be >= 1");
+    const int64_t a_rows = d->transA ? d->K : d->M, a_cols = d->transA ? d->M : d->K;
+    const int64_t b_rows = d->transB ? d->N : d->K, b_cols = d->transB ? d->K : d->N;
+    (void)a_rows; (void)b_rows;
+    if (d->lda < a_cols || d->ldb < b_cols || d->ldc < d->N) return fail(NZB_ERR_BAD_ARG, "leading dimension smaller than the row length");
+    if (d->bias_mode < NZB_BIAS_NONE || d->bias_mode > NZB_BIAS_MATRIX) return fail(NZB_ERR_BAD_ARG, "unknown bias mode");
+    if (d->bias_mode == NZB_BIAS_MATRIX && d->bias_ld < d->N) return fail(NZB_ERR_BAD_ARG, "bias_ld smaller than N");
+    pl->M = d->M; pl->N = d->N; pl->K = d->K;
+    pl->Kp = round_up(d->K > 0 ? d->K : 1, kOperandKAlign);
+    const int64_t e0 = d->batch[0], e1 = d->batch[1];
+    pl->nA0 = (e0 > 1 && d->strideA[0] != 0) ? e0 : 1;
+    pl->nA1 = (e1 > 1 && d->strideA[1] != 0) ? e1 : 1;
+    pl->nB0 = (e0 > 1 && d->strideB[0] != 0) ? e0 : 1;
+    pl->nB1 = (e1 > 1 && d->strideB[1] != 0) ? e1 : 1;
+    pl->a_bytes = (size_t)round_up(pl->nA0 * pl->nA1 * pl->M * pl->Kp * 2, 256);
+    pl->b_bytes = (size_t)round_up(pl->nB0 * pl->nB1 * pl->N * pl->Kp * 2, 256);
+    GemmLaunch& g = pl->g;
+    g = GemmLaunch{};
+    g.nA = pl->nA0 * pl->nA1;
+    g.nB = pl->nB0 * pl->nB1;
+    g.M = d->M; g.N = d->N; g.K = d->K; g.Kp = pl->Kp;
+    g.ldc = d->ldc;
+    const int64_t ext[2] = {e0, e1};
+    for (int k = 0; k < 2; k++) {
+        const bool reduce = ext[k] > 1 && d->strideC[k] == 0;
+        g.out_e[k] = reduce ? 1 : (int32_t)ext[k];
+        g.red_e[k] = reduce ? (int32_t)ext[k] : 1;
+        g.c_stride[k] = reduce ? 0 : d->strideC[k];
+    }
+    g.a_mul[0] = pl->nA0 > 1 ? pl->nA1 : 0;
+    g.a_mul[1] = pl->nA1 > 1 ? 1 : 0;
+    g.b_mul[0] = pl->nB0 > 1 ? pl->nB1 : 0;
+    g.b_mul[1] = pl->nB1 > 1 ? 1 : 0;
+    g.bias_mode = d->bias_mode;
+    g.bias_ld = d->bias_ld;
+    g.accumulate = d->accumulate ? 1 : 0;
+    g.relu = d->relu ? 1 : 0;
+    return NZB_OK;
+}
+
+static int run_gemm(const nzb_gemm_desc* d, const float* A, const float* B, float* C, const float* bias, void* ws,
+                    size_t ws_bytes, cudaStream_t stream) {
+    Plan pl;
+    int rc = make_plan(d, &pl);
+    if (rc != NZB_OK) return rc;
+    if (d->M == 0 || d->N == 0) return NZB_OK;
+    if (!A || !B || !C) return fail(NZB_ERR_BAD_ARG, "A, B and C must be non-null");
+    if (d->bias_mode != NZB_BIAS_NONE && !bias) return fail(NZB_ERR_BAD_ARG, "bias_mode set but bias is null");
+    if (d->K == 0) return fail(NZB_ERR_UNSUPPORTED, "K = 0 is not supported");
+    if (!ws || ws_bytes < pl.a_bytes + pl.b_bytes) return fail(NZB_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", pl.a_bytes + pl.b_bytes, ws ? ws_bytes : (size_t)0);
+    if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(NZB_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    __half* A16 = reinterpret_cast<__half*>(ws);
+    __half* B16 = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(ws) + pl.a_bytes);
+    // op(A) rows = M, contraction along columns. Stored M x K -> plain cast; stored K x M -> transpose.
+    rc = launch_cast(A, A16, d->M, d->K, d->lda, pl.Kp, d->transA ? 1 : 0, pl.nA0, pl.nA1, d->strideA[0],
+                     d->strideA[1], stream);
+    if (rc != NZB_OK) return rc;
+    // B' holds N rows of K: stored K x N -> transpose; stored N x K -> plain cast.
+    rc = launch_cast(B, B16, d->N, d->K, d->ldb, pl.Kp, d->transB ? 0 : 1, pl.nB0, pl.nB1, d->strideB[0],
+                     d->strideB[1], stream);
+    if (rc != NZB_OK) return rc;
+    pl.g.A16 = A16;
+    pl.g.B16 = B16;
+    pl.g.C = C;
+    pl.g.bias = bias;
+    return launch_gemm(pl.g, stream);
+}
+
+// NeuZephyr 4-D shapes -> descriptor (TensorCoreGEMMParallel / GEMMBackwardParallel rules).
+static int desc_from_shapes(const int64_t* sa, const int64_t* sb, const int64_t* sc, int backward, nzb_gemm_desc* d) {
+    if (!sa || !sb || !sc) return fail(NZB_ERR_BAD_ARG, "shape pointer is null");
+    for (int i = 0; i < 4; i++)
+        if (sa[i] < 0 || sb[i] < 0 || sc[i] < 0) return fail(NZB_ERR_BAD_ARG, "negative extent");
+    *d = nzb_gemm_desc{};
+    d->M = sa[2]; d->K = sa[3]; d->N = sb[3];
+    if (sb[2] != d->K) return fail(NZB_ERR_BAD_ARG, "A.W (%lld) != B.H (%lld)", (long long)sa[3], (long long)sb[2]);
+    if (sc[2] != d->M || sc[3] != d->N) return fail(NZB_ERR_BAD_ARG, "C matrix extent does not match A.H x B.W");
+    d->lda = d->K; d->ldb = d->N; d->ldc = d->N;
+    for (int k = 0; k < 2; k++) {
+        const int64_t a = sa[k], b = sb[k], c = sc[k];
+        const int64_t e = a > b ? a : b;
+        if (a < 1 || b < 1 || c < 1) return fail(NZB_ERR_BAD_ARG, "batch extents must be >= 1");
+        if ((a != e && a != 1) || (b != e && b != 1)) return fail(NZB_ERR_BAD_ARG, "batch extents are not broadcast compatible");
+        if (backward ? (c != e && c != 1) : (c != e)) return fail(NZB_ERR_BAD_ARG, "C batch extent does not match the operands");
+        if (e > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "batch extent exceeds 2^31");
+        d->batch[k] = (int32_t)e;
+    }
+    // contiguous strides {C*H*W, H*W}; extent-1 dimensions broadcast (src/OperationKernels.cu:978-986)
+    d->strideA[0] = sa[0] > 1 ? sa[1] * d->M * d->K : 0;
+    d->strideA[1] = sa[1] > 1 ? d->M * d->K : 0;
+    d->strideB[0] = sb[0] > 1 ? sb[1] * d->K * d->N : 0;
+    d->strideB[1] = sb[1] > 1 ? d->K * d->N : 0;
+    d->strideC[0] = sc[0] > 1 ? sc[1] * d->M * d->N : 0;
+    d->strideC[1] = sc[1] > 1 ? d->M * d->N : 0;
+    d->accumulate = backward ? 1 : 0;
+    return NZB_OK;
+}
+
+}  // namespace nzb
+
+using namespace nzb;
+
+extern "C" {
+
+int nzb_version(void) { return 100; }
+
+const char* nzb_last_error_string(void) { return g_err; }
+
+int nzb_device_status(int* status_out) {
+    if (!status_out) return fail(NZB_ERR_BAD_ARG, "status_out is null");
+    DeviceState* ds;
+    int rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    *status_out = *reinterpret_cast<volatile int*>(ds->status_host);
+    return NZB_OK;
+}
+
+int nzb_device_status_reset(void) {
+    DeviceState* ds;
+    int rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    *reinterpret_cast<volatile int*>(ds->status_host) = 0;
+    return NZB_OK;
+}
+
+int nzb_gemm_workspace_bytes(const nzb_gemm_desc* desc, size_t* bytes_out) {
+    if (!bytes_out) return fail(NZB_ERR_BAD_ARG, "bytes_out is null");
+    Plan pl;
+    int rc = make_plan(desc, &pl);
+    if (rc != NZB_OK) return rc;
+    *bytes_out = pl.a_bytes + pl.b_bytes;
+    return NZB_OK;
+}
+
+int nzb_gemm(const nzb_gemm_desc* desc, const float* A, const float* B, float* C, const float* bias, void* workspace,
+             size_t workspace_bytes, void* stream) {
+    return run_gemm(desc, A, B, C, bias, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int nzb_tensorcore_gemm_workspace_bytes(const int64_t shapeA[4], const int64_t shapeB[4], const int64_t shapeC[4],
+                                        size_t* bytes_out) {
+    nzb_gemm_desc d;
+    // the backward form accepts a superset of C shapes and needs the same scratch
+    int rc = desc_from_shapes(shapeA, shapeB, shapeC, 1, &d);
+    if (rc != NZB_OK) return rc;
+    return nzb_gemm_workspace_bytes(&d, bytes_out);
+}
+
+int nzb_tensorcore_gemm(const float* A, const float* B, float* C, const int64_t shapeA[4], const int64_t shapeB[4],
+                        const int64_t shapeC[4], void* workspace, size_t workspace_bytes, void* stream) {
+    nzb_gemm_desc d;
+    int rc = desc_from_shapes(shapeA, shapeB, shapeC, 0, &d);
+    if (rc != NZB_OK) return rc;
+    return run_gemm(&d, A, B, C, nullptr, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int nzb_gemm_backward(const float* A, const float* B, float* C, const int64_t shapeA[4], const int64_t shapeB[4],
+                      const int64_t shapeC[4], void* workspace, size_t workspace_bytes, void* stream) {
+    nzb_gemm_desc d;
+    int rc = desc_from_shapes(shapeA, shapeB, shapeC, 1, &d);
+    if (rc != NZB_OK) return rc;
+    return run_gemm(&d, A, B, C, nullptr, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int nzb_cast_f32_f16(const float* in, void* out_f16, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
+                     int transpose, void* stream) {
+    if (!in || !out_f16) return fail(NZB_ERR_BAD_ARG, "null pointer");
+    if (rows < 0 || cols < 0) return fail(NZB_ERR_BAD_ARG, "negative extent");
+    if (reinterpret_cast<uintptr_t>(out_f16) & 15) return fail(NZB_ERR_BAD_ARG, "fp16 destination must be 16-byte aligned");
+    return launch_cast(in, reinterpret_cast<__half*>(out_f16), rows, cols, ld_in, ld_out, transpose, 1, 1, 0, 0,
+                       static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,389 @@
+// fp16 x fp16 -> fp32 GEMM for sm_100a: TMA-fed shared-memory ring, tcgen05.mma into
+// tensor memory, fused epilogue (accumulate / bias / ReLU / fp32 store).
+//
+// Stands in for GeneralMatrixMulTensorKernel and its Cutting / CuttingAndCompress
+// passes (NeuZephyr src/OperationKernels.cu:821-883) behind the batched drivers
+// (:914-1144). Operands arrive as K-major fp16 copies: A' [nA][M][Kp], B' [nB][N][Kp].
+//
+// CTA layout (192 threads, persistent over a static round-robin tile list):
+//   warp 0    TMA producer (one lane)
+//   warp 1    tensor-memory allocator; one lane issues tcgen05.mma
+//   warps 2-5 epilogue: tcgen05.ld -> shared staging -> coalesced global stores
+// Two accumulators live in tensor memory so the epilogue of tile i overlaps the
+// main loop of tile i+1. Every mbarrier wait is bounded; on expiry the CTA raises an
+// abort flag, writes NZB_ERR_DEVICE_TIMEOUT to the status word, drains and returns.
+#include <cuda_fp16.h>
+
+#include "nzb_internal.h"
+#include "nzb_ptx.cuh"
+
+namespace nzb {
+
+struct GemmParams {
+    float* C;
+    int64_t ldc;
+    int32_t M, N, K;
+    int32_t tiles_m, tiles_n;
+    int32_t out_e0, out_e1, red_e0, red_e1;
+    int32_t a_mul0, a_mul1, b_mul0, b_mul1;
+    int64_t c_stride0, c_stride1;
+    const float* bias;
+    int64_t bias_ld;
+    int32_t bias_mode;
+    int32_t accumulate, relu;
+    int32_t k_blocks;     // ceil(K / 64)
+    int32_t last_ksteps;  // 16-wide MMA steps in the last k block (1..4)
+    int32_t vec4;         // C (and bias) allow aligned float4 access
+    int64_t total_tiles;
+    int* status;
+};
+
+template <int BN_, int STAGES_>
+struct GemmCfg {
+    static constexpr int BM = 128, BN = BN_, BK = 64, STAGES = STAGES_;
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int EPI_STRIDE = 36;  // floats per staged row: 16-byte aligned, conflict-free
+    static constexpr int EPI_BYTES = 4 * 32 * EPI_STRIDE * 4;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+    static constexpr int CHUNK = (BN < 32) ? BN : 32;  // accumulator columns per tcgen05.ld
+    static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
+};
+
+constexpr int kGroupM = 16;  // m-tiles per rasterisation group (keeps a wave's operands in L2)
+
+struct TileCoord {
+    int32_t mt, nt, b0, b1;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int64_t tile) {
+    const int64_t per_batch = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+    const int64_t ob = tile / per_batch;
+    const int32_t rem = static_cast<int32_t>(tile - ob * per_batch);
+    const int32_t group_size = kGroupM * p.tiles_n;
+    const int32_t g = rem / group_size;
+    const int32_t first_m = g * kGroupM;
+    const int32_t gm = min(p.tiles_m - first_m, kGroupM);
+    const int32_t within = rem - g * group_size;
+    TileCoord t;
+    t.mt = first_m + within % gm;
+    t.nt = within / gm;
+    t.b0 = static_cast<int32_t>(ob / p.out_e1);
+    t.b1 = static_cast<int32_t>(ob % p.out_e1);
+    return t;
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(192, 1)
+gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                        const GemmParams p) {
+    using namespace ptx;
+    constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* epi = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
+    uint64_t* full = bars;                  // [STAGES] TMA landed
+    uint64_t* empty = bars + STAGES;        // [STAGES] MMAs that read the stage retired
+    uint64_t* tfull = bars + 2 * STAGES;    // [2] accumulator complete
+    uint64_t* tempty = bars + 2 * STAGES + 2;  // [2] accumulator drained by the epilogue
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int32_t k_iters = p.red_e0 * p.red_e1 * p.k_blocks;  // per tile
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---------------- TMA producer ----------------
+            uint32_t it = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+                const TileCoord t = decode_tile(p, tile);
+                for (int32_t r0 = 0; r0 < p.red_e0 && ok; r0++) {
+                    for (int32_t r1 = 0; r1 < p.red_e1 && ok; r1++) {
+                        const int32_t i0 = t.b0 + r0, i1 = t.b1 + r1;
+                        const int32_t za = i0 * p.a_mul0 + i1 * p.a_mul1;
+                        const int32_t zb = i0 * p.b_mul0 + i1 * p.b_mul1;
+                        for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                            if (!mbar_wait_bounded(&empty[s], ph ^ 1, abort_flag)) {
+                                ok = false;
+                                break;
+                            }
+                            uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
+                            mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
+                            tma_load_3d(sa, &tmA, kb * 64, t.mt * 128, za, &full[s]);
+                            tma_load_3d(sa + Cfg::A_BYTES, &tmB, kb * 64, t.nt * BN, zb, &full[s]);
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                // Wait (bounded) for the copies still in flight so none lands after exit.
+                const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
+                for (uint32_t j = first; j < it; j++) {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1)) {
+                        if (clock64() - t0 > kWaitCycleLimit) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---------------- MMA issuer ----------------
+            constexpr uint32_t idesc = make_idesc_f16_f32(128, BN);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, tcount++) {
+                const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+                if (!mbar_wait_bounded(&tempty[acc], aph ^ 1, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int32_t kk = 0; kk < k_iters; kk++, it++) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait_bounded(&full[s], ph, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                    const uint64_t da = make_sw128_kmajor_desc(sa);
+                    const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                    const int32_t kb = kk % p.k_blocks;
+                    const int32_t ksteps = (kb == p.k_blocks - 1) ? p.last_ksteps : 4;
+                    for (int32_t j = 0; j < ksteps; j++) {
+                        // one k step = 16 halves = 32 bytes = 2 descriptor address units
+                        mma_f16_ss(d_tmem, da + 2 * j, db + 2 * j, idesc, (kk > 0 || j > 0) ? 1u : 0u);
+                    }
+                    mma_commit(&empty[s]);
+                }
+                if (ok) mma_commit(&tfull[acc]);
+            }
+        }
+    } else {
+        // ---------------- epilogue warps ----------------
+        const int q = warp & 3;  // tensor-memory lane quarter this warp may read
+        float* stage = epi + (warp - 2) * 32 * Cfg::EPI_STRIDE;
+        uint32_t tcount = 0;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, tcount++) {
+            const TileCoord t = decode_tile(p, tile);
+            const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+            if (!mbar_wait_bounded(&tfull[acc], aph, abort_flag)) break;
+            tc_fence_after();
+            float* Cb = p.C + t.b0 * p.c_stride0 + t.b1 * p.c_stride1;
+            const int32_t row0 = t.mt * 128 + q * 32;
+            const int32_t col_tile = t.nt * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += Cfg::CHUNK) {
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c0;
+                if constexpr (Cfg::CHUNK == 32) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(taddr, v);
+                    tmem_ld_wait();
+                    float4* dst = reinterpret_cast<float4*>(stage + lane * Cfg::EPI_STRIDE);
+#pragma unroll
+                    for (int j = 0; j < 8; j++)
+                        dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                             __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                } else {
+                    uint32_t v[16];
+                    tmem_ld_32x16(taddr, v);
+                    tmem_ld_wait();
+                    float4* dst = reinterpret_cast<float4*>(stage + lane * Cfg::EPI_STRIDE);
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                             __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+                }
+                __syncwarp();
+                const int32_t gc0 = col_tile + c0;
+                if (p.vec4) {
+                    constexpr int LPR = Cfg::CHUNK / 4;  // lanes per staged row
+                    constexpr int RPI = 32 / LPR;        // rows per iteration
+                    const int cl = (lane % LPR) * 4;
+                    const int32_t gc = gc0 + cl;
+#pragma unroll
+                    for (int rr = 0; rr < 32; rr += RPI) {
+                        const int r = rr + lane / LPR;
+                        const int32_t gr = row0 + r;
+                        if (gr < p.M && gc < p.N) {  // N % 4 == 0 on this path: the whole float4 is in range
+                            float4 x = *reinterpret_cast<const float4*>(stage + r * Cfg::EPI_STRIDE + cl);
+                            float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
+                            if (p.accumulate) {
+                                const float4 o = *reinterpret_cast<const float4*>(cp);
+                                x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+                            }
+                            if (p.bias_mode == NZB_BIAS_ROW) {
+                                const float4 b = *reinterpret_cast<const float4*>(p.bias + gc);
+                                x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                            } else if (p.bias_mode == NZB_BIAS_COL) {
+                                const float b = p.bias[gr];
+                                x.x += b; x.y += b; x.z += b; x.w += b;
+                            } else if (p.bias_mode == NZB_BIAS_MATRIX) {
+                                const float4 b = *reinterpret_cast<const float4*>(
+                                    p.bias + static_cast<int64_t>(gr) * p.bias_ld + gc);
+                                x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                            }
+                            if (p.relu) {
+                                x.x = fmaxf(x.x, 0.f); x.y = fmaxf(x.y, 0.f);
+                                x.z = fmaxf(x.z, 0.f); x.w = fmaxf(x.w, 0.f);
+                            }
+                            *reinterpret_cast<float4*>(cp) = x;
+                        }
+                    }
+                } else {
+                    constexpr int RPI = 32 / Cfg::CHUNK;  // 1, or 2 when the chunk is 16 wide
+                    const int cl = lane % Cfg::CHUNK;
+                    const int32_t gc = gc0 + cl;
+#pragma unroll 4
+                    for (int rr = 0; rr < 32; rr += RPI) {
+                        const int r = rr + lane / Cfg::CHUNK;
+                        const int32_t gr = row0 + r;
+                        if (gr < p.M && gc < p.N) {
+                            float x = stage[r * Cfg::EPI_STRIDE + cl];
+                            float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
+                            if (p.accumulate) x += *cp;
+                            if (p.bias_mode == NZB_BIAS_ROW) x += p.bias[gc];
+                            else if (p.bias_mode == NZB_BIAS_COL) x += p.bias[gr];
+                            else if (p.bias_mode == NZB_BIAS_MATRIX)
+                                x += p.bias[static_cast<int64_t>(gr) * p.bias_ld + gc];
+                            if (p.relu) x = fmaxf(x, 0.f);
+                            *cp = x;
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = NZB_ERR_DEVICE_TIMEOUT;
+        __threadfence_system();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+static int make_operand_map(CUtensorMap* map, const __half* base, int64_t K, int64_t Kp, int64_t rows, int64_t nmat,
+                            int box_rows) {
+    EncodeTiledFn enc;
+    int rc = get_encode_tiled(&enc);
+    if (rc != NZB_OK) return rc;
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)nmat};
+    cuuint64_t strides[2] = {(cuuint64_t)Kp * 2, (cuuint64_t)rows * (cuuint64_t)Kp * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return NZB_OK;
+}
+
+template <class Cfg>
+static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds, cudaStream_t stream) {
+    CUtensorMap tmA, tmB;
+    int rc = make_operand_map(&tmA, g.A16, g.K, g.Kp, g.M, g.nA, 128);
+    if (rc != NZB_OK) return rc;
+    rc = make_operand_map(&tmB, g.B16, g.K, g.Kp, g.N, g.nB, Cfg::BN);
+    if (rc != NZB_OK) return rc;
+    p.tiles_n = (int32_t)((g.N + Cfg::BN - 1) / Cfg::BN);
+    p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * p.out_e0 * p.out_e1;
+    static bool attr_set = false;  // per instantiation
+    if (!attr_set) {
+        NZB_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    const int64_t grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
+    gemm_f16_tcgen05_kernel<Cfg><<<(unsigned)grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    NZB_CUDA_TRY(cudaGetLastError());
+    return NZB_OK;
+}
+
+int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
+    DeviceState* ds;
+    int rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    if (g.M <= 0 || g.N <= 0) return NZB_OK;
+    if (g.K <= 0) return fail(NZB_ERR_UNSUPPORTED, "K = 0 is not supported");
+    if (g.M > INT32_MAX - 256 || g.N > INT32_MAX - 256 || g.K > INT32_MAX - 256 || g.nA > INT32_MAX ||
+        g.nB > INT32_MAX)
+        return fail(NZB_ERR_UNSUPPORTED, "extent exceeds 2^31");
+    GemmParams p{};
+    p.C = g.C;
+    p.ldc = g.ldc;
+    p.M = (int32_t)g.M;
+    p.N = (int32_t)g.N;
+    p.K = (int32_t)g.K;
+    p.tiles_m = (int32_t)((g.M + 127) / 128);
+    p.out_e0 = g.out_e[0]; p.out_e1 = g.out_e[1];
+    p.red_e0 = g.red_e[0]; p.red_e1 = g.red_e[1];
+    p.a_mul0 = (int32_t)g.a_mul[0]; p.a_mul1 = (int32_t)g.a_mul[1];
+    p.b_mul0 = (int32_t)g.b_mul[0]; p.b_mul1 = (int32_t)g.b_mul[1];
+    p.c_stride0 = g.c_stride[0]; p.c_stride1 = g.c_stride[1];
+    p.bias = g.bias;
+    p.bias_ld = g.bias_ld;
+    p.bias_mode = g.bias ? g.bias_mode : NZB_BIAS_NONE;
+    p.accumulate = g.accumulate;
+    p.relu = g.relu;
+    p.k_blocks = (int32_t)((g.K + 63) / 64);
+    p.last_ksteps = (int32_t)((g.K - (int64_t)(p.k_blocks - 1) * 64 + 15) / 16);
+    p.status = ds->status_dev;
+    bool v4 = (g.N % 4 == 0) && (g.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.C) & 15) == 0) &&
+              (g.c_stride[0] % 4 == 0) && (g.c_stride[1] % 4 == 0);
+    if (p.bias_mode == NZB_BIAS_ROW) v4 = v4 && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);
+    if (p.bias_mode == NZB_BIAS_MATRIX)
+        v4 = v4 && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0) && (g.bias_ld % 4 == 0);
+    p.vec4 = v4 ? 1 : 0;
+
+    if (g.N > 128) return launch_cfg<GemmCfg<256, 4>>(g, p, *ds, stream);
+    if (g.N > 64) return launch_cfg<GemmCfg<128, 6>>(g, p, *ds, stream);
+    if (g.N > 32) return launch_cfg<GemmCfg<64, 8>>(g, p, *ds, stream);
+    if (g.N > 16) return launch_cfg<GemmCfg<32, 8>>(g, p, *ds, stream);
+    return launch_cfg<GemmCfg<16, 8>>(g, p, *ds, stream);
+}
+
+}  // namespace nzb

@@ -1,0 +1,70 @@
+// Host-side internals shared by the translation units of libnzb.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stddef.h>
+
+#include "../../include/nzb.h"
+
+namespace nzb {
+
+// Records the message returned by nzb_last_error_string() and passes the code through.
+int fail(int code, const char* fmt, ...);
+
+#define NZB_CUDA_TRY(expr)                                                                         \
+    do {                                                                                           \
+        cudaError_t _e = (expr);                                                                   \
+        if (_e != cudaSuccess)                                                                     \
+            return ::nzb::fail(NZB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e), \
+                               __FILE__, __LINE__);                                                \
+    } while (0)
+
+// Per-device state created on first use: SM count, the mapped status word kernels write
+// when a bounded wait expires, and the driver entry point for tensor-map encoding.
+struct DeviceState {
+    int device = -1;
+    int sm_count = 0;
+    int cc_major = 0;
+    int* status_host = nullptr;  // mapped, pinned
+    int* status_dev = nullptr;   // device alias of status_host
+};
+int get_device_state(DeviceState** out);
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+int get_encode_tiled(EncodeTiledFn* out);
+
+inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+// fp16 operand copy layout: rows x Kp halves, Kp = K rounded up to one 128-byte line.
+constexpr int64_t kOperandKAlign = 64;
+
+// Launchers (defined in the .cu files). All return NZB_* codes.
+// Batched fp32 -> fp16 cast of `nmat` matrices; matrix b starts at in + b*in_batch_stride
+// and out + b*rows*ld_out.
+int launch_cast(const float* in, __half* out, int64_t rows, int64_t cols, int64_t ld_in, int64_t ld_out,
+                int transpose, int64_t nmat0, int64_t nmat1, int64_t in_stride0, int64_t in_stride1,
+                cudaStream_t stream);
+
+struct GemmLaunch {
+    // fp16 operands: A' [nA][M][Kp], B' [nB][N][Kp]
+    const __half* A16;
+    const __half* B16;
+    int64_t nA, nB;  // number of matrices in each operand copy
+    int64_t M, N, K, Kp;
+    float* C;
+    int64_t ldc;
+    // batch grid; for each dimension d exactly one of out_e[d] / red_e[d] is > 1
+    int32_t out_e[2], red_e[2];
+    int64_t a_mul[2], b_mul[2];  // matrix-index multipliers of A' / B' along each batch dimension
+    int64_t c_stride[2];         // element stride of C along each (output) batch dimension
+    const float* bias;
+    int32_t bias_mode;
+    int64_t bias_ld;
+    int32_t accumulate, relu;
+};
+int launch_gemm(const GemmLaunch& g, cudaStream_t stream);
+
+}  // namespace nzb

@@ -1,0 +1,106 @@
+"""Torch-tensor conveniences over the C ABI (device memory and the current stream come
+from torch; every computation is a libnzb kernel). Used by the tests and the benchmark."""
+import ctypes
+
+import torch
+
+from . import _capi as C
+
+_ws_cache = {}
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else None
+
+
+def _workspace(nbytes, device):
+    """Grow-only scratch buffer per device (stream-ordered reuse on torch's current stream)."""
+    buf = _ws_cache.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+        _ws_cache[device] = buf
+    return buf
+
+
+def _check_f32_cuda(*ts):
+    for t in ts:
+        if t is None:
+            continue
+        if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+            raise ValueError("expected contiguous float32 CUDA tensors")
+
+
+def gemm_workspace_bytes(desc):
+    n = ctypes.c_size_t(0)
+    C.check(C.lib().nzb_gemm_workspace_bytes(ctypes.byref(desc), ctypes.byref(n)))
+    return n.value
+
+
+def gemm(A, B, out=None, transA=False, transB=False, bias=None, bias_mode=C.BIAS_NONE, relu=False,
+         accumulate=False):
+    """C = op(A) @ op(B) for 2-D row-major float32 tensors through nzb_gemm."""
+    _check_f32_cuda(A, B, bias, out)
+    M, K = (A.shape[1], A.shape[0]) if transA else A.shape
+    K2, N = (B.shape[1], B.shape[0]) if transB else B.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=A.device)
+    d = C.GemmDesc()
+    d.M, d.N, d.K = M, N, K
+    d.lda, d.ldb, d.ldc = A.shape[1], B.shape[1], N
+    d.transA, d.transB = int(transA), int(transB)
+    d.batch[0] = d.batch[1] = 1
+    d.accumulate, d.relu = int(accumulate), int(relu)
+    d.bias_mode = bias_mode if bias is not None else C.BIAS_NONE
+    d.bias_ld = N
+    ws = _workspace(gemm_workspace_bytes(d), A.device)
+    C.check(C.lib().nzb_gemm(ctypes.byref(d), _ptr(A), _ptr(B), _ptr(out), _ptr(bias), _ptr(ws), ws.numel(),
+                             _stream()))
+    return out
+
+
+def _ws4(A, B, Cs):
+    n = ctypes.c_size_t(0)
+    C.check(C.lib().nzb_tensorcore_gemm_workspace_bytes(C.shape4(A.shape), C.shape4(B.shape), C.shape4(Cs),
+                                                        ctypes.byref(n)))
+    return n.value
+
+
+def tensorcore_gemm(A, B, out=None):
+    """4-D batched forward GEMM with N/C broadcast (the iTensorCoreGEMM seam)."""
+    _check_f32_cuda(A, B, out)
+    sc = (max(A.shape[0], B.shape[0]), max(A.shape[1], B.shape[1]), A.shape[2], B.shape[3])
+    if out is None:
+        out = torch.empty(sc, dtype=torch.float32, device=A.device)
+    ws = _workspace(_ws4(A, B, out.shape), A.device)
+    C.check(C.lib().nzb_tensorcore_gemm(_ptr(A), _ptr(B), _ptr(out), C.shape4(A.shape), C.shape4(B.shape),
+                                        C.shape4(out.shape), _ptr(ws), ws.numel(), _stream()))
+    return out
+
+
+def gemm_backward(A, B, out):
+    """out += A @ B reduced over broadcast batch dims of out (the iGEMMBackward seam)."""
+    _check_f32_cuda(A, B, out)
+    ws = _workspace(_ws4(A, B, out.shape), A.device)
+    C.check(C.lib().nzb_gemm_backward(_ptr(A), _ptr(B), _ptr(out), C.shape4(A.shape), C.shape4(B.shape),
+                                      C.shape4(out.shape), _ptr(ws), ws.numel(), _stream()))
+    return out
+
+
+def cast_f32_f16(x, transpose=False):
+    """Returns the [rows][ld_out] fp16 operand copy of a 2-D float32 tensor."""
+    _check_f32_cuda(x)
+    rows, cols = (x.shape[1], x.shape[0]) if transpose else x.shape
+    ld_out = (cols + 63) // 64 * 64
+    out = torch.empty((rows, ld_out), dtype=torch.float16, device=x.device)
+    C.check(C.lib().nzb_cast_f32_f16(_ptr(x), _ptr(out), rows, cols, x.shape[1], ld_out, int(transpose), _stream()))
+    return out
+
+
+def device_status():
+    return C.device_status()

@@ -1,0 +1,226 @@
+"""Parity of the sm_100a GEMM path (through the C ABI) against the host oracle.
+
+Error metric: e_max = max|x - x64| / max|x64| per output tensor.
+  * against the fp64 product of the fp16-rounded operands (what the reference's WMMA
+    kernel approximates): e_max <= 2e-5 -- only fp32 accumulation order differs;
+  * against the fp64 product of the raw fp32 operands: e_max <= 1e-2, the bound the
+    baseline contract states for this path.
+"""
+import ctypes
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import nz_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TOL_ROUNDED = 2e-5
+TOL_RAW = 1e-2
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_kat.json")))
+
+
+@pytest.fixture(scope="module")
+def nz():
+    import neuzephyr_b200 as nz
+    return nz
+
+
+def emax(x, ref):
+    ref = np.asarray(ref, dtype=np.float64)
+    den = np.max(np.abs(ref))
+    return float(np.max(np.abs(np.asarray(x, dtype=np.float64) - ref)) / (den if den > 0 else 1.0))
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).cuda()
+
+
+def check_status(nz):
+    torch.cuda.synchronize()
+    assert nz.device_status() == 0
+
+
+SHAPES = [
+    (1, 1, 1), (16, 16, 16), (15, 17, 16), (17, 15, 33), (127, 129, 131), (128, 256, 64), (129, 257, 65),
+    (300, 40, 700), (1, 512, 640), (640, 1, 512), (256, 512, 1), (1024, 1024, 1024), (3, 1000, 7),
+    (513, 72, 1030), (200, 130, 48), (2000, 24, 200),
+]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+def test_gemm_shapes(nz, M, N, K):
+    rng = np.random.default_rng(M * 1000003 + N * 1009 + K)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    C = nz.gemm(dev(A), dev(B)).cpu().numpy()
+    check_status(nz)
+    assert emax(C, O.gemm_f64(A, B, True)) <= TOL_ROUNDED
+    assert emax(C, O.gemm_f64(A, B, False)) <= TOL_RAW
+
+
+def test_config1_seed0_1024(nz):
+    """The headline configuration's CPU-runnable case: 1024^3, uniform[-1,1], seed 0."""
+    rng = np.random.default_rng(0)
+    A = rng.uniform(-1, 1, (1024, 1024)).astype(np.float32)
+    B = rng.uniform(-1, 1, (1024, 1024)).astype(np.float32)
+    C = nz.gemm(dev(A), dev(B)).cpu().numpy()
+    check_status(nz)
+    e_r = emax(C, O.gemm_f64(A, B, True))
+    e_raw = emax(C, O.gemm_f64(A, B, False))
+    assert e_r <= TOL_ROUNDED and e_raw <= TOL_RAW
+
+
+@pytest.mark.parametrize("tA,tB", [(False, False), (True, False), (False, True), (True, True)])
+def test_gemm_transposed_operands(nz, tA, tB):
+    M, N, K = 150, 90, 210
+    rng = np.random.default_rng(42)
+    A = rng.normal(0, 1, (M, K)).astype(np.float32)
+    B = rng.normal(0, 1, (K, N)).astype(np.float32)
+    As = np.ascontiguousarray(A.T) if tA else A
+    Bs = np.ascontiguousarray(B.T) if tB else B
+    C = nz.gemm(dev(As), dev(Bs), transA=tA, transB=tB).cpu().numpy()
+    check_status(nz)
+    assert emax(C, O.gemm_f64(A, B, True)) <= TOL_ROUNDED
+
+
+def test_gemm_epilogue_bias_relu_accumulate(nz):
+    from neuzephyr_b200 import _capi as C
+    rng = np.random.default_rng(7)
+    for (M, N, K) in [(130, 96, 200), (77, 33, 50)]:
+        A = rng.normal(0, 1, (M, K)).astype(np.float32)
+        B = rng.normal(0, 1, (K, N)).astype(np.float32)
+        ref = O.gemm_f64(A, B, True)
+        brow = rng.normal(0, 1, N).astype(np.float32)
+        bcol = rng.normal(0, 1, M).astype(np.float32)
+        bmat = rng.normal(0, 1, (M, N)).astype(np.float32)
+        got = nz.gemm(dev(A), dev(B), bias=dev(brow), bias_mode=C.BIAS_ROW).cpu().numpy()
+        assert emax(got, ref + brow[None, :]) <= TOL_ROUNDED
+        got = nz.gemm(dev(A), dev(B), bias=dev(bcol), bias_mode=C.BIAS_COL, relu=True).cpu().numpy()
+        assert emax(got, np.maximum(ref + bcol[:, None], 0)) <= TOL_ROUNDED
+        got = nz.gemm(dev(A), dev(B), bias=dev(bmat), bias_mode=C.BIAS_MATRIX, relu=True).cpu().numpy()
+        assert emax(got, np.maximum(ref + bmat, 0)) <= TOL_ROUNDED
+        c0 = rng.normal(0, 1, (M, N)).astype(np.float32)
+        out = dev(c0)
+        nz.gemm(dev(A), dev(B), out=out, accumulate=True)
+        assert emax(out.cpu().numpy(), ref + c0) <= TOL_ROUNDED
+    check_status(nz)
+
+
+def test_reference_kat_matmul_forward(nz):
+    """TensorCore.TensorCoreGEMMTest / NodeBasic.MatMulForward literals; integers are exact in fp16."""
+    g = GOLD["matmul_forward"]
+    A = np.array(g["A"], np.float32).reshape(g["shapeA"])
+    B = np.array(g["B"], np.float32).reshape(g["shapeB"])
+    C = nz.tensorcore_gemm(dev(A), dev(B)).cpu().numpy()
+    check_status(nz)
+    assert C.shape == tuple(g["shapeC"])
+    assert np.array_equal(C, np.array(g["C"], np.float32).reshape(g["shapeC"]))
+
+
+def test_reference_kat_matmul_backward(nz):
+    """NodeBasic.MatMulBackwardSpecial / MatMulBackwardNormal: dA = dC B^T, dB = A^T dC, summed over broadcast dims."""
+    g = GOLD["matmul_backward_normal"]
+    A = np.array(g["A"], np.float32).reshape(g["shapeA"])
+    B = np.array(g["B"], np.float32).reshape(g["shapeB"])
+    dC = np.array(g["dC"], np.float32).reshape(2, 3, 2, 2)
+    dA = torch.zeros(g["shapeA"], device="cuda")
+    dB = torch.zeros(g["shapeB"], device="cuda")
+    nz.gemm_backward(dev(dC), dev(O.transpose(B)), dA)
+    nz.gemm_backward(dev(O.transpose(A)), dev(dC), dB)
+    check_status(nz)
+    assert np.array_equal(dA.cpu().numpy().ravel(), np.array(g["dA"], np.float32))
+    assert np.array_equal(dB.cpu().numpy().ravel(), np.array(g["dB"], np.float32))
+    s = GOLD["matmul_backward_special"]
+    A1 = torch.ones(s["shapeA"], device="cuda")
+    B1 = torch.ones(s["shapeB"], device="cuda")
+    dC1 = torch.ones((2, 3, 2, 2), device="cuda")
+    dA1 = torch.zeros(s["shapeA"], device="cuda")
+    dB1 = torch.zeros(s["shapeB"], device="cuda")
+    nz.gemm_backward(dC1, dev(O.transpose(B1.cpu().numpy())), dA1)
+    nz.gemm_backward(dev(O.transpose(A1.cpu().numpy())), dC1, dB1)
+    assert torch.all(dA1 == s["dA_fill"]) and torch.all(dB1 == s["dB_fill"])
+
+
+@pytest.mark.parametrize("sa,sb", [((2, 1, 40, 70), (1, 3, 70, 50)), ((3, 2, 33, 17), (3, 2, 17, 65)),
+                                   ((1, 1, 20, 30), (4, 1, 30, 10)), ((2, 3, 130, 64), (1, 1, 64, 24))])
+def test_batched_broadcast_forward(nz, sa, sb):
+    rng = np.random.default_rng(sum(sa) * 31 + sum(sb))
+    A = rng.uniform(-1, 1, sa).astype(np.float32)
+    B = rng.uniform(-1, 1, sb).astype(np.float32)
+    C = nz.tensorcore_gemm(dev(A), dev(B)).cpu().numpy()
+    check_status(nz)
+    assert emax(C, O.gemm_forward(A, B, True, f64=True)) <= TOL_ROUNDED
+
+
+@pytest.mark.parametrize("sa,sb,sc", [
+    ((2, 3, 20, 30), (1, 3, 30, 10), (2, 3, 20, 10)),   # no reduction
+    ((2, 3, 30, 20), (2, 3, 20, 10), (1, 3, 30, 10)),   # sum over N
+    ((4, 2, 16, 100), (4, 2, 100, 8), (1, 1, 16, 8)),   # sum over N and C
+    ((2, 3, 30, 20), (2, 3, 20, 10), (2, 1, 30, 10)),   # sum over C
+])
+def test_batched_backward_accumulate_and_reduce(nz, sa, sb, sc):
+    rng = np.random.default_rng(sum(sa) * 17 + sum(sc))
+    A = rng.uniform(-1, 1, sa).astype(np.float32)
+    B = rng.uniform(-1, 1, sb).astype(np.float32)
+    C0 = rng.uniform(-1, 1, sc).astype(np.float32)
+    ref = C0.astype(np.float64)
+    O.gemm_backward(A, B, ref, True)
+    out = dev(C0)
+    nz.gemm_backward(dev(A), dev(B), out)
+    check_status(nz)
+    assert emax(out.cpu().numpy(), ref) <= TOL_ROUNDED
+
+
+def test_cast_matches_oracle_bits(nz):
+    rng = np.random.default_rng(5)
+    x = np.concatenate([rng.uniform(-1, 1, 3000), rng.normal(0, 300, 3000), rng.uniform(-1e-5, 1e-5, 2000),
+                        [65504, 65519, 65520, 7e4, -7e4, 2.0 ** -24, 2.0 ** -25, 0.0]]).astype(np.float32)
+    x = x[: (x.size // 77) * 77].reshape(-1, 77)
+    got = nz.cast_f32_f16(dev(x)).cpu().numpy()
+    assert got.shape[1] == 128 and np.all(got[:, 77:] == 0)
+    assert np.array_equal(got[:, :77].view(np.uint16), O.f16_bits(x))
+    gt = nz.cast_f32_f16(dev(x), transpose=True).cpu().numpy()
+    assert np.array_equal(gt[:, : x.shape[0]].view(np.uint16), O.f16_bits(x.T.copy()))
+    assert np.all(gt[:, x.shape[0]:] == 0)
+
+
+def test_linearity_large(nz):
+    """Size-independent property at a size the CPU oracle does not check in full:
+    (A1 + A2) B == A1 B + A2 B for operands whose sums are exact in fp16 (small integers),
+    plus sampled rows against the fp64 oracle."""
+    M, N, K = 2048, 2304, 4096
+    rng = np.random.default_rng(99)
+    A1 = rng.integers(-4, 5, (M, K)).astype(np.float32)
+    A2 = rng.integers(-4, 5, (M, K)).astype(np.float32)
+    B = rng.integers(-4, 5, (K, N)).astype(np.float32)
+    Bd = dev(B)
+    c12 = nz.gemm(dev(A1 + A2), Bd)
+    c1 = nz.gemm(dev(A1), Bd)
+    c2 = nz.gemm(dev(A2), Bd)
+    check_status(nz)
+    assert torch.equal(c12, c1 + c2)  # all partial sums are integers below 2^24: exact
+    rows = np.array([0, 1, 127, 128, 1000, 2047])
+    assert np.array_equal(c1.cpu().numpy()[rows], O.gemm_f64_rows(A1, B, rows, True).astype(np.float32))
+
+
+def test_argument_errors(nz):
+    from neuzephyr_b200 import _capi as C
+    L = C.lib()
+    d = C.GemmDesc()
+    d.M, d.N, d.K = 4, 4, 4
+    d.lda = d.ldb = d.ldc = 4
+    d.batch[0] = d.batch[1] = 1
+    a = torch.zeros(16, device="cuda")
+    p = ctypes.c_void_p(a.data_ptr())
+    assert L.nzb_gemm(ctypes.byref(d), p, p, p, None, None, 0, None) == C.ERR_WORKSPACE
+    assert L.nzb_gemm(ctypes.byref(d), None, p, p, None, p, 1 << 20, None) == C.ERR_BAD_ARG
+    d.lda = 2
+    assert L.nzb_gemm(ctypes.byref(d), p, p, p, None, p, 1 << 20, None) == C.ERR_BAD_ARG
+    bad = C.shape4((1, 1, 4, 5))
+    ok = C.shape4((1, 1, 4, 4))
+    assert L.nzb_tensorcore_gemm(p, p, p, bad, ok, ok, p, 1 << 20, None) == C.ERR_BAD_ARG
+    assert b"B.H" in L.nzb_last_error_string()
