@@ -1,0 +1,298 @@
+#!/usr/bin/env python
+"""Benchmark of the dense-contraction hot path: C = A.B at 8192^3, fp32 in/out, fp16
+operands, fp32 accumulation (NeuZephyr's GEMMTensorCore).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one pass of the hot path over one synthetic problem: fp32 -> fp16 operand
+staging (2 kernels) + the tcgen05 GEMM (1 kernel), through the C ABI (nzb_gemm).
+Prints ONE JSON line on rank 0. Under torchrun every rank runs an independent replica of
+the problem (the GEMM itself has no exchange step); the time is the max over ranks.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M = N = K = 8192
+FLOP = 2.0 * M * N * K
+WORKLOAD = "gemm 8192x8192x8192, fp32 row-major in/out, fp16 operands (RN), fp32 accumulate, uniform[-1,1]"
+METRIC = "gemm_tflops_8192"
+UNIT = "TFLOP/s"
+CPU_SAMPLE_ROWS = 256  # rows of C computed by the CPU baseline per step
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["bf16_tflops"]), float(p["hbm_gbs"]), "measured"
+    except Exception:
+        return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx = float(r[1])
+                for nme, v in zip(names, r[3:7]):
+                    if v.lower().startswith("active"):
+                        reasons.add(nme)
+            except Exception:
+                pass
+        sm.sort()
+        # under load = the upper half of the samples (idle samples bracket the timed region)
+        load = sm[len(sm) // 2:] if sm else []
+        med = load[len(load) // 2] if load else None
+        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def cpu_baseline(seconds_hint=None):
+    """Times the host oracle (fp16-rounded operands, fp32 accumulation, all threads) on a
+    bounded sample: CPU_SAMPLE_ROWS rows of the 8192^3 product."""
+    import numpy as np
+    from oracle import nz_oracle as O
+    rng = np.random.default_rng(0)
+    A = rng.uniform(-1, 1, (CPU_SAMPLE_ROWS, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    Ar, Br = O.round_f16(A), O.round_f16(B)
+    O.gemm_f32(Ar[:8], Br, False)  # warm the thread pool
+    t0 = time.perf_counter()
+    O.gemm_f32(Ar, Br, False)
+    dt = time.perf_counter() - t0
+    tf = 2.0 * CPU_SAMPLE_ROWS * N * K / dt / 1e12
+    return {"value": tf, "unit": UNIT, "cores": O.num_threads(), "kind": "port",
+            "sample": "%d of %d rows of C (%.1f GFLOP), operands pre-rounded to fp16, %.2f s"
+                      % (CPU_SAMPLE_ROWS, M, 2.0 * CPU_SAMPLE_ROWS * N * K / 1e9, dt)}
+
+
+def run_ours(args):
+    import ctypes
+    import torch
+    import torch.distributed as dist
+    import neuzephyr_b200 as nz
+    from neuzephyr_b200 import _capi as C
+
+    rank, world, local = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    L = C.lib()
+    dev = torch.device("cuda", local)
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+    A = torch.rand((M, K), device=dev, generator=g) * 2 - 1
+    B = torch.rand((K, N), device=dev, generator=g) * 2 - 1
+    Cd = torch.empty((M, N), device=dev)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        nz.gemm(A, B, out=Cd)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    # ---- device-resident timing: `value` -------------------------------------------------
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    if nz.device_status() != 0:
+        raise SystemExit("device-side wait expired (status %d)" % nz.device_status())
+
+    # ---- GEMM kernel alone, for the roofline (fp16 operands already staged) ------------
+    A16 = nz.cast_f32_f16(A)
+    B16 = nz.cast_f32_f16(B, transpose=True)
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(3):
+        nz.gemm_f16(A16, B16, M, N, K, out=Cd)
+    torch.cuda.synchronize()
+    k0.record(stream)
+    for _ in range(args.steps):
+        nz.gemm_f16(A16, B16, M, N, K, out=Cd)
+    k1.record(stream)
+    torch.cuda.synchronize()
+    kms = k0.elapsed_time(k1) / args.steps
+    del A16, B16
+
+    # ---- end to end through the C ABI with host buffers: `e2e` ----------------------------
+    hA = torch.empty((M, K), dtype=torch.float32).pin_memory()
+    hB = torch.empty((K, N), dtype=torch.float32).pin_memory()
+    hC = torch.empty((M, N), dtype=torch.float32).pin_memory()
+    hA.copy_(A)
+    hB.copy_(B)
+    e2e_steps = max(2, min(args.steps, 5))
+
+    def e2e_step():
+        A.copy_(hA, non_blocking=True)
+        B.copy_(hB, non_blocking=True)
+        nz.gemm(A, B, out=Cd)
+        hC.copy_(Cd, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    e0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record(stream)
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    t = torch.tensor([ms, kms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, kms, e2e_ms = [float(x) for x in t.tolist()]
+    if rank == 0:
+        peak_tf, peak_hbm, how = measured_peaks()
+        achieved = FLOP / (kms * 1e-3) / 1e12
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "gemm_8192_traffic.json")
+        if os.path.exists(tpath):
+            try:
+                traffic = json.load(open(tpath)).get("dram_bytes_per_launch")
+            except Exception:
+                traffic = None
+        out = {
+            "metric": METRIC, "value": world * FLOP / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "parallelism": "replicas only (x%d)" % world,
+                       "l2": "inputs 512 MiB + output 256 MiB per step exceed the 126 MB L2; no flush needed",
+                       "timed_region": "nzb_gemm: 2 staging kernels + 1 tcgen05 GEMM kernel per step"},
+            "e2e": {"value": world * FLOP / (e2e_ms * 1e-3) / 1e12, "unit": UNIT,
+                    "h2d_bytes_per_step": 4 * (M * K + K * N), "d2h_bytes_per_step": 4 * M * N,
+                    "ms_per_step": e2e_ms, "steps": e2e_steps},
+            "gpu_launches": 3 * args.steps,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+                         "frac": achieved / peak_tf, "traffic": traffic, "kernel": "gemm_f16_tcgen05_kernel",
+                         "kernel_ms": kms, "peak_source": "of %s (cuBLAS bf16 burst)" % how,
+                         "frac_of_nominal_2250": achieved / 2250.0},
+            "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu:
+            out["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference arm. NeuZephyr has no CPU implementation: its own path is the WMMA
+    kernel behind GEMMTensorCore, which runs on the GPU. When the library built from the
+    reference's sources is present (oracle/_ref), it is timed through GEMMTensorCore on
+    this box's GPU; the host oracle port is timed beside it as the CPU baseline."""
+    rank, world, local = dist_env()
+    if rank != 0:
+        return
+    harness = os.path.join(ROOT, "oracle", "_ref", "ref_harness")
+    cpu = cpu_baseline()
+    steps, warm = max(1, min(args.steps, 5)), max(1, min(args.warmup, 2))
+    out = {"impl": "reference", "metric": METRIC, "unit": UNIT, "n_gpus": 1, "steps": steps, "warmup": warm,
+           "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "data": "synthetic",
+           "dtype": "f16 operands, f32 accumulate",
+           "config": {"workload": WORKLOAD, "parallelism": "single GPU (the reference has no multi-GPU path)"}}
+    ran = False
+    if os.path.exists(harness):
+        env = dict(os.environ, CUDA_VISIBLE_DEVICES=os.environ.get("CUDA_VISIBLE_DEVICES", str(local)))
+        try:
+            r = subprocess.run([harness, "gemm_bench", str(M), str(N), str(K), str(steps), str(warm), "0"],
+                               capture_output=True, text=True, timeout=600, env=env)
+            j = json.loads(r.stdout.strip().splitlines()[-1])
+            r2 = subprocess.run([harness, "gemm_bench", str(M), str(N), str(K), "2", "1", "1"],
+                                capture_output=True, text=True, timeout=600, env=env)
+            j2 = json.loads(r2.stdout.strip().splitlines()[-1])
+            out.update({"value": j["tflops"], "ms_per_step": j["ms_per_step"],
+                        "e2e": {"value": j2["tflops"], "unit": UNIT, "h2d_bytes_per_step": 4 * (M * K + K * N),
+                                "d2h_bytes_per_step": 4 * M * N, "ms_per_step": j2["ms_per_step"]},
+                        "reference_device": "gpu (NeuZephyr WMMA kernel rebuilt for sm_100, via GEMMTensorCore)",
+                        "cpu_baseline": dict(cpu, kind="port")})
+            ran = True
+        except Exception as e:  # fall through to the CPU port
+            out["reference_gpu_error"] = repr(e)[:200]
+    if not ran:
+        out.update({"value": cpu["value"], "ms_per_step": FLOP / (cpu["value"] * 1e12) * 1e3,
+                    "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                    "cpu_baseline": cpu})
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

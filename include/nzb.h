@@ -125,6 +125,18 @@ NZB_API int nzb_gemm_backward(const float* A, const float* B, float* C, const in
                               size_t workspace_bytes, void* stream);
 
 /*
+ * The GEMM alone on operands that are already staged as fp16: A16 holds op(A) as
+ * [nA][M][ldk] and B16 holds op(B)^T as [nB][N][ldk] (both K-major, ldk >= K, ldk % 8 == 0,
+ * 16-byte aligned), e.g. written by nzb_cast_f32_f16 or kept as fp16 shadow copies of
+ * weights. This is the seam of GeneralMatrixMulTensorKernel itself (half operands in,
+ * fp32 out; src/OperationKernels.cu:821-844) with the crop/accumulate and bias/ReLU
+ * epilogue fused. lda/ldb/transA/transB of the descriptor are ignored; a zero batch stride
+ * of A or B still means "broadcast", any non-zero value means "densely packed matrices".
+ */
+NZB_API int nzb_gemm_f16(const nzb_gemm_desc* desc, const void* A16, const void* B16, int64_t ldk, float* C,
+                         const float* bias, void* stream);
+
+/*
  * fp32 -> fp16 (round to nearest even) copy of `rows` x `cols` with source leading
  * dimension ld_in into a dense fp16 matrix with leading dimension ld_out (columns
  * cols..ld_out-1 are zero filled): the Padding kernel (src/OperationKernels.cu:846-860)

@@ -213,6 +213,27 @@ int nzb_gemm(const nzb_gemm_desc* desc, const float* A, const float* B, float* C
     return run_gemm(desc, A, B, C, bias, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
+int nzb_gemm_f16(const nzb_gemm_desc* desc, const void* A16, const void* B16, int64_t ldk, float* C,
+                 const float* bias, void* stream) {
+    if (!desc) return fail(NZB_ERR_BAD_ARG, "descriptor is null");
+    nzb_gemm_desc d = *desc;
+    d.transA = 0; d.transB = 1; d.lda = d.K; d.ldb = d.K;  // layout fields are not used on this path
+    Plan pl;
+    int rc = make_plan(&d, &pl);
+    if (rc != NZB_OK) return rc;
+    if (d.M == 0 || d.N == 0) return NZB_OK;
+    if (!A16 || !B16 || !C) return fail(NZB_ERR_BAD_ARG, "A16, B16 and C must be non-null");
+    if (d.bias_mode != NZB_BIAS_NONE && !bias) return fail(NZB_ERR_BAD_ARG, "bias_mode set but bias is null");
+    if (ldk < d.K || ldk % 8 != 0) return fail(NZB_ERR_BAD_ARG, "ldk must be >= K and a multiple of 8");
+    if ((reinterpret_cast<uintptr_t>(A16) | reinterpret_cast<uintptr_t>(B16)) & 15) return fail(NZB_ERR_BAD_ARG, "fp16 operands must be 16-byte aligned");
+    pl.g.Kp = ldk;
+    pl.g.A16 = reinterpret_cast<const __half*>(A16);
+    pl.g.B16 = reinterpret_cast<const __half*>(B16);
+    pl.g.C = C;
+    pl.g.bias = bias;
+    return launch_gemm(pl.g, static_cast<cudaStream_t>(stream));
+}
+
 int nzb_tensorcore_gemm_workspace_bytes(const int64_t shapeA[4], const int64_t shapeB[4], const int64_t shapeC[4],
                                         size_t* bytes_out) {
     nzb_gemm_desc d;

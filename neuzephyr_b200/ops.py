@@ -64,6 +64,22 @@ def gemm(A, B, out=None, transA=False, transB=False, bias=None, bias_mode=C.BIAS
     return out
 
 
+def gemm_f16(A16, B16, M, N, K, out=None, bias=None, bias_mode=C.BIAS_NONE, relu=False, accumulate=False):
+    """GEMM on pre-staged K-major fp16 operands A16 [M][ldk], B16 [N][ldk] (nzb_gemm_f16)."""
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float32, device=A16.device)
+    d = C.GemmDesc()
+    d.M, d.N, d.K = M, N, K
+    d.ldc = N
+    d.batch[0] = d.batch[1] = 1
+    d.accumulate, d.relu = int(accumulate), int(relu)
+    d.bias_mode = bias_mode if bias is not None else C.BIAS_NONE
+    d.bias_ld = N
+    C.check(C.lib().nzb_gemm_f16(ctypes.byref(d), _ptr(A16), _ptr(B16), A16.shape[1], _ptr(out), _ptr(bias),
+                                 _stream()))
+    return out
+
+
 def _ws4(A, B, Cs):
     n = ctypes.c_size_t(0)
     C.check(C.lib().nzb_tensorcore_gemm_workspace_bytes(C.shape4(A.shape), C.shape4(B.shape), C.shape4(Cs),

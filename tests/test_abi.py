@@ -1,0 +1,69 @@
+"""CPU-side checks of the C-ABI boundary: the library loads and exports every symbol
+include/nzb.h declares; descriptor validation and workspace sizing need no GPU."""
+import ctypes
+import os
+import re
+
+from neuzephyr_b200 import _capi as C
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "nzb.h")).read()
+    return sorted(set(re.findall(r"NZB_API\s+[\w\s\*]+?\b(nzb_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    L = C.lib()
+    names = declared_symbols()
+    assert len(names) >= 10
+    for n in names:
+        assert hasattr(L, n), n
+    assert sorted(C.EXPORTS) == names
+
+
+def test_desc_layout_matches_header():
+    # 3+3 int64, 2 int32, 2 int32, 6 int64, 2 int32, int64, 2 int32
+    assert ctypes.sizeof(C.GemmDesc) == 48 + 8 + 8 + 48 + 8 + 8 + 8
+
+
+def test_workspace_sizing_and_validation():
+    L = C.lib()
+    d = C.GemmDesc()
+    d.M, d.N, d.K = 127, 129, 131
+    d.lda, d.ldb, d.ldc = 131, 129, 129
+    d.batch[0] = d.batch[1] = 1
+    n = ctypes.c_size_t(0)
+    assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.OK
+    kp = 192
+    assert n.value == (127 * kp * 2 + 255) // 256 * 256 + (129 * kp * 2 + 255) // 256 * 256
+    d.batch[0], d.batch[1] = 4, 3
+    d.strideA[0], d.strideA[1] = 3 * 127 * 131, 127 * 131
+    d.strideB[0], d.strideB[1] = 0, 131 * 129
+    assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.OK
+    assert n.value == (12 * 127 * kp * 2 + 255) // 256 * 256 + (3 * 129 * kp * 2 + 255) // 256 * 256
+    d.ldc = 5
+    assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.ERR_BAD_ARG
+    assert b"leading dimension" in L.nzb_last_error_string()
+    d.ldc = 129
+    d.batch[0] = 0
+    assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.ERR_BAD_ARG
+    assert L.nzb_gemm_workspace_bytes(None, ctypes.byref(n)) == C.ERR_BAD_ARG
+
+
+def test_shape_entry_points_validate_without_a_device():
+    L = C.lib()
+    n = ctypes.c_size_t(0)
+    sa, sb, sc = C.shape4((2, 1, 8, 16)), C.shape4((1, 3, 16, 4)), C.shape4((2, 3, 8, 4))
+    assert L.nzb_tensorcore_gemm_workspace_bytes(sa, sb, sc, ctypes.byref(n)) == C.OK
+    assert n.value == (2 * 8 * 64 * 2 + 255) // 256 * 256 + (3 * 4 * 64 * 2 + 255) // 256 * 256
+    bad = C.shape4((2, 3, 8, 5))
+    assert L.nzb_tensorcore_gemm_workspace_bytes(sa, sb, bad, ctypes.byref(n)) == C.ERR_BAD_ARG
+    incompatible = C.shape4((3, 1, 8, 16))
+    sb2 = C.shape4((2, 3, 16, 4))
+    assert L.nzb_tensorcore_gemm_workspace_bytes(incompatible, sb2, sc, ctypes.byref(n)) == C.ERR_BAD_ARG
+
+
+def test_version():
+    assert C.lib().nzb_version() >= 100
