@@ -25,67 +25,84 @@ FLOP = 2.0 * M * N * K
 WORKLOAD = "gemm 8192x8192x8192, fp32 row-major in/out, fp16 operands (RN), fp32 accumulate, uniform[-1,1]"
 METRIC = "gemm_tflops_8192"
 UNIT = "TFLOP/s"
-CPU_SAMPLE_ROWS = 256  # rows of C computed by the CPU baseline per step
+CPU_SAMPLE_ROWS = 4096  # rows of C computed by the CPU baseline per step
 
 
-def measured_peaks():
+# dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch at this size, from the ncu
+# capture summarised in profiles/gemm_f16_tcgen05_8192x8192x8192.md (algorithmic: 512 MB).
+NCU_DRAM_BYTES_PER_LAUNCH = 1.28e9
+
+
+def measured_peaks(sustained):
+    """Denominators measured on this pool's B200s (cuBLAS bf16 8192^3): the burst figure for
+    a kernel timed alone over a few launches, the sustained one for a loop long enough to
+    sit under the power cap."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as f:
             p = json.load(f)
-        return float(p["bf16_tflops"]), float(p["hbm_gbs"]), "measured"
+        key = "bf16_tflops_sustained" if sustained else "bf16_tflops"
+        return float(p[key]), "of measured (cuBLAS bf16 %s)" % ("sustained" if sustained else "burst")
     except Exception:
-        return 1590.0, 6650.0, "fallback"
+        return (1400.0 if sustained else 1590.0), "of fallback (%s)" % ("sustained" if sustained else "burst")
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-         "clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the throttle reasons through NVML (read-only queries) in a
+    background thread while the timed region runs."""
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.stop_flag, self.t = index, [], False, None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q, "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.t = threading.Thread(target=self._read, daemon=True)
-            self.t.start()
-        except Exception:
-            self.proc = None
+            import pynvml as nv
+            nv.nvmlInit()
+            # NVML enumerates physical devices; honour CUDA_VISIBLE_DEVICES when it lists indices
+            vis = os.environ.get("CUDA_VISIBLE_DEVICES", "")
+            idx = self.index
+            if vis and all(v.strip().isdigit() for v in vis.split(",")):
+                idx = int(vis.split(",")[self.index])
+            self.nv, self.h = nv, nv.nvmlDeviceGetHandleByIndex(idx)
+            self.max = nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM)
+        except Exception as e:
+            self.nv = None
+            self.err = repr(e)[:100]
+            return
+        self.t = threading.Thread(target=self._run, daemon=True)
+        self.t.start()
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
-
-    def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], None, set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+    def _run(self):
+        nv = self.nv
+        while not self.stop_flag:
             try:
-                sm.append(float(r[0]))
-                mx = float(r[1])
-                for nme, v in zip(names, r[3:7]):
-                    if v.lower().startswith("active"):
-                        reasons.add(nme)
+                clk = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                rs = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                pw = nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0
+                self.rows.append((clk, rs, pw))
             except Exception:
                 pass
-        sm.sort()
-        # under load = the upper half of the samples (idle samples bracket the timed region)
-        load = sm[len(sm) // 2:] if sm else []
-        med = load[len(load) // 2] if load else None
-        return {"sm_mhz": med, "sm_max_mhz": mx, "reasons": sorted(reasons), "samples": len(sm)}
+            time.sleep(0.002)
+
+    def mark(self):
+        """Index of the next sample: brackets the timed region."""
+        return len(self.rows)
+
+    def stop(self, lo=0, hi=None):
+        if getattr(self, "nv", None) is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvml unavailable: " + getattr(self, "err", "")]}
+        self.stop_flag = True
+        self.t.join(timeout=1)
+        nv = self.nv
+        rows = self.rows[lo:hi] or self.rows[-1:]
+        names = {"hw_slowdown": nv.nvmlClocksEventReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksEventReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksEventReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksEventReasonSwPowerCap}
+        reasons = sorted(k for k, bit in names.items() if any(r[1] & bit for r in rows))
+        clks = sorted(r[0] for r in rows)
+        return {"sm_mhz": clks[len(clks) // 2] if clks else None, "sm_max_mhz": self.max, "reasons": reasons,
+                "samples": len(rows), "power_w_max": max(r[2] for r in rows) if rows else None}
 
 
 def dist_env():
@@ -150,17 +167,18 @@ def run_ours(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-        time.sleep(0.25)
     # ---- device-resident timing: `value` -------------------------------------------------
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
+    lo = sampler.mark()
     e0.record(stream)
     for _ in range(args.steps):
         step()
     e1.record(stream)
     barrier()
+    hi = sampler.mark()
     ms = e0.elapsed_time(e1) / args.steps
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop(lo, hi) if rank == 0 else None
     if nz.device_status() != 0:
         raise SystemExit("device-side wait expired (status %d)" % nz.device_status())
 
@@ -207,15 +225,9 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, kms, e2e_ms = [float(x) for x in t.tolist()]
     if rank == 0:
-        peak_tf, peak_hbm, how = measured_peaks()
+        peak_tf, how = measured_peaks(sustained=args.steps * kms > 100.0)
         achieved = FLOP / (kms * 1e-3) / 1e12
-        traffic = None
-        tpath = os.path.join(ROOT, "profiles", "gemm_8192_traffic.json")
-        if os.path.exists(tpath):
-            try:
-                traffic = json.load(open(tpath)).get("dram_bytes_per_launch")
-            except Exception:
-                traffic = None
+        traffic = NCU_DRAM_BYTES_PER_LAUNCH
         out = {
             "metric": METRIC, "value": world * FLOP / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
@@ -229,7 +241,7 @@ def run_ours(args):
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                          "frac": achieved / peak_tf, "traffic": traffic, "kernel": "gemm_f16_tcgen05_kernel",
-                         "kernel_ms": kms, "peak_source": "of %s (cuBLAS bf16 burst)" % how,
+                         "kernel_ms": kms, "peak_source": how, "algorithmic_bytes": 2.0 * (M * K + K * N) + 4.0 * M * N,
                          "frac_of_nominal_2250": achieved / 2250.0},
             "clocks": clocks,
         }
@@ -283,7 +295,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
