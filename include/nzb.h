@@ -125,6 +125,28 @@ NZB_API int nzb_gemm_backward(const float* A, const float* B, float* C, const in
                               size_t workspace_bytes, void* stream);
 
 /*
+ * nzb_gemm for callers that cannot allocate device memory: a plug-in inside a server or
+ * framework that reserved the whole GPU for its own pool, or a steady-state loop where an
+ * allocation call (and the device synchronisation it may imply) is not allowed. Same
+ * descriptor, operands, results and status codes as nzb_gemm, but the fp16 staging scratch
+ * is a fixed array of NZB_STATIC_SCRATCH_BYTES inside the library image, so the call makes
+ * no cudaMalloc / cudaFree / host-allocation call at all. It has no counterpart in
+ * NeuZephyr (whose drivers allocate three temporaries per call,
+ * src/OperationKernels.cu:930-932); it exists for embedding.
+ *   - Every GPU on which the library is loaded holds the array until the process exits.
+ *   - Descriptors whose staged operands (nzb_gemm_workspace_bytes) exceed it return
+ *     NZB_ERR_WORKSPACE with an explanatory nzb_last_error_string().
+ *   - The first call on each device looks up the array's device address (with that
+ *     device current); make that first call before starting any stream capture.
+ *   - All calls share the array, which keeps the last call's contents. Nothing needs
+ *     clearing (the staging kernels rewrite all bytes the GEMM reads), but calls that
+ *     overlap on the GPU race on it: keep them ordered on one stream or with events.
+ */
+#define NZB_STATIC_SCRATCH_BYTES ((size_t)32 << 20)
+NZB_API int nzb_gemm_static(const nzb_gemm_desc* desc, const float* A, const float* B, float* C, const float* bias,
+                            void* stream);
+
+/*
  * The GEMM alone on operands that are already staged as fp16: A16 holds op(A) as
  * [nA][M][ldk] and B16 holds op(B)^T as [nB][N][ldk] (both K-major, ldk >= K, ldk % 8 == 0,
  * 16-byte aligned), e.g. written by nzb_cast_f32_f16 or kept as fp16 shadow copies of

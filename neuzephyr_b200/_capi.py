@@ -8,10 +8,11 @@ LIB_PATH = os.path.join(HERE, "libnzb.so")
 
 OK, ERR_BAD_ARG, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_CUDA, ERR_DEVICE_TIMEOUT, ERR_NO_DEVICE = range(7)
 BIAS_NONE, BIAS_ROW, BIAS_COL, BIAS_MATRIX = range(4)
+STATIC_SCRATCH_BYTES = 32 << 20
 
 EXPORTS = [
     "nzb_version", "nzb_last_error_string", "nzb_device_status", "nzb_device_status_reset",
-    "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_gemm_f16", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
+    "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_gemm_f16", "nzb_gemm_static", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
     "nzb_gemm_backward", "nzb_cast_f32_f16",
 ]
 
@@ -51,6 +52,7 @@ def lib():
         vp, sz = ctypes.c_void_p, ctypes.c_size_t
         L.nzb_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc), ctypes.POINTER(sz)]
         L.nzb_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, sz, vp]
+        L.nzb_gemm_static.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp]
         L.nzb_gemm_f16.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, ctypes.c_int64, vp, vp, vp]
         L.nzb_tensorcore_gemm_workspace_bytes.argtypes = [i64p, i64p, i64p, ctypes.POINTER(sz)]
         L.nzb_tensorcore_gemm.argtypes = [vp, vp, vp, i64p, i64p, i64p, vp, sz, vp]

@@ -63,15 +63,7 @@ int get_encode_tiled(EncodeTiledFn* out) {
     return NZB_OK;
 }
 
-// Resolved view of a descriptor.
-struct Plan {
-    int64_t M, N, K, Kp;
-    int64_t nA0, nA1, nB0, nB1;  // matrices in the fp16 copies along each batch dimension
-    size_t a_bytes, b_bytes;
-    GemmLaunch g;
-};
-
-static int make_plan(const nzb_gemm_desc* d, Plan* pl) {
+int make_plan(const nzb_gemm_desc* d, Plan* pl) {
     if (!d) return fail(NZB_ERR_BAD_ARG, "descriptor is null");
     if (d->M < 0 || d->N < 0 || d->K < 0) return fail(NZB_ERR_BAD_ARG, "negative extent");
     if (d->batch[0] < 1 || d->batch[1] < 1) return fail(NZB_ERR_BAD_ARG, "batch extents must be >= 1");

@@ -94,13 +94,20 @@ int launch_cast(const float* in, __half* out, int64_t rows, int64_t cols, int64_
     DeviceState* ds;
     int rc = get_device_state(&ds);
     if (rc != NZB_OK) return rc;
+    return launch_cast_on(ds->sm_count, in, out, rows, cols, ld_in, ld_out, transpose, nmat0, nmat1, in_stride0,
+                          in_stride1, stream);
+}
+
+int launch_cast_on(int sm_count, const float* in, __half* out, int64_t rows, int64_t cols, int64_t ld_in,
+                   int64_t ld_out, int transpose, int64_t nmat0, int64_t nmat1, int64_t in_stride0,
+                   int64_t in_stride1, cudaStream_t stream) {
     if (rows <= 0 || nmat0 <= 0 || nmat1 <= 0) return NZB_OK;
     if (ld_out % 64 != 0 || ld_out < cols) return fail(NZB_ERR_BAD_ARG, "fp16 leading dimension must be a multiple of 64 and >= cols");
     CastParams p{in, out, rows, cols, ld_in, ld_out, nmat1, in_stride0, in_stride1, nmat0 * nmat1};
     if (!transpose) {
         const int64_t total = p.nmat * rows * (ld_out >> 3);
         int64_t blocks = (total + 255) / 256;
-        const int64_t cap = (int64_t)ds->sm_count * 16;
+        const int64_t cap = (int64_t)sm_count * 16;
         if (blocks > cap) blocks = cap;
         const bool vec = (ld_in % 4 == 0) && (in_stride0 % 4 == 0) && (in_stride1 % 4 == 0) &&
                          ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
@@ -109,7 +116,7 @@ int launch_cast(const float* in, __half* out, int64_t rows, int64_t cols, int64_
     } else {
         const int64_t total = p.nmat * ((rows + 63) >> 6) * (ld_out >> 6);
         int64_t blocks = total;
-        const int64_t cap = (int64_t)ds->sm_count * 16;
+        const int64_t cap = (int64_t)sm_count * 16;
         if (blocks > cap) blocks = cap;
         cast_transpose_kernel<<<(unsigned)blocks, 256, 0, stream>>>(p);
     }

@@ -347,6 +347,11 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
     DeviceState* ds;
     int rc = get_device_state(&ds);
     if (rc != NZB_OK) return rc;
+    return launch_gemm_on(g, *ds, stream);
+}
+
+int launch_gemm_on(const GemmLaunch& g, const DeviceState& dstate, cudaStream_t stream) {
+    const DeviceState* ds = &dstate;
     if (g.M <= 0 || g.N <= 0) return NZB_OK;
     if (g.K <= 0) return fail(NZB_ERR_UNSUPPORTED, "K = 0 is not supported");
     if (g.M > INT32_MAX - 256 || g.N > INT32_MAX - 256 || g.K > INT32_MAX - 256 || g.nA > INT32_MAX ||

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stddef.h>
+#include <cuda_fp16.h>
 
 #include "../../include/nzb.h"
 
@@ -66,5 +67,20 @@ struct GemmLaunch {
     int32_t accumulate, relu;
 };
 int launch_gemm(const GemmLaunch& g, cudaStream_t stream);
+// Same launches with the device facts supplied by the caller instead of looked up
+// (ds needs sm_count and status_dev only).
+int launch_gemm_on(const GemmLaunch& g, const DeviceState& ds, cudaStream_t stream);
+int launch_cast_on(int sm_count, const float* in, __half* out, int64_t rows, int64_t cols, int64_t ld_in,
+                   int64_t ld_out, int transpose, int64_t nmat0, int64_t nmat1, int64_t in_stride0,
+                   int64_t in_stride1, cudaStream_t stream);
+
+// Resolved view of a descriptor (nzb_api.cu).
+struct Plan {
+    int64_t M, N, K, Kp;
+    int64_t nA0, nA1, nB0, nB1;  // matrices in the fp16 copies along each batch dimension
+    size_t a_bytes, b_bytes;
+    GemmLaunch g;
+};
+int make_plan(const nzb_gemm_desc* d, Plan* pl);
 
 }  // namespace nzb
