@@ -240,7 +240,7 @@ def run_ours(args):
                     "ms_per_step": e2e_ms, "steps": e2e_steps},
             "gpu_launches": 3 * args.steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
-                         "frac": achieved / peak_tf, "traffic": traffic, "kernel": "gemm_f16_tcgen05_kernel",
+                         "frac": achieved / peak_tf, "traffic": traffic, "kernel": "gemm_f16_tcgen05_pair_kernel",
                          "kernel_ms": kms, "peak_source": how, "algorithmic_bytes": 2.0 * (M * K + K * N) + 4.0 * M * N,
                          "frac_of_nominal_2250": achieved / 2250.0},
             "clocks": clocks,

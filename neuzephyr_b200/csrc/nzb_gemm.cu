@@ -34,6 +34,7 @@ struct GemmParams {
     int32_t k_blocks;     // ceil(K / 64)
     int32_t last_ksteps;  // 16-wide MMA steps in the last k block (1..4)
     int32_t vec4;         // C (and bias) allow aligned float4 access
+    int32_t group_m;      // m-tiles per rasterisation group
     int64_t total_tiles;
     int* status;
 };
@@ -54,7 +55,6 @@ struct GemmCfg {
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 };
 
-constexpr int kGroupM = 16;  // m-tiles per rasterisation group (keeps a wave's operands in L2)
 
 struct TileCoord {
     int32_t mt, nt, b0, b1;
@@ -64,10 +64,10 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int64_t ti
     const int64_t per_batch = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int64_t ob = tile / per_batch;
     const int32_t rem = static_cast<int32_t>(tile - ob * per_batch);
-    const int32_t group_size = kGroupM * p.tiles_n;
+    const int32_t group_size = p.group_m * p.tiles_n;
     const int32_t g = rem / group_size;
-    const int32_t first_m = g * kGroupM;
-    const int32_t gm = min(p.tiles_m - first_m, kGroupM);
+    const int32_t first_m = g * p.group_m;
+    const int32_t gm = min(p.tiles_m - first_m, p.group_m);
     const int32_t within = rem - g * group_size;
     TileCoord t;
     t.mt = first_m + within % gm;
@@ -75,6 +75,97 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int64_t ti
     t.b0 = static_cast<int32_t>(ob / p.out_e1);
     t.b1 = static_cast<int32_t>(ob % p.out_e1);
     return t;
+}
+
+// Drains one finished accumulator quarter (32 tensor-memory lanes x BN columns, owned by
+// this warp) through the warp's shared staging buffer into coalesced global stores, applying
+// accumulate / bias / ReLU. tmem_acc addresses lane quarter and first column.
+template <class Cfg>
+__device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t tmem_acc, float* stage, int lane,
+                                                  float* Cb, int32_t row0, int32_t col_tile) {
+    using namespace ptx;
+    constexpr int BN = Cfg::BN;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += Cfg::CHUNK) {
+        const uint32_t taddr = tmem_acc + c0;
+        if constexpr (Cfg::CHUNK == 32) {
+            uint32_t v[32];
+            tmem_ld_32x32(taddr, v);
+            tmem_ld_wait();
+            float4* dst = reinterpret_cast<float4*>(stage + lane * Cfg::EPI_STRIDE);
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                     __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        } else {
+            uint32_t v[16];
+            tmem_ld_32x16(taddr, v);
+            tmem_ld_wait();
+            float4* dst = reinterpret_cast<float4*>(stage + lane * Cfg::EPI_STRIDE);
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                                     __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        }
+        __syncwarp();
+        const int32_t gc0 = col_tile + c0;
+        if (p.vec4) {
+            constexpr int LPR = Cfg::CHUNK / 4;  // lanes per staged row
+            constexpr int RPI = 32 / LPR;        // rows per iteration
+            const int cl = (lane % LPR) * 4;
+            const int32_t gc = gc0 + cl;
+#pragma unroll
+            for (int rr = 0; rr < 32; rr += RPI) {
+                const int r = rr + lane / LPR;
+                const int32_t gr = row0 + r;
+                if (gr < p.M && gc < p.N) {  // N % 4 == 0 on this path: the whole float4 is in range
+                    float4 x = *reinterpret_cast<const float4*>(stage + r * Cfg::EPI_STRIDE + cl);
+                    float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
+                    if (p.accumulate) {
+                        const float4 o = *reinterpret_cast<const float4*>(cp);
+                        x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
+                    }
+                    if (p.bias_mode == NZB_BIAS_ROW) {
+                        const float4 b = *reinterpret_cast<const float4*>(p.bias + gc);
+                        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                    } else if (p.bias_mode == NZB_BIAS_COL) {
+                        const float b = p.bias[gr];
+                        x.x += b; x.y += b; x.z += b; x.w += b;
+                    } else if (p.bias_mode == NZB_BIAS_MATRIX) {
+                        const float4 b = *reinterpret_cast<const float4*>(
+                            p.bias + static_cast<int64_t>(gr) * p.bias_ld + gc);
+                        x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
+                    }
+                    if (p.relu) {
+                        x.x = fmaxf(x.x, 0.f); x.y = fmaxf(x.y, 0.f);
+                        x.z = fmaxf(x.z, 0.f); x.w = fmaxf(x.w, 0.f);
+                    }
+                    *reinterpret_cast<float4*>(cp) = x;
+                }
+            }
+        } else {
+            constexpr int RPI = 32 / Cfg::CHUNK;  // 1, or 2 when the chunk is 16 wide
+            const int cl = lane % Cfg::CHUNK;
+            const int32_t gc = gc0 + cl;
+#pragma unroll 4
+            for (int rr = 0; rr < 32; rr += RPI) {
+                const int r = rr + lane / Cfg::CHUNK;
+                const int32_t gr = row0 + r;
+                if (gr < p.M && gc < p.N) {
+                    float x = stage[r * Cfg::EPI_STRIDE + cl];
+                    float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
+                    if (p.accumulate) x += *cp;
+                    if (p.bias_mode == NZB_BIAS_ROW) x += p.bias[gc];
+                    else if (p.bias_mode == NZB_BIAS_COL) x += p.bias[gr];
+                    else if (p.bias_mode == NZB_BIAS_MATRIX)
+                        x += p.bias[static_cast<int64_t>(gr) * p.bias_ld + gc];
+                    if (p.relu) x = fmaxf(x, 0.f);
+                    *cp = x;
+                }
+            }
+        }
+        __syncwarp();
+    }
 }
 
 template <class Cfg>
@@ -123,73 +214,78 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
     const int32_t k_iters = p.red_e0 * p.red_e1 * p.k_blocks;  // per tile
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---------------- TMA producer ----------------
-            uint32_t it = 0;
-            bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-                const TileCoord t = decode_tile(p, tile);
-                for (int32_t r0 = 0; r0 < p.red_e0 && ok; r0++) {
-                    for (int32_t r1 = 0; r1 < p.red_e1 && ok; r1++) {
-                        const int32_t i0 = t.b0 + r0, i1 = t.b1 + r1;
-                        const int32_t za = i0 * p.a_mul0 + i1 * p.a_mul1;
-                        const int32_t zb = i0 * p.b_mul0 + i1 * p.b_mul1;
-                        for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
-                            const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                            if (!mbar_wait_bounded(&empty[s], ph ^ 1, abort_flag)) {
-                                ok = false;
-                                break;
-                            }
+        // ---------------- TMA producer (whole warp waits, one elected lane issues) ----------------
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            const TileCoord t = decode_tile(p, tile);
+            for (int32_t r0 = 0; r0 < p.red_e0 && ok; r0++) {
+                for (int32_t r1 = 0; r1 < p.red_e1 && ok; r1++) {
+                    const int32_t i0 = t.b0 + r0, i1 = t.b1 + r1;
+                    const int32_t za = i0 * p.a_mul0 + i1 * p.a_mul1;
+                    const int32_t zb = i0 * p.b_mul0 + i1 * p.b_mul1;
+                    for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                        if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        if (elect_one()) {
                             uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
                             mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
                             tma_load_3d(sa, &tmA, kb * 64, t.mt * 128, za, &full[s]);
                             tma_load_3d(sa + Cfg::A_BYTES, &tmB, kb * 64, t.nt * BN, zb, &full[s]);
                         }
-                    }
-                }
-            }
-            if (!ok) {
-                // Wait (bounded) for the copies still in flight so none lands after exit.
-                const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
-                for (uint32_t j = first; j < it; j++) {
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1)) {
-                        if (clock64() - t0 > kWaitCycleLimit) break;
+                        __syncwarp();
                     }
                 }
             }
         }
+        if (!ok && lane == 0) {
+            // Wait (bounded) for the copies still in flight so none lands after exit.
+            const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
+            for (uint32_t j = first; j < it; j++) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1)) {
+                    if (clock64() - t0 > kWaitCycleLimit) break;
+                }
+            }
+        }
     } else if (warp == 1) {
-        if (lane == 0) {
-            // ---------------- MMA issuer ----------------
-            constexpr uint32_t idesc = make_idesc_f16_f32(128, BN);
-            uint32_t it = 0, tcount = 0;
-            bool ok = true;
-            for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, tcount++) {
-                const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
-                if (!mbar_wait_bounded(&tempty[acc], aph ^ 1, abort_flag)) break;
+        // ---------------- MMA issuer (whole warp runs the loop, one elected lane issues) ----------------
+        constexpr uint32_t idesc = make_idesc_f16_f32(128, BN);
+        uint32_t it = 0, tcount = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, tcount++) {
+            const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+            if (!mbar_wait_warp(&tempty[acc], aph ^ 1, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            int32_t kb = 0;
+            for (int32_t kk = 0; kk < k_iters; kk++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+                    ok = false;
+                    break;
+                }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int32_t kk = 0; kk < k_iters; kk++, it++) {
-                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                    if (!mbar_wait_bounded(&full[s], ph, abort_flag)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    const uint64_t da = make_sw128_kmajor_desc(sa);
-                    const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
-                    const int32_t kb = kk % p.k_blocks;
-                    const int32_t ksteps = (kb == p.k_blocks - 1) ? p.last_ksteps : 4;
-                    for (int32_t j = 0; j < ksteps; j++) {
-                        // one k step = 16 halves = 32 bytes = 2 descriptor address units
-                        mma_f16_ss(d_tmem, da + 2 * j, db + 2 * j, idesc, (kk > 0 || j > 0) ? 1u : 0u);
-                    }
+                const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                const uint64_t da = make_sw128_kmajor_desc(sa);
+                const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                const int32_t ksteps = (kb == p.k_blocks - 1) ? p.last_ksteps : 4;
+                if (++kb == p.k_blocks) kb = 0;
+                if (elect_one()) {
+                    // one k step = 16 halves = 32 bytes = 2 descriptor address units
+                    mma_f16_ss(d_tmem, da, db, idesc, kk > 0 ? 1u : 0u);
+                    if (ksteps > 1) mma_f16_ss(d_tmem, da + 2, db + 2, idesc, 1u);
+                    if (ksteps > 2) mma_f16_ss(d_tmem, da + 4, db + 4, idesc, 1u);
+                    if (ksteps > 3) mma_f16_ss(d_tmem, da + 6, db + 6, idesc, 1u);
                     mma_commit(&empty[s]);
                 }
-                if (ok) mma_commit(&tfull[acc]);
+                __syncwarp();
             }
+            if (ok && elect_one()) mma_commit(&tfull[acc]);
+            __syncwarp();
         }
     } else {
         // ---------------- epilogue warps ----------------
@@ -204,87 +300,8 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             float* Cb = p.C + t.b0 * p.c_stride0 + t.b1 * p.c_stride1;
             const int32_t row0 = t.mt * 128 + q * 32;
             const int32_t col_tile = t.nt * BN;
-#pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += Cfg::CHUNK) {
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c0;
-                if constexpr (Cfg::CHUNK == 32) {
-                    uint32_t v[32];
-                    tmem_ld_32x32(taddr, v);
-                    tmem_ld_wait();
-                    float4* dst = reinterpret_cast<float4*>(stage + lane * Cfg::EPI_STRIDE);
-#pragma unroll
-                    for (int j = 0; j < 8; j++)
-                        dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                             __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                } else {
-                    uint32_t v[16];
-                    tmem_ld_32x16(taddr, v);
-                    tmem_ld_wait();
-                    float4* dst = reinterpret_cast<float4*>(stage + lane * Cfg::EPI_STRIDE);
-#pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        dst[j] = make_float4(__uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
-                                             __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
-                }
-                __syncwarp();
-                const int32_t gc0 = col_tile + c0;
-                if (p.vec4) {
-                    constexpr int LPR = Cfg::CHUNK / 4;  // lanes per staged row
-                    constexpr int RPI = 32 / LPR;        // rows per iteration
-                    const int cl = (lane % LPR) * 4;
-                    const int32_t gc = gc0 + cl;
-#pragma unroll
-                    for (int rr = 0; rr < 32; rr += RPI) {
-                        const int r = rr + lane / LPR;
-                        const int32_t gr = row0 + r;
-                        if (gr < p.M && gc < p.N) {  // N % 4 == 0 on this path: the whole float4 is in range
-                            float4 x = *reinterpret_cast<const float4*>(stage + r * Cfg::EPI_STRIDE + cl);
-                            float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
-                            if (p.accumulate) {
-                                const float4 o = *reinterpret_cast<const float4*>(cp);
-                                x.x += o.x; x.y += o.y; x.z += o.z; x.w += o.w;
-                            }
-                            if (p.bias_mode == NZB_BIAS_ROW) {
-                                const float4 b = *reinterpret_cast<const float4*>(p.bias + gc);
-                                x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
-                            } else if (p.bias_mode == NZB_BIAS_COL) {
-                                const float b = p.bias[gr];
-                                x.x += b; x.y += b; x.z += b; x.w += b;
-                            } else if (p.bias_mode == NZB_BIAS_MATRIX) {
-                                const float4 b = *reinterpret_cast<const float4*>(
-                                    p.bias + static_cast<int64_t>(gr) * p.bias_ld + gc);
-                                x.x += b.x; x.y += b.y; x.z += b.z; x.w += b.w;
-                            }
-                            if (p.relu) {
-                                x.x = fmaxf(x.x, 0.f); x.y = fmaxf(x.y, 0.f);
-                                x.z = fmaxf(x.z, 0.f); x.w = fmaxf(x.w, 0.f);
-                            }
-                            *reinterpret_cast<float4*>(cp) = x;
-                        }
-                    }
-                } else {
-                    constexpr int RPI = 32 / Cfg::CHUNK;  // 1, or 2 when the chunk is 16 wide
-                    const int cl = lane % Cfg::CHUNK;
-                    const int32_t gc = gc0 + cl;
-#pragma unroll 4
-                    for (int rr = 0; rr < 32; rr += RPI) {
-                        const int r = rr + lane / Cfg::CHUNK;
-                        const int32_t gr = row0 + r;
-                        if (gr < p.M && gc < p.N) {
-                            float x = stage[r * Cfg::EPI_STRIDE + cl];
-                            float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
-                            if (p.accumulate) x += *cp;
-                            if (p.bias_mode == NZB_BIAS_ROW) x += p.bias[gc];
-                            else if (p.bias_mode == NZB_BIAS_COL) x += p.bias[gr];
-                            else if (p.bias_mode == NZB_BIAS_MATRIX)
-                                x += p.bias[static_cast<int64_t>(gr) * p.bias_ld + gc];
-                            if (p.relu) x = fmaxf(x, 0.f);
-                            *cp = x;
-                        }
-                    }
-                }
-                __syncwarp();
-            }
+            drain_accumulator<Cfg>(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, stage, lane, Cb,
+                                   row0, col_tile);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -300,6 +317,188 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         __syncwarp();
         tc_fence_after();
         tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant (cluster of 2, tcgen05 cta_group::2): one 256 x 256 output tile per
+// pair and k block. Each CTA loads its own 128 rows of A and its own 128 rows of B
+// (half of the tile's N) -- 32 KB per k block instead of 48 KB for the single-CTA
+// 128 x 256 tile -- and the leader's single MMA thread drives both tensor cores, each
+// accumulating its 128 rows x 256 columns in its own tensor memory. Loads are plain
+// per-CTA TMA copies; only barrier arrivals cross between the CTAs.
+// ---------------------------------------------------------------------------
+struct PairCfg {
+    static constexpr int BN = 256, STAGES = 6;
+    static constexpr int A_BYTES = 128 * 64 * 2;
+    static constexpr int B_BYTES = 128 * 64 * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int EPI_STRIDE = 36;
+    static constexpr int EPI_BYTES = 4 * 32 * EPI_STRIDE * 4;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int CHUNK = 32;
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                             const GemmParams p) {
+    using namespace ptx;
+    using Cfg = PairCfg;
+    constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* epi = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
+    uint64_t* full = bars;                     // [STAGES] leader's copy counts both CTAs' TMA bytes
+    uint64_t* empty = bars + STAGES;           // [STAGES] per CTA, signalled by the leader's commits
+    uint64_t* tfull = bars + 2 * STAGES;       // [2] per CTA, signalled by the leader's commits
+    uint64_t* tempty = bars + 2 * STAGES + 2;  // [2] leader's copy: 8 epilogue warps arrive
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();  // 0 = leader
+    const int64_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 8);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();  // both CTAs' barriers are initialised before anything crosses over
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int32_t k_iters = p.red_e0 * p.red_e1 * p.k_blocks;  // per tile
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs; whole warp waits, one elected lane issues) ----------------
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t tile = pair; tile < p.total_tiles && ok; tile += npairs) {
+            const TileCoord t = decode_tile(p, tile);
+            const int32_t row_a = t.mt * 256 + (int32_t)rank * 128;
+            const int32_t row_b = t.nt * 256 + (int32_t)rank * 128;
+            for (int32_t r0 = 0; r0 < p.red_e0 && ok; r0++) {
+                for (int32_t r1 = 0; r1 < p.red_e1 && ok; r1++) {
+                    const int32_t i0 = t.b0 + r0, i1 = t.b1 + r1;
+                    const int32_t za = i0 * p.a_mul0 + i1 * p.a_mul1;
+                    const int32_t zb = i0 * p.b_mul0 + i1 * p.b_mul1;
+                    for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                        if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                            ok = false;
+                            break;
+                        }
+                        if (elect_one()) {
+                            uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
+                            const uint32_t leader_full = map_to_cta(smem_u32(&full[s]), 0);
+                            if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
+                            tma_load_3d_pair(sa, &tmA, kb * 64, row_a, za, leader_full);
+                            tma_load_3d_pair(sa + Cfg::A_BYTES, &tmB, kb * 64, row_b, zb, leader_full);
+                        }
+                        __syncwarp();
+                    }
+                }
+            }
+        }
+        if (!ok && rank == 0 && lane == 0) {
+            // Wait (bounded) for the copies still in flight so none lands after exit.
+            const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
+            for (uint32_t j = first; j < it; j++) {
+                const long long t0 = clock64();
+                while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1)) {
+                    if (clock64() - t0 > kWaitCycleLimit) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (rank == 0) {
+            // ---------------- MMA issuer (leader only; whole warp runs the loop) ----------------
+            constexpr uint32_t idesc = make_idesc_f16_f32(256, BN);
+            uint32_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int64_t tile = pair; tile < p.total_tiles && ok; tile += npairs, tcount++) {
+                const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+                if (!mbar_wait_warp(&tempty[acc], aph ^ 1, abort_flag)) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                int32_t kb = 0;
+                for (int32_t kk = 0; kk < k_iters; kk++, it++) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                    const uint64_t da = make_sw128_kmajor_desc(sa);
+                    const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                    const int32_t ksteps = (kb == p.k_blocks - 1) ? p.last_ksteps : 4;
+                    if (++kb == p.k_blocks) kb = 0;
+                    if (elect_one()) {
+                        mma_f16_ss_pair(d_tmem, da, db, idesc, kk > 0 ? 1u : 0u);
+                        if (ksteps > 1) mma_f16_ss_pair(d_tmem, da + 2, db + 2, idesc, 1u);
+                        if (ksteps > 2) mma_f16_ss_pair(d_tmem, da + 4, db + 4, idesc, 1u);
+                        if (ksteps > 3) mma_f16_ss_pair(d_tmem, da + 6, db + 6, idesc, 1u);
+                        mma_commit_pair(&empty[s]);
+                    }
+                    __syncwarp();
+                }
+                if (ok && elect_one()) mma_commit_pair(&tfull[acc]);
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------- epilogue warps (both CTAs) ----------------
+        const int q = warp & 3;
+        float* stage = epi + (warp - 2) * 32 * Cfg::EPI_STRIDE;
+        uint32_t tcount = 0;
+        for (int64_t tile = pair; tile < p.total_tiles; tile += npairs, tcount++) {
+            const TileCoord t = decode_tile(p, tile);
+            const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+            if (!mbar_wait_bounded(&tfull[acc], aph, abort_flag)) break;
+            tc_fence_after();
+            float* Cb = p.C + t.b0 * p.c_stride0 + t.b1 * p.c_stride1;
+            const int32_t row0 = t.mt * 256 + (int32_t)rank * 128 + q * 32;
+            const int32_t col_tile = t.nt * BN;
+            drain_accumulator<Cfg>(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, stage, lane, Cb,
+                                   row0, col_tile);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty[acc]), 0));
+        }
+    }
+
+    __syncwarp();
+    tc_fence_before();
+    cluster_sync_all();  // neither CTA leaves while its pair may still touch its shared memory
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = NZB_ERR_DEVICE_TIMEOUT;
+        __threadfence_system();
+    }
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, Cfg::TMEM_COLS);
     }
 }
 
@@ -343,6 +542,31 @@ static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds,
     return NZB_OK;
 }
 
+
+static int launch_pair(const GemmLaunch& g, GemmParams& p, const DeviceState& ds, cudaStream_t stream) {
+    CUtensorMap tmA, tmB;
+    int rc = make_operand_map(&tmA, g.A16, g.K, g.Kp, g.M, g.nA, 128);
+    if (rc != NZB_OK) return rc;
+    rc = make_operand_map(&tmB, g.B16, g.K, g.Kp, g.N, g.nB, 128);
+    if (rc != NZB_OK) return rc;
+    p.tiles_m = (int32_t)((g.M + 255) / 256);
+    p.tiles_n = (int32_t)((g.N + 255) / 256);
+    p.group_m = 8;
+    p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * p.out_e0 * p.out_e1;
+    static bool attr_set = false;
+    if (!attr_set) {
+        NZB_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          PairCfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    int64_t pairs = ds.sm_count / 2;
+    if (p.total_tiles < pairs) pairs = p.total_tiles;
+    gemm_f16_tcgen05_pair_kernel<<<(unsigned)(2 * pairs), 192, PairCfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    NZB_CUDA_TRY(cudaGetLastError());
+    return NZB_OK;
+}
+
+
 int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
     DeviceState* ds;
     int rc = get_device_state(&ds);
@@ -383,6 +607,9 @@ int launch_gemm_on(const GemmLaunch& g, const DeviceState& dstate, cudaStream_t 
     if (p.bias_mode == NZB_BIAS_MATRIX)
         v4 = v4 && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0) && (g.bias_ld % 4 == 0);
     p.vec4 = v4 ? 1 : 0;
+    p.group_m = 16;
+
+    if (g.N > 128 && g.M > 128 && !g.force_single_cta) return launch_pair(g, p, *ds, stream);
 
     if (g.N > 128) return launch_cfg<GemmCfg<256, 4>>(g, p, *ds, stream);
     if (g.N > 64) return launch_cfg<GemmCfg<128, 6>>(g, p, *ds, stream);

@@ -65,6 +65,7 @@ struct GemmLaunch {
     int32_t bias_mode;
     int64_t bias_ld;
     int32_t accumulate, relu;
+    int32_t force_single_cta;  // keep the 128 x BN single-CTA kernel even where the CTA-pair kernel applies
 };
 int launch_gemm(const GemmLaunch& g, cudaStream_t stream);
 // Same launches with the device facts supplied by the caller instead of looked up
