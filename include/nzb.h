@@ -167,6 +167,84 @@ NZB_API int nzb_gemm_f16(const nzb_gemm_desc* desc, const void* A16, const void*
 NZB_API int nzb_cast_f32_f16(const float* in, void* out_f16, int64_t rows, int64_t cols, int64_t ld_in,
                              int64_t ld_out, int transpose, void* stream);
 
+/* Node operations around the contraction ---------------------------------------------- */
+
+/*
+ * nz::data::iImg2col / iImg2colBackward (include/NeuZephyr/TensorOperations.cuh:1108-1114,
+ * src/TensorOperations.cu:135-149; img2colKernel / img2colBackwardKernel,
+ * src/OperationKernels.cu:1308-1362). out is {batch, 1, H_out*W_out, C*K_h*K_w}; the backward
+ * ADDS the scattered column gradient to dx (gather form, no atomics).
+ */
+NZB_API int nzb_img2col(float* out, const float* in, int64_t H_out, int64_t W_out, int64_t C, int64_t K_h,
+                        int64_t K_w, int64_t stride, int64_t pad, int64_t H_in, int64_t W_in, int64_t batch,
+                        void* stream);
+NZB_API int nzb_img2col_backward(float* dx, const float* dcol, int64_t H_out, int64_t W_out, int64_t C, int64_t K_h,
+                                 int64_t K_w, int64_t stride, int64_t pad, int64_t H_in, int64_t W_in, int64_t batch,
+                                 void* stream);
+
+/*
+ * nz::data::iCol2img / iCol2imgBackward (include/NeuZephyr/TensorOperations.cuh:1132-1146;
+ * col2imgKernel / col2imgBackwardKernel, src/OperationKernels.cu:1364-1402):
+ * {b, 1, H*W, C} -> {b, C, H, W} and back; both overwrite.
+ */
+NZB_API int nzb_col2img(float* out, const float* in, int64_t H_out, int64_t W_out, int64_t C_out, int64_t batches,
+                        void* stream);
+NZB_API int nzb_col2img_backward(float* out, const float* in, int64_t H_out, int64_t W_out, int64_t C_out,
+                                 int64_t batches, void* stream);
+
+/*
+ * AddNode forward / backward (src/Nodes.cu:95-146; MatrixAddKernel src/OperationKernels.cu:12-37,
+ * gradCopyKernel :1230-1236). Shapes are {N,C,H,W}; N and C broadcast. Backward: an input of
+ * the output's shape receives a copy (overwrite); a broadcast input receives += the sum over
+ * the batches it was broadcast to (the reference's racy per-slice launches, made deterministic).
+ */
+NZB_API int nzb_add_broadcast(float* out, const float* a, const float* b, const int64_t shapeA[4],
+                              const int64_t shapeB[4], void* stream);
+NZB_API int nzb_add_backward(float* gin, const float* gout, const int64_t shapeIn[4], const int64_t shapeOut[4],
+                             void* stream);
+
+/* ReLU and its backward (overwrite), src/OperationKernels.cu:230-253. */
+NZB_API int nzb_relu(float* out, const float* in, int64_t n, void* stream);
+NZB_API int nzb_relu_backward(float* gin, const float* x, const float* gout, int64_t n, void* stream);
+
+/*
+ * Average pooling, divisor = in-bounds taps (src/OperationKernels.cu:1404-1490). The backward
+ * ADDS to gin (gather form of the reference's atomicAdd scatter).
+ */
+NZB_API int nzb_avgpool(float* out, const float* in, int64_t pool, int64_t stride, int64_t pad, int64_t batches,
+                        int64_t channels, int64_t H_in, int64_t W_in, int64_t H_out, int64_t W_out, void* stream);
+NZB_API int nzb_avgpool_backward(float* gin, const float* gout, int64_t pool, int64_t stride, int64_t pad,
+                                 int64_t batches, int64_t channels, int64_t H_in, int64_t W_in, int64_t H_out,
+                                 int64_t W_out, void* stream);
+
+/*
+ * Softmax over each of `batches` vectors of n elements, fully on the device (the reference
+ * syncs the host once per vector for the exp-sum: Tensor::expSum, src/Tensor.cu:713-735;
+ * SummationExpKernel / SoftmaxKernel, src/OperationKernels.cu:477-523), and
+ * SoftmaxNode::backward (src/Nodes.cu:538-548): gin = J(y) * gout (overwrite).
+ * round_f16 != 0 rounds J and gout to fp16 as the reference's GEMM does.
+ */
+NZB_API int nzb_softmax(float* out, const float* in, int64_t batches, int64_t n, void* stream);
+NZB_API int nzb_softmax_backward(float* gin, const float* y, const float* gout, int64_t batches, int64_t n,
+                                 int round_f16, void* stream);
+
+/*
+ * Binary cross-entropy, mean over n elements (BinaryCrossEntropyKernel / BCEBackwardKernel,
+ * src/OperationKernels.cu:648-704). nzb_bce ADDS the loss to the device scalar loss_out
+ * (the reference's loss node accumulates too, src/Nodes.cu:822-840).
+ */
+NZB_API int nzb_bce(float* loss_out, const float* predict, const float* target, int64_t n, void* stream);
+NZB_API int nzb_bce_backward(float* out, const float* predict, const float* target, int64_t n, void* stream);
+
+/* Adam step with explicit t (AdamKernel, src/OperationKernels.cu:753-773; opt::Adam::step, src/Optimizer.cu:86-102). */
+NZB_API int nzb_adam(float* data, float* m, float* v, const float* grad, float lr, float beta1, float beta2,
+                     float eps, int t, int64_t n, void* stream);
+
+/* FillKernel (src/OperationKernels.cu:1146-1156), ExpandKernel (:1282-1296; batch broadcast copy), in-place scale. */
+NZB_API int nzb_fill(float* data, float value, int64_t n, void* stream);
+NZB_API int nzb_expand(float* out, const float* in, int64_t per_batch, int64_t batches, void* stream);
+NZB_API int nzb_scale(float* data, float factor, int64_t n, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

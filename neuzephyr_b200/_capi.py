@@ -14,6 +14,9 @@ EXPORTS = [
     "nzb_version", "nzb_last_error_string", "nzb_device_status", "nzb_device_status_reset",
     "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_gemm_f16", "nzb_gemm_static", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
     "nzb_gemm_backward", "nzb_cast_f32_f16",
+    "nzb_img2col", "nzb_img2col_backward", "nzb_col2img", "nzb_col2img_backward", "nzb_add_broadcast",
+    "nzb_add_backward", "nzb_relu", "nzb_relu_backward", "nzb_avgpool", "nzb_avgpool_backward", "nzb_softmax",
+    "nzb_softmax_backward", "nzb_bce", "nzb_bce_backward", "nzb_adam", "nzb_fill", "nzb_expand", "nzb_scale",
 ]
 
 
@@ -60,6 +63,25 @@ def lib():
         L.nzb_cast_f32_f16.argtypes = [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                        ctypes.c_int, vp]
         L.nzb_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+        i64, f32, ci = ctypes.c_int64, ctypes.c_float, ctypes.c_int
+        L.nzb_img2col.argtypes = [vp, vp] + [i64] * 10 + [vp]
+        L.nzb_img2col_backward.argtypes = [vp, vp] + [i64] * 10 + [vp]
+        L.nzb_col2img.argtypes = [vp, vp] + [i64] * 4 + [vp]
+        L.nzb_col2img_backward.argtypes = [vp, vp] + [i64] * 4 + [vp]
+        L.nzb_add_broadcast.argtypes = [vp, vp, vp, i64p, i64p, vp]
+        L.nzb_add_backward.argtypes = [vp, vp, i64p, i64p, vp]
+        L.nzb_relu.argtypes = [vp, vp, i64, vp]
+        L.nzb_relu_backward.argtypes = [vp, vp, vp, i64, vp]
+        L.nzb_avgpool.argtypes = [vp, vp] + [i64] * 9 + [vp]
+        L.nzb_avgpool_backward.argtypes = [vp, vp] + [i64] * 9 + [vp]
+        L.nzb_softmax.argtypes = [vp, vp, i64, i64, vp]
+        L.nzb_softmax_backward.argtypes = [vp, vp, vp, i64, i64, ci, vp]
+        L.nzb_bce.argtypes = [vp, vp, vp, i64, vp]
+        L.nzb_bce_backward.argtypes = [vp, vp, vp, i64, vp]
+        L.nzb_adam.argtypes = [vp, vp, vp, vp, f32, f32, f32, f32, ci, i64, vp]
+        L.nzb_fill.argtypes = [vp, f32, i64, vp]
+        L.nzb_expand.argtypes = [vp, vp, i64, i64, vp]
+        L.nzb_scale.argtypes = [vp, f32, i64, vp]
         _lib = L
     return _lib
 
