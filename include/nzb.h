@@ -167,6 +167,51 @@ NZB_API int nzb_gemm_f16(const nzb_gemm_desc* desc, const void* A16, const void*
 NZB_API int nzb_cast_f32_f16(const float* in, void* out_f16, int64_t rows, int64_t cols, int64_t ld_in,
                              int64_t ld_out, int transpose, void* stream);
 
+/* Convolution ------------------------------------------------------------------------------ */
+
+/*
+ * Conv2d as NeuZephyr composes it (Model::Conv2d, src/Model.cu:244-263):
+ *   x {N, C, H, W} NCHW; w {wN, 1, C*Kh*Kw, Cout} row-major with k = c*Kh*Kw + kh*Kw + kw and
+ *   wN = 1 (shared) or N (weights_per_sample: one matrix per sample, as the reference
+ *   allocates them); y {N, Cout, Ho, Wo}; Ho = (H + 2 pad - Kh)/stride + 1.
+ *   bias_mode NZB_BIAS_MATRIX: bias {1, 1, Ho*Wo, Cout} (the reference's untied bias);
+ *   NZB_BIAS_ROW: one value per output channel.
+ *   accumulate: y += result; relu: max(., 0) last.
+ */
+typedef struct nzb_conv_desc {
+    int64_t N, C, H, W, Cout, Kh, Kw, stride, pad;
+    int32_t weights_per_sample;
+    int32_t bias_mode;
+    int32_t relu;
+    int32_t accumulate;
+} nzb_conv_desc;
+
+/* Scratch bytes for any of the nzb_conv2d_* calls with this descriptor (fp16 weight staging). */
+NZB_API int nzb_conv2d_workspace_bytes(const nzb_conv_desc* desc, size_t* bytes_out);
+
+/*
+ * Forward: one implicit-GEMM kernel in place of Img2Col -> MatMul -> Bias -> [ReLU] -> Col2Img
+ * (src/Nodes.cu:624-630, 165-167, 95-97, 344-354, 655-658; kernels src/OperationKernels.cu:1308-1335,
+ * 821-1026, 12-37, 230-240, 1364-1382). fp32 in/out, operands rounded to fp16, fp32 accumulation.
+ */
+NZB_API int nzb_conv2d_forward(const nzb_conv_desc* desc, const float* x, const float* w, const float* bias,
+                               float* y, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * dx += gradient of the forward with respect to x: replaces col2imgBackward ->
+ * MatMulNode::backward's dA = dC * B^T (transpose + GEMMBackwardParallel) -> img2colBackward's
+ * atomicAdd scatter (src/Nodes.cu:660-665, 169-176, 632-640; src/OperationKernels.cu:1384-1402,
+ * 125-160, 1028-1144, 1337-1362) with one gather-form implicit GEMM over dy. stride 1, square kernels.
+ */
+NZB_API int nzb_conv2d_backward_data(const nzb_conv_desc* desc, const float* dy, const float* w, float* dx,
+                                     void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * dbias {1,1,Ho*Wo,Cout} += sum over the batch of dy (AddNode::backward's gradCopy on the
+ * bias after col2imgBackward, src/Nodes.cu:106-121, 660-665).
+ */
+NZB_API int nzb_conv2d_backward_bias(const nzb_conv_desc* desc, const float* dy, float* dbias, void* stream);
+
 /* Node operations around the contraction ---------------------------------------------- */
 
 /*

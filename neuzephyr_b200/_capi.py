@@ -14,6 +14,7 @@ EXPORTS = [
     "nzb_version", "nzb_last_error_string", "nzb_device_status", "nzb_device_status_reset",
     "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_gemm_f16", "nzb_gemm_static", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
     "nzb_gemm_backward", "nzb_cast_f32_f16",
+    "nzb_conv2d_workspace_bytes", "nzb_conv2d_forward", "nzb_conv2d_backward_data", "nzb_conv2d_backward_bias",
     "nzb_img2col", "nzb_img2col_backward", "nzb_col2img", "nzb_col2img_backward", "nzb_add_broadcast",
     "nzb_add_backward", "nzb_relu", "nzb_relu_backward", "nzb_avgpool", "nzb_avgpool_backward", "nzb_softmax",
     "nzb_softmax_backward", "nzb_bce", "nzb_bce_backward", "nzb_adam", "nzb_fill", "nzb_expand", "nzb_scale",
@@ -32,6 +33,12 @@ class GemmDesc(ctypes.Structure):
         ("bias_ld", ctypes.c_int64),
         ("relu", ctypes.c_int32), ("reserved", ctypes.c_int32),
     ]
+
+
+class ConvDesc(ctypes.Structure):
+    """struct nzb_conv_desc"""
+    _fields_ = [(n, ctypes.c_int64) for n in ("N", "C", "H", "W", "Cout", "Kh", "Kw", "stride", "pad")] + \
+               [(n, ctypes.c_int32) for n in ("weights_per_sample", "bias_mode", "relu", "accumulate")]
 
 
 class NzbError(RuntimeError):
@@ -64,6 +71,11 @@ def lib():
                                        ctypes.c_int, vp]
         L.nzb_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
         i64, f32, ci = ctypes.c_int64, ctypes.c_float, ctypes.c_int
+        cd = ctypes.POINTER(ConvDesc)
+        L.nzb_conv2d_workspace_bytes.argtypes = [cd, ctypes.POINTER(sz)]
+        L.nzb_conv2d_forward.argtypes = [cd, vp, vp, vp, vp, vp, sz, vp]
+        L.nzb_conv2d_backward_data.argtypes = [cd, vp, vp, vp, vp, sz, vp]
+        L.nzb_conv2d_backward_bias.argtypes = [cd, vp, vp, vp]
         L.nzb_img2col.argtypes = [vp, vp] + [i64] * 10 + [vp]
         L.nzb_img2col_backward.argtypes = [vp, vp] + [i64] * 10 + [vp]
         L.nzb_col2img.argtypes = [vp, vp] + [i64] * 4 + [vp]

@@ -1,0 +1,548 @@
+// Convolution as an implicit GEMM on sm_100a: no im2col buffer is ever materialised.
+//
+// Replaces the composition Model::Conv2d builds (NeuZephyr src/Model.cu:244-263):
+//   Img2Col (img2colKernel, src/OperationKernels.cu:1308-1328) -> MatMul (the WMMA GEMM,
+//   :821-1026) -> Bias (MatrixAddKernel :12-37) -> [ReLU :230-240] -> Col2Img (:1364-1376)
+// by ONE kernel, and its backward-data half (col2imgBackward -> GEMMBackward(dC, W^T) ->
+// img2colBackward atomics, src/Nodes.cu:660-665, 169-176, 632-640) by the same kernel run
+// on dY with flipped taps (gather form, no atomics).
+//
+// GEMM view: M = output pixels of one image (tiles of 128 consecutive pixels), N = output
+// channels, K = C*Kh*Kw in the reference's order k = c*Kh*Kw + kh*Kw + kw.
+//   A tile (128 pixels x 64 k): gathered straight from the NCHW fp32 input by four producer
+//     warps, rounded to fp16 (RN) in registers and written to shared memory in the
+//     tensor core's M-major 128-byte-swizzled layout (pixels are the contiguous direction
+//     of both the input image rows and the tile).
+//   B tile (BN channels x 64 k): fp16 K-major weights staged once per call, loaded by TMA.
+//   D: fp32 accumulators in tensor memory (double buffered).
+//   Epilogue: lanes are consecutive pixels, so each channel is written to NCHW with
+//     coalesced stores straight from registers, after bias (per pixel x channel matrix as in
+//     NeuZephyr, or per channel) / accumulate / ReLU.
+// CTA = 320 threads: warp 0 weight TMA, warp 1 MMA issue + tensor-memory owner, warps 2-5
+// epilogue, warps 6-9 A-tile producers. Persistent over (image, pixel tile, channel tile).
+// Every wait is bounded as in the GEMM kernel.
+#include <cuda_fp16.h>
+
+#include "nzb_internal.h"
+#include "nzb_ptx.cuh"
+
+namespace nzb {
+
+struct ConvParams {
+    const float* X;  // gathered tensor {N, C, H, W}
+    float* Y;        // result {N, Cout, Ho, Wo}
+    const float* bias;
+    int32_t C, H, W, Cout, Kh, Kw, stride, pad;
+    int32_t Ho, Wo, HoWo, K;
+    int32_t k_blocks, last_ksteps;
+    int32_t tiles_per_image, tiles_n;
+    int32_t w_per_sample;  // weight matrix index = image index
+    int32_t bias_mode;     // NZB_BIAS_NONE, NZB_BIAS_ROW ([Cout]) or NZB_BIAS_MATRIX ([Ho*Wo][Cout])
+    int32_t accumulate, relu;
+    int64_t total_tiles;
+    int* status;
+};
+
+template <int BN_, int STAGES_>
+struct ConvCfg {
+    static constexpr int BN = BN_, STAGES = STAGES_;
+    static constexpr int A_BYTES = 128 * 64 * 2;
+    static constexpr int B_BYTES = BN * 64 * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+    static constexpr int CHUNK = (BN < 32) ? BN : 32;
+    static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
+};
+
+// A operand descriptor: M-major, SWIZZLE_128B. The tile is stored as 2 pixel blocks of 64
+// (8192 bytes apart = leading byte offset) x 8 k-groups of 8 (1024 bytes apart = stride
+// byte offset); inside a 1024-byte atom row r = k % 8 holds 64 pixels (128 bytes) with its
+// 16-byte chunks XOR-swizzled by r.
+__device__ __forceinline__ uint64_t make_sw128_mmajor_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+    d |= static_cast<uint64_t>(8192 >> 4) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+// kind::f16, fp16 operands, fp32 accumulate, A M-major (bit 15), B K-major.
+__host__ __device__ constexpr uint32_t make_idesc_conv(uint32_t M, uint32_t N) {
+    return (1u << 4) | (1u << 15) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+struct ConvTile {
+    int32_t img, mt, nt;
+};
+__device__ __forceinline__ ConvTile decode_conv_tile(const ConvParams& p, int64_t tile) {
+    // channel tiles innermost so that the CTAs sharing an input window run together
+    ConvTile t;
+    t.nt = static_cast<int32_t>(tile % p.tiles_n);
+    const int64_t r = tile / p.tiles_n;
+    t.mt = static_cast<int32_t>(r % p.tiles_per_image);
+    t.img = static_cast<int32_t>(r / p.tiles_per_image);
+    return t;
+}
+
+template <class Cfg>
+__global__ void __launch_bounds__(320, 1)
+conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvParams p) {
+    using namespace ptx;
+    constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full = bars;                     // [STAGES] weights landed (tx) + 4 producer warps arrived
+    uint64_t* empty = bars + STAGES;           // [STAGES]
+    uint64_t* tfull = bars + 2 * STAGES;       // [2]
+    uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmW);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 5);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- weight TMA ----------------
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            const ConvTile t = decode_conv_tile(p, tile);
+            const int32_t zw = p.w_per_sample ? t.img : 0;
+            for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&full[s], Cfg::B_BYTES);
+                    tma_load_3d(smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmW, kb * 64, t.nt * BN, zw, &full[s]);
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok && lane == 0) {
+            // Wait (one bounded budget in total) for weight copies still in flight.
+            const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
+            const long long t0 = clock64();
+            for (uint32_t j = first; j < it; j++) {
+                while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1)) {
+                    if (clock64() - t0 > kWaitCycleLimit) break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        constexpr uint32_t idesc = make_idesc_conv(128, BN);
+        uint32_t it = 0, tcount = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, tcount++) {
+            const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+            if (!mbar_wait_warp(&tempty[acc], aph ^ 1, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                const uint64_t da = make_sw128_mmajor_desc(sa);
+                const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                const int32_t ksteps = (kb == p.k_blocks - 1) ? p.last_ksteps : 4;
+                if (elect_one()) {
+                    // A: one k step = two 8-k groups = 2048 bytes = 128 address units;
+                    // B: one k step = 32 bytes = 2 address units
+                    mma_f16_ss(d_tmem, da, db, idesc, kb > 0 ? 1u : 0u);
+                    if (ksteps > 1) mma_f16_ss(d_tmem, da + 128, db + 2, idesc, 1u);
+                    if (ksteps > 2) mma_f16_ss(d_tmem, da + 256, db + 4, idesc, 1u);
+                    if (ksteps > 3) mma_f16_ss(d_tmem, da + 384, db + 6, idesc, 1u);
+                    mma_commit(&empty[s]);
+                }
+                __syncwarp();
+            }
+            if (ok && elect_one()) mma_commit(&tfull[acc]);
+            __syncwarp();
+        }
+    } else if (warp < 6) {
+        // ---------------- epilogue: lanes = consecutive pixels, coalesced per channel ----------------
+        const int q = warp & 3;
+        uint32_t tcount = 0;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, tcount++) {
+            const ConvTile t = decode_conv_tile(p, tile);
+            const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+            if (!mbar_wait_bounded(&tfull[acc], aph, abort_flag)) break;
+            tc_fence_after();
+            const int32_t pix = t.mt * 128 + q * 32 + lane;
+            const bool pix_ok = pix < p.HoWo;
+            float* yb = p.Y + (static_cast<int64_t>(t.img) * p.Cout) * p.HoWo + pix;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += Cfg::CHUNK) {
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c0;
+                uint32_t v[Cfg::CHUNK];
+                if constexpr (Cfg::CHUNK == 32) tmem_ld_32x32(taddr, v);
+                else tmem_ld_32x16(taddr, v);
+                tmem_ld_wait();
+                const int32_t co0 = t.nt * BN + c0;
+                if (pix_ok) {
+#pragma unroll
+                    for (int j = 0; j < Cfg::CHUNK; j++) {
+                        const int32_t co = co0 + j;
+                        if (co < p.Cout) {
+                            float x = __uint_as_float(v[j]);
+                            float* dst = yb + static_cast<int64_t>(co) * p.HoWo;
+                            if (p.accumulate) x += *dst;
+                            if (p.bias_mode == NZB_BIAS_MATRIX) x += __ldg(p.bias + static_cast<int64_t>(pix) * p.Cout + co);
+                            else if (p.bias_mode == NZB_BIAS_ROW) x += __ldg(p.bias + co);
+                            if (p.relu) x = fmaxf(x, 0.f);
+                            *dst = x;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+    } else {
+        // ---------------- A-tile producers: gather + round + swizzled store ----------------
+        const int pw = warp - 6;
+        const int mb = pw & 1;     // pixel block of 64 inside the tile
+        const int khalf = pw >> 1;  // which 32 of the k block's 64 columns
+        const int KHW = p.Kh * p.Kw;
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            const ConvTile t = decode_conv_tile(p, tile);
+            // this lane's two pixels
+            const int32_t p0 = t.mt * 128 + mb * 64 + 2 * lane, p1 = p0 + 1;
+            const bool v0 = p0 < p.HoWo, v1 = p1 < p.HoWo;
+            const int32_t h0 = (p0 / p.Wo) * p.stride - p.pad, w0 = (p0 % p.Wo) * p.stride - p.pad;
+            const int32_t h1 = (p1 / p.Wo) * p.stride - p.pad, w1 = (p1 % p.Wo) * p.stride - p.pad;
+            const float* xb = p.X + static_cast<int64_t>(t.img) * p.C * p.H * p.W;
+            for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                uint8_t* sA = smem + s * Cfg::STAGE_BYTES + mb * 8192 + khalf * 4096;
+                int32_t k = kb * 64 + khalf * 32;
+                int32_t c = k / KHW;
+                int32_t r = k - c * KHW;
+                int32_t kh = r / p.Kw, kw = r - kh * p.Kw;
+#pragma unroll 1
+                for (int g = 0; g < 4; g++) {  // four 8-k groups
+                    float a0[8], a1[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int32_t hh0 = h0 + kh, ww0 = w0 + kw, hh1 = h1 + kh, ww1 = w1 + kw;
+                        const bool kin = k < p.K;
+                        const float* src = xb + static_cast<int64_t>(c) * p.H * p.W;
+                        const bool in0 = kin && v0 && (unsigned)hh0 < (unsigned)p.H && (unsigned)ww0 < (unsigned)p.W;
+                        const bool in1 = kin && v1 && (unsigned)hh1 < (unsigned)p.H && (unsigned)ww1 < (unsigned)p.W;
+                        a0[j] = in0 ? __ldg(src + hh0 * p.W + ww0) : 0.f;
+                        a1[j] = in1 ? __ldg(src + hh1 * p.W + ww1) : 0.f;
+                        k++;
+                        if (++kw == p.Kw) {
+                            kw = 0;
+                            if (++kh == p.Kh) {
+                                kh = 0;
+                                c++;
+                            }
+                        }
+                    }
+                    uint8_t* atom = sA + g * 1024;
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const __half2 h = __floats2half2_rn(a0[j], a1[j]);
+                        const uint32_t off = j * 128 + ((((lane >> 2) ^ j) & 7) << 4) + ((lane & 3) << 2);
+                        *reinterpret_cast<__half2*>(atom + off) = h;
+                    }
+                }
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
+            }
+        }
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = NZB_ERR_DEVICE_TIMEOUT;
+        __threadfence_system();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Weight staging for backward-data: W2[c][co*Kh*Kw + kh'*Kw + kw'] =
+//   half(W[wb][(c*Kh + (Kh-1-kh'))*Kw + (Kw-1-kw')][co])  -- the flipped-tap kernel whose
+// forward convolution over dY is the gradient with respect to the input.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) flip_weights_kernel(__half* __restrict__ out, const float* __restrict__ w,
+                                                           int64_t C, int64_t Cout, int64_t Kh, int64_t Kw, int64_t Kp2,
+                                                           int64_t wN) {
+    const int64_t K2 = Cout * Kh * Kw;
+    const int64_t total = wN * C * Kp2;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t k2 = i % Kp2;
+        const int64_t c = (i / Kp2) % C;
+        const int64_t b = i / (Kp2 * C);
+        float v = 0.f;
+        if (k2 < K2) {
+            const int64_t co = k2 / (Kh * Kw), r = k2 % (Kh * Kw);
+            const int64_t kh = Kh - 1 - r / Kw, kw = Kw - 1 - r % Kw;
+            v = __ldg(w + (b * C * Kh * Kw + (c * Kh + kh) * Kw + kw) * Cout + co);
+        }
+        out[i] = __float2half_rn(v);
+    }
+}
+
+// dbias[p][co] += sum_b dy[b][co][p]   (AddNode::backward on the untied conv bias after
+// col2imgBackward; src/Nodes.cu:106-121, 660-665). Tiled transpose-reduce, coalesced both ways.
+__global__ void __launch_bounds__(256) conv_bias_grad_kernel(float* __restrict__ dbias, const float* __restrict__ dy,
+                                                             int64_t N, int64_t Cout, int64_t HoWo) {
+    __shared__ float tile[32][33];
+    const int64_t tp = (HoWo + 31) >> 5, tc = (Cout + 31) >> 5;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int64_t t = blockIdx.x; t < tp * tc; t += gridDim.x) {
+        const int64_t p0 = (t / tc) << 5, c0 = (t % tc) << 5;
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int64_t co = c0 + ty + i * 8, pp = p0 + tx;
+            float s = 0.f;
+            if (co < Cout && pp < HoWo)
+                for (int64_t b = 0; b < N; b++) s += __ldg(dy + (b * Cout + co) * HoWo + pp);
+            tile[ty + i * 8][tx] = s;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int64_t pp = p0 + ty + i * 8, co = c0 + tx;
+            if (pp < HoWo && co < Cout) dbias[pp * Cout + co] += tile[tx][ty + i * 8];
+        }
+        __syncthreads();
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+static int make_weight_map(CUtensorMap* map, const __half* base, int64_t K, int64_t Kp, int64_t rows, int64_t nmat,
+                           int box_rows) {
+    EncodeTiledFn enc;
+    int rc = get_encode_tiled(&enc);
+    if (rc != NZB_OK) return rc;
+    cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)nmat};
+    cuuint64_t strides[2] = {(cuuint64_t)Kp * 2, (cuuint64_t)rows * (cuuint64_t)Kp * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return NZB_OK;
+}
+
+// Runs the implicit-GEMM kernel: Y (op)= conv(X, W16) with W16 staged as [wN][Cout][Kp].
+struct ConvRun {
+    const float* X;
+    float* Y;
+    const float* bias;
+    int64_t N, C, H, W, Cout, Kh, Kw, stride, pad, Ho, Wo;
+    int32_t w_per_sample, bias_mode, accumulate, relu;
+};
+
+template <class Cfg>
+static int run_conv_cfg(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN, const DeviceState& ds,
+                        cudaStream_t stream) {
+    ConvParams p{};
+    p.X = r.X; p.Y = r.Y; p.bias = r.bias;
+    p.C = (int32_t)r.C; p.H = (int32_t)r.H; p.W = (int32_t)r.W; p.Cout = (int32_t)r.Cout;
+    p.Kh = (int32_t)r.Kh; p.Kw = (int32_t)r.Kw; p.stride = (int32_t)r.stride; p.pad = (int32_t)r.pad;
+    p.Ho = (int32_t)r.Ho; p.Wo = (int32_t)r.Wo; p.HoWo = (int32_t)(r.Ho * r.Wo);
+    p.K = (int32_t)(r.C * r.Kh * r.Kw);
+    p.k_blocks = (p.K + 63) / 64;
+    p.last_ksteps = (p.K - (p.k_blocks - 1) * 64 + 15) / 16;
+    p.tiles_per_image = (p.HoWo + 127) / 128;
+    p.w_per_sample = r.w_per_sample;
+    p.bias_mode = r.bias ? r.bias_mode : NZB_BIAS_NONE;
+    p.accumulate = r.accumulate; p.relu = r.relu;
+    p.status = ds.status_dev;
+    p.tiles_n = (p.Cout + Cfg::BN - 1) / Cfg::BN;
+    CUtensorMap tmW;
+    int rc = make_weight_map(&tmW, W16, p.K, Kp, p.Cout, wN, Cfg::BN);
+    if (rc != NZB_OK) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_igemm_tcgen05_kernel<Cfg>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    p.total_tiles = (int64_t)r.N * p.tiles_per_image * p.tiles_n;
+    const int64_t grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
+    conv2d_igemm_tcgen05_kernel<Cfg><<<(unsigned)grid, 320, Cfg::SMEM_BYTES, stream>>>(tmW, p);
+    NZB_CUDA_TRY(cudaGetLastError());
+    return NZB_OK;
+}
+
+static int run_conv(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN, cudaStream_t stream) {
+    DeviceState* ds;
+    int rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    if (r.N <= 0 || r.Cout <= 0 || r.Ho <= 0 || r.Wo <= 0) return NZB_OK;
+    if (r.Ho * r.Wo > INT32_MAX - 256 || r.C * r.Kh * r.Kw > INT32_MAX - 256 || r.C * r.H * r.W > INT32_MAX)
+        return fail(NZB_ERR_UNSUPPORTED, "per-image extent exceeds 2^31");
+    if (r.Cout > 128) return run_conv_cfg<ConvCfg<256, 4>>(r, W16, Kp, wN, *ds, stream);
+    if (r.Cout > 64) return run_conv_cfg<ConvCfg<128, 6>>(r, W16, Kp, wN, *ds, stream);
+    if (r.Cout > 32) return run_conv_cfg<ConvCfg<64, 8>>(r, W16, Kp, wN, *ds, stream);
+    if (r.Cout > 16) return run_conv_cfg<ConvCfg<32, 8>>(r, W16, Kp, wN, *ds, stream);
+    return run_conv_cfg<ConvCfg<16, 8>>(r, W16, Kp, wN, *ds, stream);
+}
+
+static int check_conv_desc(const nzb_conv_desc* d, int64_t* Ho, int64_t* Wo) {
+    if (!d) return fail(NZB_ERR_BAD_ARG, "descriptor is null");
+    if (d->N < 0 || d->C < 1 || d->H < 1 || d->W < 1 || d->Cout < 1 || d->Kh < 1 || d->Kw < 1 || d->stride < 1 ||
+        d->pad < 0)
+        return fail(NZB_ERR_BAD_ARG, "bad convolution extent");
+    if (d->H + 2 * d->pad < d->Kh || d->W + 2 * d->pad < d->Kw) return fail(NZB_ERR_BAD_ARG, "kernel larger than the padded input");
+    if (d->bias_mode != NZB_BIAS_NONE && d->bias_mode != NZB_BIAS_ROW && d->bias_mode != NZB_BIAS_MATRIX)
+        return fail(NZB_ERR_BAD_ARG, "bias_mode must be NONE, ROW ([Cout]) or MATRIX ([Ho*Wo][Cout])");
+    *Ho = (d->H + 2 * d->pad - d->Kh) / d->stride + 1;
+    *Wo = (d->W + 2 * d->pad - d->Kw) / d->stride + 1;
+    return NZB_OK;
+}
+
+}  // namespace nzb
+
+using namespace nzb;
+
+extern "C" {
+
+int nzb_conv2d_workspace_bytes(const nzb_conv_desc* d, size_t* bytes_out) {
+    if (!bytes_out) return fail(NZB_ERR_BAD_ARG, "bytes_out is null");
+    int64_t Ho, Wo;
+    int rc = check_conv_desc(d, &Ho, &Wo);
+    if (rc != NZB_OK) return rc;
+    const int64_t wN = d->weights_per_sample ? d->N : 1;
+    const int64_t Kf = round_up(d->C * d->Kh * d->Kw, kOperandKAlign);      // forward: [Cout][Kf]
+    const int64_t Kb = round_up(d->Cout * d->Kh * d->Kw, kOperandKAlign);   // backward data: [C][Kb]
+    const int64_t f = wN * d->Cout * Kf * 2, b = wN * d->C * Kb * 2;
+    *bytes_out = (size_t)round_up(f > b ? f : b, 256);
+    return NZB_OK;
+}
+
+int nzb_conv2d_forward(const nzb_conv_desc* d, const float* x, const float* w, const float* bias, float* y,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+    int64_t Ho, Wo;
+    int rc = check_conv_desc(d, &Ho, &Wo);
+    if (rc != NZB_OK) return rc;
+    if (d->N == 0) return NZB_OK;
+    if (!x || !w || !y) return fail(NZB_ERR_BAD_ARG, "x, w and y must be non-null");
+    if (d->bias_mode != NZB_BIAS_NONE && !bias) return fail(NZB_ERR_BAD_ARG, "bias_mode set but bias is null");
+    size_t need;
+    nzb_conv2d_workspace_bytes(d, &need);
+    if (!workspace || workspace_bytes < need) return fail(NZB_ERR_WORKSPACE, "workspace of %zu bytes needed", need);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(NZB_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t wN = d->weights_per_sample ? d->N : 1;
+    const int64_t K = d->C * d->Kh * d->Kw, Kp = round_up(K, kOperandKAlign);
+    __half* W16 = reinterpret_cast<__half*>(workspace);
+    // w is {wN, 1, K, Cout} row-major: stage as [wN][Cout][Kp] (transpose + round)
+    rc = launch_cast(w, W16, d->Cout, K, d->Cout, Kp, 1, wN, 1, K * d->Cout, 0, s);
+    if (rc != NZB_OK) return rc;
+    ConvRun r{x, y, bias, d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, d->pad, Ho, Wo,
+              d->weights_per_sample ? 1 : 0, d->bias_mode, d->accumulate ? 1 : 0, d->relu ? 1 : 0};
+    return run_conv(r, W16, Kp, wN, s);
+}
+
+int nzb_conv2d_backward_data(const nzb_conv_desc* d, const float* dy, const float* w, float* dx, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+    int64_t Ho, Wo;
+    int rc = check_conv_desc(d, &Ho, &Wo);
+    if (rc != NZB_OK) return rc;
+    if (d->N == 0) return NZB_OK;
+    if (!dy || !w || !dx) return fail(NZB_ERR_BAD_ARG, "dy, w and dx must be non-null");
+    if (d->stride != 1) return fail(NZB_ERR_UNSUPPORTED, "the fused backward-data kernel handles stride 1; use nzb_gemm_backward + nzb_img2col_backward for other strides");
+    if (d->Kh - 1 - d->pad < 0 || d->Kw - 1 - d->pad < 0) return fail(NZB_ERR_UNSUPPORTED, "pad larger than kernel - 1");
+    if (d->Kh != d->Kw) return fail(NZB_ERR_UNSUPPORTED, "the fused backward-data kernel needs a square kernel (one pad value)");
+    size_t need;
+    nzb_conv2d_workspace_bytes(d, &need);
+    if (!workspace || workspace_bytes < need) return fail(NZB_ERR_WORKSPACE, "workspace of %zu bytes needed", need);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(NZB_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    DeviceState* ds;
+    rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t wN = d->weights_per_sample ? d->N : 1;
+    const int64_t K2 = d->Cout * d->Kh * d->Kw, Kp2 = round_up(K2, kOperandKAlign);
+    __half* W16 = reinterpret_cast<__half*>(workspace);
+    {
+        const int64_t total = wN * d->C * Kp2;
+        int64_t blocks = (total + 255) / 256;
+        if (blocks > (int64_t)ds->sm_count * 16) blocks = (int64_t)ds->sm_count * 16;
+        flip_weights_kernel<<<(unsigned)blocks, 256, 0, s>>>(W16, w, d->C, d->Cout, d->Kh, d->Kw, Kp2, wN);
+        NZB_CUDA_TRY(cudaGetLastError());
+    }
+    // dX {N, C, H, W} += conv(dY {N, Cout, Ho, Wo}, flipped weights, pad' = Kh - 1 - pad, stride 1)
+    ConvRun r{dy, dx, nullptr, d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, 1, d->Kh - 1 - d->pad, d->H, d->W,
+              d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, 1, 0};
+    return run_conv(r, W16, Kp2, wN, s);
+}
+
+int nzb_conv2d_backward_bias(const nzb_conv_desc* d, const float* dy, float* dbias, void* stream) {
+    int64_t Ho, Wo;
+    int rc = check_conv_desc(d, &Ho, &Wo);
+    if (rc != NZB_OK) return rc;
+    if (!dy || !dbias) return fail(NZB_ERR_BAD_ARG, "null pointer");
+    DeviceState* ds;
+    rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    if (d->N == 0) return NZB_OK;
+    const int64_t tiles = ((Ho * Wo + 31) / 32) * ((d->Cout + 31) / 32);
+    int64_t blocks = tiles < (int64_t)ds->sm_count * 16 ? tiles : (int64_t)ds->sm_count * 16;
+    conv_bias_grad_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(dbias, dy, d->N, d->Cout,
+                                                                                        Ho * Wo);
+    NZB_CUDA_TRY(cudaGetLastError());
+    return NZB_OK;
+}
+
+}  // extern "C"

@@ -120,3 +120,50 @@ def cast_f32_f16(x, transpose=False):
 
 def device_status():
     return C.device_status()
+
+
+def _conv_desc(x_shape, w_shape, Kh, Kw, stride, pad, bias_mode=C.BIAS_NONE, relu=False, accumulate=False):
+    d = C.ConvDesc()
+    d.N, d.C, d.H, d.W = [int(v) for v in x_shape]
+    d.Cout, d.Kh, d.Kw, d.stride, d.pad = int(w_shape[3]), Kh, Kw, stride, pad
+    d.weights_per_sample = int(w_shape[0] > 1)
+    d.bias_mode, d.relu, d.accumulate = bias_mode, int(relu), int(accumulate)
+    return d
+
+
+def _conv_ws(d, device):
+    n = ctypes.c_size_t(0)
+    C.check(C.lib().nzb_conv2d_workspace_bytes(ctypes.byref(d), ctypes.byref(n)))
+    return _workspace(n.value, device)
+
+
+def conv2d_forward(x, w, bias, Kh, Kw, stride, pad, relu=False, bias_mode=None, out=None):
+    """y = conv(x, w) (+ bias) (ReLU); x {N,C,H,W}, w {wN,1,C*Kh*Kw,Cout}, bias {1,1,Ho*Wo,Cout} or [Cout]."""
+    _check_f32_cuda(x, w, bias, out)
+    if bias_mode is None:
+        bias_mode = C.BIAS_NONE if bias is None else (C.BIAS_ROW if bias.dim() == 1 else C.BIAS_MATRIX)
+    d = _conv_desc(x.shape, w.shape, Kh, Kw, stride, pad, bias_mode, relu)
+    Ho, Wo = (d.H + 2 * pad - Kh) // stride + 1, (d.W + 2 * pad - Kw) // stride + 1
+    if out is None:
+        out = torch.empty((d.N, d.Cout, Ho, Wo), dtype=torch.float32, device=x.device)
+    ws = _conv_ws(d, x.device)
+    C.check(C.lib().nzb_conv2d_forward(ctypes.byref(d), _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _ptr(ws),
+                                       ws.numel(), _stream()))
+    return out
+
+
+def conv2d_backward_data(dy, w, x_shape, Kh, Kw, stride, pad, dx):
+    """dx += d(conv)/dx (stride 1)."""
+    _check_f32_cuda(dy, w, dx)
+    d = _conv_desc(x_shape, w.shape, Kh, Kw, stride, pad)
+    ws = _conv_ws(d, dy.device)
+    C.check(C.lib().nzb_conv2d_backward_data(ctypes.byref(d), _ptr(dy), _ptr(w), _ptr(dx), _ptr(ws), ws.numel(),
+                                             _stream()))
+    return dx
+
+
+def conv2d_backward_bias(dy, x_shape, w_shape, Kh, Kw, stride, pad, dbias):
+    _check_f32_cuda(dy, dbias)
+    d = _conv_desc(x_shape, w_shape, Kh, Kw, stride, pad)
+    C.check(C.lib().nzb_conv2d_backward_bias(ctypes.byref(d), _ptr(dy), _ptr(dbias), _stream()))
+    return dbias

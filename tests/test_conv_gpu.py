@@ -1,0 +1,85 @@
+"""Fused implicit-GEMM convolution (forward, backward-data, bias gradient) through the C ABI
+against the host oracle's restatement of NeuZephyr's Img2Col -> MatMul -> Bias -> Col2Img
+composition. e_max = max|x - ref| / max|ref| <= 2e-5 against the fp64 result on fp16-rounded
+operands (fp32 accumulation order is the only difference), <= 1e-2 against unrounded operands."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import nz_oracle as O
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-5
+
+
+@pytest.fixture(scope="module")
+def nz():
+    import neuzephyr_b200 as nz
+    return nz
+
+
+def dev(x):
+    return torch.from_numpy(np.ascontiguousarray(x, dtype=np.float32)).cuda()
+
+
+def emax(x, ref):
+    ref = np.asarray(ref, np.float64)
+    den = np.max(np.abs(ref))
+    return float(np.max(np.abs(np.asarray(x, np.float64) - ref)) / (den if den > 0 else 1.0))
+
+
+CASES = [
+    # n, c, h, w, cout, k, stride, pad, per-sample weights
+    (2, 3, 6, 5, 4, 3, 1, 1, False),
+    (1, 3, 16, 16, 16, 3, 1, 1, False),
+    (2, 16, 20, 24, 16, 3, 1, 1, False),
+    (3, 5, 13, 11, 7, 3, 1, 1, True),
+    (2, 64, 14, 14, 128, 3, 1, 1, False),
+    (1, 8, 33, 29, 40, 5, 1, 2, False),
+    (2, 4, 17, 19, 24, 3, 2, 0, False),
+    (1, 70, 9, 9, 130, 1, 1, 0, False),
+    (2, 2, 40, 40, 300, 3, 1, 0, True),
+]
+
+
+@pytest.mark.parametrize("n,c,h,w,co,k,s,p,per_sample", CASES)
+def test_conv_forward(nz, n, c, h, w, co, k, s, p, per_sample):
+    rng = np.random.default_rng(n * 100 + c * 10 + co)
+    x = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)
+    wn = n if per_sample else 1
+    wt = (rng.normal(0, 1, (wn, 1, c * k * k, co)) * np.sqrt(2.0 / (c * k * k))).astype(np.float32)
+    ho, wo = O.conv_out_hw(h, w, k, k, s, p)
+    bias = rng.normal(0, 1, (1, 1, ho * wo, co)).astype(np.float32)
+    y = nz.conv2d_forward(dev(x), dev(wt), dev(bias), k, k, s, p).cpu().numpy()
+    torch.cuda.synchronize()
+    assert nz.device_status() == 0
+    assert emax(y, O.conv2d_forward(x, wt, bias, k, k, s, p, True)) <= TOL
+    assert emax(y, O.conv2d_forward(x, wt, bias, k, k, s, p, False)) <= 1e-2
+    # no bias + ReLU, and a per-channel bias
+    y2 = nz.conv2d_forward(dev(x), dev(wt), None, k, k, s, p, relu=True).cpu().numpy()
+    assert emax(y2, O.conv2d_forward(x, wt, None, k, k, s, p, True, relu=True)) <= TOL
+    bvec = rng.normal(0, 1, co).astype(np.float32)
+    y3 = nz.conv2d_forward(dev(x), dev(wt), dev(bvec), k, k, s, p).cpu().numpy()
+    ref3 = O.conv2d_forward(x, wt, None, k, k, s, p, True).astype(np.float64) + bvec[None, :, None, None]
+    assert emax(y3, ref3) <= TOL
+
+
+@pytest.mark.parametrize("n,c,h,w,co,k,s,p,per_sample", [cs for cs in CASES if cs[6] == 1])
+def test_conv_backward_data_and_bias(nz, n, c, h, w, co, k, s, p, per_sample):
+    rng = np.random.default_rng(n * 7 + c * 3 + co)
+    x = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)
+    wn = n if per_sample else 1
+    wt = (rng.normal(0, 1, (wn, 1, c * k * k, co)) * np.sqrt(2.0 / (c * k * k))).astype(np.float32)
+    ho, wo = O.conv_out_hw(h, w, k, k, s, p)
+    dy = rng.normal(0, 1, (n, co, ho, wo)).astype(np.float32)
+    dx_ref, _, db_ref = O.conv2d_backward(dy, x, wt, k, k, s, p, want_dw=False)
+    dx0 = rng.normal(0, 1, x.shape).astype(np.float32)
+    dx = dev(dx0)
+    nz.conv2d_backward_data(dev(dy), dev(wt), x.shape, k, k, s, p, dx)
+    db0 = rng.normal(0, 1, (1, 1, ho * wo, co)).astype(np.float32)
+    db = dev(db0)
+    nz.conv2d_backward_bias(dev(dy), x.shape, wt.shape, k, k, s, p, db)
+    torch.cuda.synchronize()
+    assert nz.device_status() == 0
+    assert emax(dx.cpu().numpy() - dx0, dx_ref) <= 5e-5  # accumulated onto dx0: one extra fp32 rounding
+    assert emax(db.cpu().numpy() - db0, db_ref) <= 5e-6
