@@ -9,7 +9,7 @@
 //
 // GEMM view: M = output pixels of one image (tiles of 128 consecutive pixels), N = output
 // channels, K = C*Kh*Kw in the reference's order k = c*Kh*Kw + kh*Kw + kw.
-//   A tile (128 pixels x 64 k): gathered straight from the NCHW fp32 input by four producer
+//   A tile (128 pixels x 64 k): gathered straight from the NCHW fp32 input by the producer
 //     warps, rounded to fp16 (RN) in registers and written to shared memory in the
 //     tensor core's M-major 128-byte-swizzled layout (pixels are the contiguous direction
 //     of both the input image rows and the tile).
@@ -18,8 +18,10 @@
 //   Epilogue: lanes are consecutive pixels, so each channel is written to NCHW with
 //     coalesced stores straight from registers, after bias (per pixel x channel matrix as in
 //     NeuZephyr, or per channel) / accumulate / ReLU.
-// CTA = 320 threads: warp 0 weight TMA, warp 1 MMA issue + tensor-memory owner, warps 2-5
-// epilogue, warps 6-9 A-tile producers. Persistent over (image, pixel tile, channel tile).
+// CTA = 704 threads: warp 0 weight TMA, warp 1 MMA issue + tensor-memory owner, warps 2-5
+// epilogue, warps 6-21 A-tile producers in two groups of eight that fill alternate ring
+// stages (every lane keeps 32 gathers in flight, so global-load latency overlaps between
+// the groups). Persistent over (image, pixel tile, channel tile).
 // Every wait is bounded as in the GEMM kernel.
 #include <cuda_fp16.h>
 
@@ -50,9 +52,12 @@ struct ConvCfg {
     static constexpr int B_BYTES = BN * 64 * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+    static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;  // per epilogue warp: 32 x 33 floats for the bias transpose
+    static constexpr int KTAB_BYTES = 16 * 32 * 8;     // per producer warp: 32 (offset, kh, kw) entries
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + KTAB_BYTES + BAR_BYTES;
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
     static constexpr int CHUNK = (BN < 32) ? BN : 32;
+    static constexpr int THREADS = 22 * 32;
     static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 };
@@ -93,27 +98,29 @@ __device__ __forceinline__ ConvTile decode_conv_tile(const ConvParams& p, int64_
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(320, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
 conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvParams p) {
     using namespace ptx;
     constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
-    uint64_t* full = bars;                     // [STAGES] weights landed (tx) + 4 producer warps arrived
+    float* epi = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
+    int2* ktab_all = reinterpret_cast<int2*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES + Cfg::KTAB_BYTES);
+    uint64_t* full = bars;                     // [STAGES] weights landed (tx) + the producer group's arrival
     uint64_t* empty = bars + STAGES;           // [STAGES]
     uint64_t* tfull = bars + 2 * STAGES;       // [2]
     uint64_t* tempty = bars + 2 * STAGES + 2;  // [2]
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
-    const int warp = threadIdx.x >> 5;
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);  // warp-uniform by construction
     const int lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
         prefetch_tensormap(&tmW);
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full[s], 5);
+            mbar_init(&full[s], 2);
             mbar_init(&empty[s], 1);
         }
         for (int a = 0; a < 2; a++) {
@@ -141,7 +148,7 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
             const int32_t zw = p.w_per_sample ? t.img : 0;
             for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                if (!mbar_wait_relaxed_warp(&empty[s], ph ^ 1, abort_flag)) {
                     ok = false;
                     break;
                 }
@@ -169,12 +176,12 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, tcount++) {
             const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
-            if (!mbar_wait_warp(&tempty[acc], aph ^ 1, abort_flag)) break;
+            if (!mbar_wait_relaxed_warp(&tempty[acc], aph ^ 1, abort_flag)) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BN;
             for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+                if (!mbar_wait_relaxed_warp(&full[s], ph, abort_flag)) {
                     ok = false;
                     break;
                 }
@@ -204,19 +211,33 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
         for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, tcount++) {
             const ConvTile t = decode_conv_tile(p, tile);
             const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
-            if (!mbar_wait_bounded(&tfull[acc], aph, abort_flag)) break;
+            if (!mbar_wait_relaxed(&tfull[acc], aph, abort_flag)) break;
             tc_fence_after();
-            const int32_t pix = t.mt * 128 + q * 32 + lane;
+            const int32_t pix0 = t.mt * 128 + q * 32;
+            const int32_t pix = pix0 + lane;
             const bool pix_ok = pix < p.HoWo;
             float* yb = p.Y + (static_cast<int64_t>(t.img) * p.Cout) * p.HoWo + pix;
+            float* bt = epi + (warp - 2) * 32 * 33;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += Cfg::CHUNK) {
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c0;
                 uint32_t v[Cfg::CHUNK];
                 if constexpr (Cfg::CHUNK == 32) tmem_ld_32x32(taddr, v);
                 else tmem_ld_32x16(taddr, v);
-                tmem_ld_wait();
                 const int32_t co0 = t.nt * BN + c0;
+                if (p.bias_mode == NZB_BIAS_MATRIX) {
+                    // bias is [pixel][channel]: read with lanes along channels (coalesced), transpose in
+                    // shared memory so that each lane ends up with its own pixel's row
+                    const int32_t co = co0 + (lane % Cfg::CHUNK);
+#pragma unroll 4
+                    for (int r = lane / Cfg::CHUNK; r < 32; r += 32 / Cfg::CHUNK) {
+                        const int32_t pp = pix0 + r;
+                        bt[r * 33 + (lane % Cfg::CHUNK)] =
+                            (pp < p.HoWo && co < p.Cout) ? __ldg(p.bias + static_cast<int64_t>(pp) * p.Cout + co) : 0.f;
+                    }
+                    __syncwarp();
+                }
+                tmem_ld_wait();
                 if (pix_ok) {
 #pragma unroll
                     for (int j = 0; j < Cfg::CHUNK; j++) {
@@ -225,13 +246,14 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
                             float x = __uint_as_float(v[j]);
                             float* dst = yb + static_cast<int64_t>(co) * p.HoWo;
                             if (p.accumulate) x += *dst;
-                            if (p.bias_mode == NZB_BIAS_MATRIX) x += __ldg(p.bias + static_cast<int64_t>(pix) * p.Cout + co);
+                            if (p.bias_mode == NZB_BIAS_MATRIX) x += bt[lane * 33 + j];
                             else if (p.bias_mode == NZB_BIAS_ROW) x += __ldg(p.bias + co);
                             if (p.relu) x = fmaxf(x, 0.f);
                             *dst = x;
                         }
                     }
                 }
+                __syncwarp();
             }
             tc_fence_before();
             __syncwarp();
@@ -239,63 +261,78 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
         }
     } else {
         // ---------------- A-tile producers: gather + round + swizzled store ----------------
+        // Two groups of eight warps; group g fills the stages of k blocks with (it & 1) == g.
+        // Inside a group, warp wi owns pixels [32*(wi&3), +32) of the tile (one per lane) and
+        // k columns [32*(wi>>2), +32) of the k block. k-dependent quantities are warp-uniform.
         const int pw = warp - 6;
-        const int mb = pw & 1;     // pixel block of 64 inside the tile
-        const int khalf = pw >> 1;  // which 32 of the k block's 64 columns
+        const int grp = pw >> 3, wi = pw & 7;
+        const int pq = wi & 3, khalf = wi >> 2;
         const int KHW = p.Kh * p.Kw;
+        const int plane = p.H * p.W;
+        int2* ktab = ktab_all + pw * 32;
+        // byte offset of this lane's pixel inside a 128-byte atom row is fixed:
+        // pixel m = 32*pq + lane -> 64-pixel block mb = pq >> 1, element e = 32*(pq&1) + lane,
+        // 16-byte chunk e >> 3, byte (e & 7) * 2
+        const int e = 32 * (pq & 1) + lane;
+        const uint32_t chunk = e >> 3, inchunk = (e & 7) * 2;
         uint32_t it = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
             const ConvTile t = decode_conv_tile(p, tile);
-            // this lane's two pixels
-            const int32_t p0 = t.mt * 128 + mb * 64 + 2 * lane, p1 = p0 + 1;
-            const bool v0 = p0 < p.HoWo, v1 = p1 < p.HoWo;
-            const int32_t h0 = (p0 / p.Wo) * p.stride - p.pad, w0 = (p0 % p.Wo) * p.stride - p.pad;
-            const int32_t h1 = (p1 / p.Wo) * p.stride - p.pad, w1 = (p1 % p.Wo) * p.stride - p.pad;
-            const float* xb = p.X + static_cast<int64_t>(t.img) * p.C * p.H * p.W;
+            const int32_t pix = t.mt * 128 + pq * 32 + lane;
+            const bool pv = pix < p.HoWo;
+            const int32_t ho = pix / p.Wo;
+            const int32_t h0 = ho * p.stride - p.pad, w0 = (pix - ho * p.Wo) * p.stride - p.pad;
+            // validity of every kernel row / column for this pixel, one bit each (Kh, Kw <= 31)
+            uint32_t vh = 0, vw = 0;
+            if (pv) {
+                for (int i = 0; i < p.Kh; i++) vh |= ((unsigned)(h0 + i) < (unsigned)p.H ? 1u : 0u) << i;
+                for (int i = 0; i < p.Kw; i++) vw |= ((unsigned)(w0 + i) < (unsigned)p.W ? 1u : 0u) << i;
+            }
+            const float* xb = p.X + static_cast<int64_t>(t.img) * p.C * plane + static_cast<int64_t>(h0) * p.W + w0;
             for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                if ((it & 1) != (uint32_t)grp) continue;
+                // lane j describes k column j of this warp's 32: element offset c*H*W + kh*W + kw and
+                // the (kh, kw) bit positions; columns past K point at bit 31, which is never set
+                {
+                    const int32_t k = kb * 64 + khalf * 32 + lane;
+                    const int32_t c = k / KHW;
+                    const int32_t r = k - c * KHW;
+                    const int32_t kh = r / p.Kw, kw = r - kh * p.Kw;
+                    const bool kin = k < p.K;
+                    ktab[lane] = make_int2(kin ? c * plane + kh * p.W + kw : 0, kin ? (kh | (kw << 8)) : (31 | (31 << 8)));
+                }
+                __syncwarp();
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                 if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
                     ok = false;
                     break;
                 }
-                uint8_t* sA = smem + s * Cfg::STAGE_BYTES + mb * 8192 + khalf * 4096;
-                int32_t k = kb * 64 + khalf * 32;
-                int32_t c = k / KHW;
-                int32_t r = k - c * KHW;
-                int32_t kh = r / p.Kw, kw = r - kh * p.Kw;
-#pragma unroll 1
-                for (int g = 0; g < 4; g++) {  // four 8-k groups
-                    float a0[8], a1[8];
+                uint8_t* sA = smem + s * Cfg::STAGE_BYTES + (pq >> 1) * 8192 + khalf * 4096;
+                float a[32];
 #pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const int32_t hh0 = h0 + kh, ww0 = w0 + kw, hh1 = h1 + kh, ww1 = w1 + kw;
-                        const bool kin = k < p.K;
-                        const float* src = xb + static_cast<int64_t>(c) * p.H * p.W;
-                        const bool in0 = kin && v0 && (unsigned)hh0 < (unsigned)p.H && (unsigned)ww0 < (unsigned)p.W;
-                        const bool in1 = kin && v1 && (unsigned)hh1 < (unsigned)p.H && (unsigned)ww1 < (unsigned)p.W;
-                        a0[j] = in0 ? __ldg(src + hh0 * p.W + ww0) : 0.f;
-                        a1[j] = in1 ? __ldg(src + hh1 * p.W + ww1) : 0.f;
-                        k++;
-                        if (++kw == p.Kw) {
-                            kw = 0;
-                            if (++kh == p.Kh) {
-                                kh = 0;
-                                c++;
-                            }
-                        }
-                    }
-                    uint8_t* atom = sA + g * 1024;
-#pragma unroll
-                    for (int j = 0; j < 8; j++) {
-                        const __half2 h = __floats2half2_rn(a0[j], a1[j]);
-                        const uint32_t off = j * 128 + ((((lane >> 2) ^ j) & 7) << 4) + ((lane & 3) << 2);
-                        *reinterpret_cast<__half2*>(atom + off) = h;
-                    }
+                for (int j = 0; j < 32; j += 2) {
+                    const int4 e2 = *reinterpret_cast<const int4*>(ktab + j);  // two entries, broadcast read
+                    const bool in0 = ((vh >> (e2.y & 0xff)) & (vw >> (e2.y >> 8)) & 1u) != 0;
+                    const bool in1 = ((vh >> (e2.w & 0xff)) & (vw >> (e2.w >> 8)) & 1u) != 0;
+                    a[j] = in0 ? __ldg(xb + e2.x) : 0.f;
+                    a[j + 1] = in1 ? __ldg(xb + e2.z) : 0.f;
                 }
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&full[s]);
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    // k column j of this half: 8-k group j >> 3 (1024-byte atom), row j & 7
+                    const uint32_t off = (j >> 3) * 1024 + (j & 7) * 128 + (((chunk ^ (j & 7)) & 7) << 4) + inchunk;
+                    *reinterpret_cast<__half*>(sA + off) = __float2half_rn(a[j]);
+                }
+                // All eight warps of the group have written their part of the stage: one thread then
+                // orders those generic-proxy writes before the tensor core's async-proxy reads and
+                // publishes the stage. (One proxy fence per stage instead of one per thread: the
+                // fence sits on the causality path between every write and the MMA that reads it.)
+                asm volatile("bar.sync %0, 256;" ::"r"(1 + grp) : "memory");
+                if (wi == 0 && lane == 0) {
+                    fence_proxy_async_smem();
+                    mbar_arrive(&full[s]);
+                }
             }
         }
     }
@@ -419,7 +456,7 @@ static int run_conv_cfg(const ConvRun& r, const __half* W16, int64_t Kp, int64_t
     }
     p.total_tiles = (int64_t)r.N * p.tiles_per_image * p.tiles_n;
     const int64_t grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
-    conv2d_igemm_tcgen05_kernel<Cfg><<<(unsigned)grid, 320, Cfg::SMEM_BYTES, stream>>>(tmW, p);
+    conv2d_igemm_tcgen05_kernel<Cfg><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, p);
     NZB_CUDA_TRY(cudaGetLastError());
     return NZB_OK;
 }
@@ -431,6 +468,7 @@ static int run_conv(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN,
     if (r.N <= 0 || r.Cout <= 0 || r.Ho <= 0 || r.Wo <= 0) return NZB_OK;
     if (r.Ho * r.Wo > INT32_MAX - 256 || r.C * r.Kh * r.Kw > INT32_MAX - 256 || r.C * r.H * r.W > INT32_MAX)
         return fail(NZB_ERR_UNSUPPORTED, "per-image extent exceeds 2^31");
+    if (r.Kh > 31 || r.Kw > 31) return fail(NZB_ERR_UNSUPPORTED, "kernel extent above 31");
     if (r.Cout > 128) return run_conv_cfg<ConvCfg<256, 4>>(r, W16, Kp, wN, *ds, stream);
     if (r.Cout > 64) return run_conv_cfg<ConvCfg<128, 6>>(r, W16, Kp, wN, *ds, stream);
     if (r.Cout > 32) return run_conv_cfg<ConvCfg<64, 8>>(r, W16, Kp, wN, *ds, stream);

@@ -62,6 +62,29 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     return true;
 }
 
+// Variant for roles that are not on the critical path: backs off with nanosleep so that idle
+// warps do not take issue slots from the warps doing the work.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    uint32_t spins = 0;
+    while (!mbar_try_wait(bar, parity)) {
+        __nanosleep(spins < 16 ? 40 : 200);
+        if ((++spins & 0x3f) == 0) {
+            if (*abort_flag) return false;
+            if (clock64() - t0 > kWaitCycleLimit) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ bool mbar_wait_relaxed_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    const bool ok = mbar_wait_relaxed(bar, parity, abort_flag);
+    return __all_sync(0xffffffffu, ok);
+}
+
 // Whole-warp form: all 32 lanes poll, and the warp agrees on the outcome so that control
 // flow stays warp-uniform (which lets the compiler keep addresses and descriptors in
 // uniform registers instead of moving them there for every tcgen05/TMA instruction).
