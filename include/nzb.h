@@ -207,6 +207,15 @@ NZB_API int nzb_conv2d_backward_data(const nzb_conv_desc* desc, const float* dy,
                                      void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * dw {wN,1,C*Kh*Kw,Cout} += gradient with respect to the weights, summed over the batch when
+ * the weights are shared: replaces transpose(col) + GEMMBackwardParallel (src/Nodes.cu:177-181,
+ * src/OperationKernels.cu:125-160, 1028-1144) over the materialised im2col buffer with two fp16
+ * staging passes and one split-k GEMM.
+ */
+NZB_API int nzb_conv2d_backward_weight(const nzb_conv_desc* desc, const float* x, const float* dy, float* dw,
+                                       void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * dbias {1,1,Ho*Wo,Cout} += sum over the batch of dy (AddNode::backward's gradCopy on the
  * bias after col2imgBackward, src/Nodes.cu:106-121, 660-665).
  */

@@ -373,6 +373,64 @@ __global__ void __launch_bounds__(256) flip_weights_kernel(__half* __restrict__ 
     }
 }
 
+// ---------------------------------------------------------------------------
+// Weight gradient staging. dW[k][co] += sum over (b, p) of col[b][p][k] * dy[b][co][p] is a GEMM
+// with a very long contraction (b, p); both operands are staged K-major in fp16:
+//   colT[k][bl*HoWo + p] = half(x[b0+bl][c][ho*s-pad+kh][wo*s-pad+kw])   (k = c*Kh*Kw + kh*Kw + kw)
+//   dyT [co][bl*HoWo + p] = half(dy[b0+bl][co][p])
+// and the split-k GEMM kernel does the rest. (The reference materialises the fp32 im2col
+// buffer, transposes it and runs GEMMBackwardParallel: src/Nodes.cu:177-181.)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) im2col_f16_kmajor_kernel(__half* __restrict__ out, const float* __restrict__ x,
+                                                                int64_t C, int64_t H, int64_t W, int64_t Kh, int64_t Kw,
+                                                                int64_t stride, int64_t pad, int64_t Ho, int64_t Wo,
+                                                                int64_t b0, int64_t nb, int64_t K, int64_t Qp) {
+    const int64_t HoWo = Ho * Wo, Q = nb * HoWo;
+    const int64_t pairs = (Q + 1) >> 1;
+    const int64_t total = K * pairs;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t k = i / pairs;
+        const int64_t q0 = (i - k * pairs) << 1;
+        const int64_t c = k / (Kh * Kw), r = k % (Kh * Kw);
+        const int64_t kh = r / Kw, kw = r % Kw;
+        float v[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int64_t q = q0 + j;
+            v[j] = 0.f;
+            if (q < Q) {
+                const int64_t bl = q / HoWo, pp = q - bl * HoWo;
+                const int64_t h = (pp / Wo) * stride - pad + kh, w = (pp % Wo) * stride - pad + kw;
+                if (h >= 0 && h < H && w >= 0 && w < W) v[j] = __ldg(x + (((b0 + bl) * C + c) * H + h) * W + w);
+            }
+        }
+        *reinterpret_cast<__half2*>(out + k * Qp + q0) = __floats2half2_rn(v[0], v[1]);
+    }
+}
+
+__global__ void __launch_bounds__(256) dy_f16_kmajor_kernel(__half* __restrict__ out, const float* __restrict__ dy,
+                                                            int64_t Cout, int64_t HoWo, int64_t b0, int64_t nb,
+                                                            int64_t Qp) {
+    const int64_t Q = nb * HoWo;
+    const int64_t pairs = (Q + 1) >> 1;
+    const int64_t total = Cout * pairs;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t co = i / pairs;
+        const int64_t q0 = (i - co * pairs) << 1;
+        float v[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int64_t q = q0 + j;
+            v[j] = 0.f;
+            if (q < Q) {
+                const int64_t bl = q / HoWo, pp = q - bl * HoWo;
+                v[j] = __ldg(dy + ((b0 + bl) * Cout + co) * HoWo + pp);
+            }
+        }
+        *reinterpret_cast<__half2*>(out + co * Qp + q0) = __floats2half2_rn(v[0], v[1]);
+    }
+}
+
 // dbias[p][co] += sum_b dy[b][co][p]   (AddNode::backward on the untied conv bias after
 // col2imgBackward; src/Nodes.cu:106-121, 660-665). Tiled transpose-reduce, coalesced both ways.
 __global__ void __launch_bounds__(256) conv_bias_grad_kernel(float* __restrict__ dbias, const float* __restrict__ dy,
@@ -489,6 +547,23 @@ static int check_conv_desc(const nzb_conv_desc* d, int64_t* Ho, int64_t* Wo) {
     return NZB_OK;
 }
 
+// Images per weight-gradient chunk and the staging bytes that chunk needs.
+static int64_t weight_grad_stage_bytes(const nzb_conv_desc* d, int64_t HoWo, int64_t* nb_out) {
+    const int64_t K = d->C * d->Kh * d->Kw;
+    const int64_t per_image = (K + d->Cout) * round_up(HoWo, 64) * 2;
+    const int64_t budget = int64_t(2) << 30;
+    int64_t nb = 1;
+    if (!d->weights_per_sample && d->N > 1) {
+        int64_t nb_max = budget / (per_image > 0 ? per_image : 1);
+        if (nb_max < 1) nb_max = 1;
+        const int64_t chunks = (d->N + nb_max - 1) / nb_max;
+        nb = (d->N + chunks - 1) / chunks;
+    }
+    if (nb_out) *nb_out = nb;
+    const int64_t Qp = round_up(nb * HoWo, 64);
+    return round_up(K * Qp * 2, 256) + round_up(d->Cout * Qp * 2, 256);
+}
+
 }  // namespace nzb
 
 using namespace nzb;
@@ -504,7 +579,10 @@ int nzb_conv2d_workspace_bytes(const nzb_conv_desc* d, size_t* bytes_out) {
     const int64_t Kf = round_up(d->C * d->Kh * d->Kw, kOperandKAlign);      // forward: [Cout][Kf]
     const int64_t Kb = round_up(d->Cout * d->Kh * d->Kw, kOperandKAlign);   // backward data: [C][Kb]
     const int64_t f = wN * d->Cout * Kf * 2, b = wN * d->C * Kb * 2;
-    *bytes_out = (size_t)round_up(f > b ? f : b, 256);
+    const int64_t g = weight_grad_stage_bytes(d, Ho * Wo, nullptr);
+    int64_t m = f > b ? f : b;
+    if (g > m) m = g;
+    *bytes_out = (size_t)round_up(m, 256);
     return NZB_OK;
 }
 
@@ -564,6 +642,53 @@ int nzb_conv2d_backward_data(const nzb_conv_desc* d, const float* dy, const floa
     ConvRun r{dy, dx, nullptr, d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, 1, d->Kh - 1 - d->pad, d->H, d->W,
               d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, 1, 0};
     return run_conv(r, W16, Kp2, wN, s);
+}
+
+int nzb_conv2d_backward_weight(const nzb_conv_desc* d, const float* x, const float* dy, float* dw, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+    int64_t Ho, Wo;
+    int rc = check_conv_desc(d, &Ho, &Wo);
+    if (rc != NZB_OK) return rc;
+    if (d->N == 0) return NZB_OK;
+    if (!x || !dy || !dw) return fail(NZB_ERR_BAD_ARG, "x, dy and dw must be non-null");
+    size_t need;
+    nzb_conv2d_workspace_bytes(d, &need);
+    if (!workspace || workspace_bytes < need) return fail(NZB_ERR_WORKSPACE, "workspace of %zu bytes needed", need);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(NZB_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    DeviceState* ds;
+    rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t HoWo = Ho * Wo, K = d->C * d->Kh * d->Kw;
+    int64_t nb;
+    weight_grad_stage_bytes(d, HoWo, &nb);
+    if (nb * HoWo > INT32_MAX - 256) return fail(NZB_ERR_UNSUPPORTED, "contraction length exceeds 2^31");
+    for (int64_t b0 = 0; b0 < d->N; b0 += nb) {
+        const int64_t n = (d->N - b0 < nb) ? d->N - b0 : nb;
+        const int64_t Q = n * HoWo, Qp = round_up(Q, 64);
+        __half* colT = reinterpret_cast<__half*>(workspace);
+        __half* dyT = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(workspace) + round_up(K * Qp * 2, 256));
+        const int64_t cap = (int64_t)ds->sm_count * 32;
+        int64_t t1 = K * ((Q + 1) / 2), t2 = d->Cout * ((Q + 1) / 2);
+        int64_t g1 = (t1 + 255) / 256, g2 = (t2 + 255) / 256;
+        if (g1 > cap) g1 = cap;
+        if (g2 > cap) g2 = cap;
+        im2col_f16_kmajor_kernel<<<(unsigned)g1, 256, 0, s>>>(colT, x, d->C, d->H, d->W, d->Kh, d->Kw, d->stride,
+                                                             d->pad, Ho, Wo, b0, n, K, Qp);
+        NZB_CUDA_TRY(cudaGetLastError());
+        dy_f16_kmajor_kernel<<<(unsigned)g2, 256, 0, s>>>(dyT, dy, d->Cout, HoWo, b0, n, Qp);
+        NZB_CUDA_TRY(cudaGetLastError());
+        GemmLaunch g{};
+        g.A16 = colT; g.B16 = dyT; g.nA = 1; g.nB = 1;
+        g.M = K; g.N = d->Cout; g.K = Q; g.Kp = Qp;
+        g.C = dw + (d->weights_per_sample ? b0 * K * d->Cout : 0);
+        g.ldc = d->Cout;
+        g.out_e[0] = g.out_e[1] = 1; g.red_e[0] = g.red_e[1] = 1;
+        g.accumulate = 1;
+        rc = launch_gemm(g, s);
+        if (rc != NZB_OK) return rc;
+    }
+    return NZB_OK;
 }
 
 int nzb_conv2d_backward_bias(const nzb_conv_desc* d, const float* dy, float* dbias, void* stream) {

@@ -35,6 +35,7 @@ struct GemmParams {
     int32_t last_ksteps;  // 16-wide MMA steps in the last k block (1..4)
     int32_t vec4;         // C (and bias) allow aligned float4 access
     int32_t group_m;      // m-tiles per rasterisation group
+    int32_t splits;       // CTAs sharing one output tile along the contraction (results added atomically)
     int64_t total_tiles;
     int* status;
 };
@@ -154,6 +155,10 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
                 if (gr < p.M && gc < p.N) {
                     float x = stage[r * Cfg::EPI_STRIDE + cl];
                     float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
+                    if (p.splits > 1) {
+                        atomicAdd(cp, x);  // partial sum of one k slice; C was zeroed or holds the addend
+                        continue;
+                    }
                     if (p.accumulate) x += *cp;
                     if (p.bias_mode == NZB_BIAS_ROW) x += p.bias[gc];
                     else if (p.bias_mode == NZB_BIAS_COL) x += p.bias[gr];
@@ -213,30 +218,40 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 
     const int32_t k_iters = p.red_e0 * p.red_e1 * p.k_blocks;  // per tile
 
+    const int64_t total_items = p.total_tiles * p.splits;
     if (warp == 0) {
         // ---------------- TMA producer (whole warp waits, one elected lane issues) ----------------
         uint32_t it = 0;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-            const TileCoord t = decode_tile(p, tile);
-            for (int32_t r0 = 0; r0 < p.red_e0 && ok; r0++) {
-                for (int32_t r1 = 0; r1 < p.red_e1 && ok; r1++) {
-                    const int32_t i0 = t.b0 + r0, i1 = t.b1 + r1;
-                    const int32_t za = i0 * p.a_mul0 + i1 * p.a_mul1;
-                    const int32_t zb = i0 * p.b_mul0 + i1 * p.b_mul1;
-                    for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
-                        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                        if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
-                            ok = false;
-                            break;
-                        }
-                        if (elect_one()) {
-                            uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
-                            mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
-                            tma_load_3d(sa, &tmA, kb * 64, t.mt * 128, za, &full[s]);
-                            tma_load_3d(sa + Cfg::A_BYTES, &tmB, kb * 64, t.nt * BN, zb, &full[s]);
-                        }
-                        __syncwarp();
+        for (int64_t item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            const TileCoord t = decode_tile(p, item / p.splits);
+            const int32_t split = static_cast<int32_t>(item % p.splits);
+            const int32_t kk0 = static_cast<int32_t>(static_cast<int64_t>(k_iters) * split / p.splits);
+            const int32_t kk1 = static_cast<int32_t>(static_cast<int64_t>(k_iters) * (split + 1) / p.splits);
+            int32_t kb = kk0 % p.k_blocks;
+            int32_t r = kk0 / p.k_blocks;
+            int32_t r1 = r % p.red_e1, r0 = r / p.red_e1;
+            for (int32_t kk = kk0; kk < kk1; kk++, it++) {
+                const int32_t i0 = t.b0 + r0, i1 = t.b1 + r1;
+                const int32_t za = i0 * p.a_mul0 + i1 * p.a_mul1;
+                const int32_t zb = i0 * p.b_mul0 + i1 * p.b_mul1;
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
+                    mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
+                    tma_load_3d(sa, &tmA, kb * 64, t.mt * 128, za, &full[s]);
+                    tma_load_3d(sa + Cfg::A_BYTES, &tmB, kb * 64, t.nt * BN, zb, &full[s]);
+                }
+                __syncwarp();
+                if (++kb == p.k_blocks) {
+                    kb = 0;
+                    if (++r1 == p.red_e1) {
+                        r1 = 0;
+                        r0++;
                     }
                 }
             }
@@ -244,8 +259,8 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         if (!ok && lane == 0) {
             // Wait (bounded) for the copies still in flight so none lands after exit.
             const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
+            const long long t0 = clock64();
             for (uint32_t j = first; j < it; j++) {
-                const long long t0 = clock64();
                 while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1)) {
                     if (clock64() - t0 > kWaitCycleLimit) break;
                 }
@@ -256,13 +271,16 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         constexpr uint32_t idesc = make_idesc_f16_f32(128, BN);
         uint32_t it = 0, tcount = 0;
         bool ok = true;
-        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, tcount++) {
+        for (int64_t item = blockIdx.x; item < total_items && ok; item += gridDim.x, tcount++) {
+            const int32_t split = static_cast<int32_t>(item % p.splits);
+            const int32_t kk0 = static_cast<int32_t>(static_cast<int64_t>(k_iters) * split / p.splits);
+            const int32_t kk1 = static_cast<int32_t>(static_cast<int64_t>(k_iters) * (split + 1) / p.splits);
             const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
             if (!mbar_wait_warp(&tempty[acc], aph ^ 1, abort_flag)) break;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + acc * BN;
-            int32_t kb = 0;
-            for (int32_t kk = 0; kk < k_iters; kk++, it++) {
+            int32_t kb = kk0 % p.k_blocks;
+            for (int32_t kk = kk0; kk < kk1; kk++, it++) {
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                 if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
                     ok = false;
@@ -276,7 +294,7 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 if (++kb == p.k_blocks) kb = 0;
                 if (elect_one()) {
                     // one k step = 16 halves = 32 bytes = 2 descriptor address units
-                    mma_f16_ss(d_tmem, da, db, idesc, kk > 0 ? 1u : 0u);
+                    mma_f16_ss(d_tmem, da, db, idesc, kk > kk0 ? 1u : 0u);
                     if (ksteps > 1) mma_f16_ss(d_tmem, da + 2, db + 2, idesc, 1u);
                     if (ksteps > 2) mma_f16_ss(d_tmem, da + 4, db + 4, idesc, 1u);
                     if (ksteps > 3) mma_f16_ss(d_tmem, da + 6, db + 6, idesc, 1u);
@@ -292,8 +310,8 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         const int q = warp & 3;  // tensor-memory lane quarter this warp may read
         float* stage = epi + (warp - 2) * 32 * Cfg::EPI_STRIDE;
         uint32_t tcount = 0;
-        for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, tcount++) {
-            const TileCoord t = decode_tile(p, tile);
+        for (int64_t item = blockIdx.x; item < total_items; item += gridDim.x, tcount++) {
+            const TileCoord t = decode_tile(p, item / p.splits);
             const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
             if (!mbar_wait_bounded(&tfull[acc], aph, abort_flag)) break;
             tc_fence_after();
@@ -536,7 +554,27 @@ static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds,
                                           Cfg::SMEM_BYTES));
         attr_set = true;
     }
-    const int64_t grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
+    // Few output tiles but a long contraction: share each tile among several CTAs along k and
+    // add the partial sums atomically (only without bias / ReLU, which need the full sum).
+    p.splits = 1;
+    const int64_t k_iters = (int64_t)p.red_e0 * p.red_e1 * p.k_blocks;
+    if (p.total_tiles * 2 <= ds.sm_count && k_iters >= 16 && p.bias_mode == NZB_BIAS_NONE && !p.relu) {
+        int64_t sp = ds.sm_count / p.total_tiles;
+        if (sp > k_iters / 8) sp = k_iters / 8;
+        if (sp > 1) {
+            p.splits = (int32_t)sp;
+            p.vec4 = 0;
+            if (!p.accumulate) {
+                // partial sums are added into C: start from zero
+                for (int32_t b0 = 0; b0 < p.out_e0; b0++)
+                    for (int32_t b1 = 0; b1 < p.out_e1; b1++)
+                        NZB_CUDA_TRY(cudaMemset2DAsync(p.C + b0 * p.c_stride0 + b1 * p.c_stride1, (size_t)p.ldc * 4, 0,
+                                                       (size_t)p.N * 4, (size_t)p.M, stream));
+            }
+        }
+    }
+    const int64_t items = p.total_tiles * p.splits;
+    const int64_t grid = items < ds.sm_count ? items : ds.sm_count;
     gemm_f16_tcgen05_kernel<Cfg><<<(unsigned)grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
     NZB_CUDA_TRY(cudaGetLastError());
     return NZB_OK;
@@ -552,6 +590,7 @@ static int launch_pair(const GemmLaunch& g, GemmParams& p, const DeviceState& ds
     p.tiles_m = (int32_t)((g.M + 255) / 256);
     p.tiles_n = (int32_t)((g.N + 255) / 256);
     p.group_m = 8;
+    p.splits = 1;
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * p.out_e0 * p.out_e1;
     static bool attr_set = false;
     if (!attr_set) {
@@ -609,7 +648,13 @@ int launch_gemm_on(const GemmLaunch& g, const DeviceState& dstate, cudaStream_t 
     p.vec4 = v4 ? 1 : 0;
     p.group_m = 16;
 
-    if (g.N > 128 && g.M > 128 && !g.force_single_cta) return launch_pair(g, p, *ds, stream);
+    {
+        // few tiles and a long contraction: the single-CTA kernel can split k across CTAs
+        const int64_t tiles1 = (int64_t)p.tiles_m * ((g.N + 255) / 256) * p.out_e0 * p.out_e1;
+        const int64_t k_iters = (int64_t)p.red_e0 * p.red_e1 * p.k_blocks;
+        const bool want_split = tiles1 * 2 <= ds->sm_count && k_iters >= 64 && p.bias_mode == NZB_BIAS_NONE && !p.relu;
+        if (g.N > 128 && g.M > 128 && !g.force_single_cta && !want_split) return launch_pair(g, p, *ds, stream);
+    }
 
     if (g.N > 128) return launch_cfg<GemmCfg<256, 4>>(g, p, *ds, stream);
     if (g.N > 64) return launch_cfg<GemmCfg<128, 6>>(g, p, *ds, stream);

@@ -162,6 +162,16 @@ def conv2d_backward_data(dy, w, x_shape, Kh, Kw, stride, pad, dx):
     return dx
 
 
+def conv2d_backward_weight(x, dy, w_shape, Kh, Kw, stride, pad, dw):
+    """dw += d(conv)/dw, summed over the batch for shared weights."""
+    _check_f32_cuda(x, dy, dw)
+    d = _conv_desc(x.shape, w_shape, Kh, Kw, stride, pad)
+    ws = _conv_ws(d, x.device)
+    C.check(C.lib().nzb_conv2d_backward_weight(ctypes.byref(d), _ptr(x), _ptr(dy), _ptr(dw), _ptr(ws), ws.numel(),
+                                               _stream()))
+    return dw
+
+
 def conv2d_backward_bias(dy, x_shape, w_shape, Kh, Kw, stride, pad, dbias):
     _check_f32_cuda(dy, dbias)
     d = _conv_desc(x_shape, w_shape, Kh, Kw, stride, pad)

@@ -83,3 +83,21 @@ def test_conv_backward_data_and_bias(nz, n, c, h, w, co, k, s, p, per_sample):
     assert nz.device_status() == 0
     assert emax(dx.cpu().numpy() - dx0, dx_ref) <= 5e-5  # accumulated onto dx0: one extra fp32 rounding
     assert emax(db.cpu().numpy() - db0, db_ref) <= 5e-6
+
+
+@pytest.mark.parametrize("n,c,h,w,co,k,s,p,per_sample", CASES)
+def test_conv_backward_weight(nz, n, c, h, w, co, k, s, p, per_sample):
+    rng = np.random.default_rng(n * 11 + c * 5 + co)
+    x = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)
+    wn = n if per_sample else 1
+    wshape = (wn, 1, c * k * k, co)
+    wt = rng.normal(0, 1, wshape).astype(np.float32)
+    ho, wo = O.conv_out_hw(h, w, k, k, s, p)
+    dy = rng.normal(0, 1, (n, co, ho, wo)).astype(np.float32)
+    _, dw_ref, _ = O.conv2d_backward(dy, x, wt, k, k, s, p, want_dx=False, want_db=False)
+    dw0 = rng.normal(0, 1, wshape).astype(np.float32)
+    dw = dev(dw0)
+    nz.conv2d_backward_weight(dev(x), dev(dy), wshape, k, k, s, p, dw)
+    torch.cuda.synchronize()
+    assert nz.device_status() == 0
+    assert emax(dw.cpu().numpy() - dw0, dw_ref) <= 5e-5

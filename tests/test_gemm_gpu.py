@@ -175,6 +175,34 @@ def test_batched_backward_accumulate_and_reduce(nz, sa, sb, sc):
     assert emax(out.cpu().numpy(), ref) <= TOL_ROUNDED
 
 
+@pytest.mark.parametrize("M,N,K,acc", [(16, 24, 20000, False), (100, 300, 9000, False), (200, 130, 30000, True),
+                                       (576, 128, 12544, True), (1, 16, 70000, False)])
+def test_split_k_long_contraction(nz, M, N, K, acc):
+    """Few output tiles and a long contraction: k is split across CTAs and partial sums are added
+    with fp32 atomics (as the reference's CuttingAndCompress does), so only the tolerance applies."""
+    rng = np.random.default_rng(M + N + K)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    c0 = rng.uniform(-1, 1, (M, N)).astype(np.float32) if acc else np.zeros((M, N), np.float32)
+    out = dev(c0) if acc else torch.full((M, N), float("nan"), device="cuda")
+    nz.gemm(dev(A), dev(B), out=out, accumulate=acc)
+    check_status(nz)
+    assert emax(out.cpu().numpy(), O.gemm_f64(A, B, True) + c0) <= TOL_ROUNDED
+
+
+def test_split_k_with_batch_reduction(nz):
+    rng = np.random.default_rng(77)
+    A = rng.uniform(-1, 1, (6, 1, 40, 3000)).astype(np.float32)
+    B = rng.uniform(-1, 1, (6, 1, 3000, 24)).astype(np.float32)
+    C0 = rng.uniform(-1, 1, (1, 1, 40, 24)).astype(np.float32)
+    ref = C0.astype(np.float64)
+    O.gemm_backward(A, B, ref, True)
+    out = dev(C0)
+    nz.gemm_backward(dev(A), dev(B), out)
+    check_status(nz)
+    assert emax(out.cpu().numpy(), ref) <= TOL_ROUNDED
+
+
 def test_cast_matches_oracle_bits(nz):
     rng = np.random.default_rng(5)
     x = np.concatenate([rng.uniform(-1, 1, 3000), rng.normal(0, 300, 3000), rng.uniform(-1e-5, 1e-5, 2000),
