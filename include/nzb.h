@@ -167,6 +167,34 @@ NZB_API int nzb_gemm_f16(const nzb_gemm_desc* desc, const void* A16, const void*
 NZB_API int nzb_cast_f32_f16(const float* in, void* out_f16, int64_t rows, int64_t cols, int64_t ld_in,
                              int64_t ld_out, int transpose, void* stream);
 
+/* Linear ----------------------------------------------------------------------------------- */
+
+/*
+ * Linear layer as Model::Linear composes it (src/Model.cu:87-103): x {batch, in}, w {out, in}
+ * (the reference's {1,1,out,in}), bias {out} ({1,1,out,1}), y {batch, out} (the reference's
+ * {batch,1,out,1}); relu applies max(.,0) (a following ReLUNode, src/Nodes.cu:344-364).
+ * One GEMM instead of one padded matrix-vector product per sample
+ * (src/OperationKernels.cu:977-999).
+ */
+typedef struct nzb_linear_desc {
+    int64_t batch, in_features, out_features;
+    int32_t relu;
+    int32_t reserved;
+} nzb_linear_desc;
+
+NZB_API int nzb_linear_workspace_bytes(const nzb_linear_desc* desc, size_t* bytes_out);
+NZB_API int nzb_linear_forward(const nzb_linear_desc* desc, const float* x, const float* w, const float* bias,
+                               float* y, void* workspace, size_t workspace_bytes, void* stream);
+/*
+ * Backward of the same composition (ReLUNode::backward -> AddNode::backward ->
+ * MatMulNode::backward, src/Nodes.cu:356-364, 99-146, 169-182) without the two transposes and
+ * the per-sample launches: dx += dy' w, dw += dy'^T x, dbias += column sums of dy', with
+ * dy' = dy * (y > 0) when relu is set (y is the forward output). Null outputs are skipped.
+ */
+NZB_API int nzb_linear_backward(const nzb_linear_desc* desc, const float* x, const float* w, const float* y,
+                                const float* dy, float* dx, float* dw, float* dbias, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
 /* Convolution ------------------------------------------------------------------------------ */
 
 /*

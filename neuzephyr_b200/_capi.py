@@ -14,6 +14,7 @@ EXPORTS = [
     "nzb_version", "nzb_last_error_string", "nzb_device_status", "nzb_device_status_reset",
     "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_gemm_f16", "nzb_gemm_static", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
     "nzb_gemm_backward", "nzb_cast_f32_f16",
+    "nzb_linear_workspace_bytes", "nzb_linear_forward", "nzb_linear_backward",
     "nzb_conv2d_workspace_bytes", "nzb_conv2d_forward", "nzb_conv2d_backward_data", "nzb_conv2d_backward_weight",
     "nzb_conv2d_backward_bias",
     "nzb_img2col", "nzb_img2col_backward", "nzb_col2img", "nzb_col2img_backward", "nzb_add_broadcast",
@@ -40,6 +41,12 @@ class ConvDesc(ctypes.Structure):
     """struct nzb_conv_desc"""
     _fields_ = [(n, ctypes.c_int64) for n in ("N", "C", "H", "W", "Cout", "Kh", "Kw", "stride", "pad")] + \
                [(n, ctypes.c_int32) for n in ("weights_per_sample", "bias_mode", "relu", "accumulate")]
+
+
+class LinearDesc(ctypes.Structure):
+    """struct nzb_linear_desc"""
+    _fields_ = [("batch", ctypes.c_int64), ("in_features", ctypes.c_int64), ("out_features", ctypes.c_int64),
+                ("relu", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
 class NzbError(RuntimeError):
@@ -72,6 +79,10 @@ def lib():
                                        ctypes.c_int, vp]
         L.nzb_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
         i64, f32, ci = ctypes.c_int64, ctypes.c_float, ctypes.c_int
+        ld = ctypes.POINTER(LinearDesc)
+        L.nzb_linear_workspace_bytes.argtypes = [ld, ctypes.POINTER(sz)]
+        L.nzb_linear_forward.argtypes = [ld, vp, vp, vp, vp, vp, sz, vp]
+        L.nzb_linear_backward.argtypes = [ld, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
         cd = ctypes.POINTER(ConvDesc)
         L.nzb_conv2d_workspace_bytes.argtypes = [cd, ctypes.POINTER(sz)]
         L.nzb_conv2d_forward.argtypes = [cd, vp, vp, vp, vp, vp, sz, vp]

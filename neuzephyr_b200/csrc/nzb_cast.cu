@@ -16,6 +16,7 @@ struct CastParams {
     int64_t nmat1;  // extent of the inner batch dimension
     int64_t in_stride0, in_stride1;
     int64_t nmat;  // total matrices
+    const float* mask;  // optional, same layout as `in`: elements whose mask value is <= 0 are staged as 0
 };
 
 // Row-preserving cast. One thread produces 8 consecutive halves (one 16-byte store).
@@ -37,9 +38,22 @@ __global__ void __launch_bounds__(256) cast_rows_kernel(const CastParams p) {
             const float4 b = __ldg(reinterpret_cast<const float4*>(src + c + 4));
             v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
             v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+            if (p.mask) {
+                const float* mk = p.mask + (src - p.in);
+                const float4 ma = __ldg(reinterpret_cast<const float4*>(mk + c));
+                const float4 mb = __ldg(reinterpret_cast<const float4*>(mk + c + 4));
+                v[0] = ma.x > 0.f ? v[0] : 0.f; v[1] = ma.y > 0.f ? v[1] : 0.f;
+                v[2] = ma.z > 0.f ? v[2] : 0.f; v[3] = ma.w > 0.f ? v[3] : 0.f;
+                v[4] = mb.x > 0.f ? v[4] : 0.f; v[5] = mb.y > 0.f ? v[5] : 0.f;
+                v[6] = mb.z > 0.f ? v[6] : 0.f; v[7] = mb.w > 0.f ? v[7] : 0.f;
+            }
         } else {
+            const float* mk = p.mask ? p.mask + (src - p.in) : nullptr;
 #pragma unroll
-            for (int j = 0; j < 8; j++) v[j] = (c + j < p.cols) ? __ldg(src + c + j) : 0.f;
+            for (int j = 0; j < 8; j++) {
+                v[j] = (c + j < p.cols) ? __ldg(src + c + j) : 0.f;
+                if (mk && c + j < p.cols && !(__ldg(mk + c + j) > 0.f)) v[j] = 0.f;
+            }
         }
         uint4 o;
         __half2 h;
@@ -66,12 +80,15 @@ __global__ void __launch_bounds__(256) cast_transpose_kernel(const CastParams p)
         const int64_t tr = tm % tiles_r;
         const int64_t mat = tm / tiles_r;
         const float* src = p.in + (mat / p.nmat1) * p.in_stride0 + (mat % p.nmat1) * p.in_stride1;
+        const float* mk = p.mask ? p.mask + (src - p.in) : nullptr;
         const int64_t r0 = tr << 6, c0 = tc << 6;
 #pragma unroll
         for (int i = 0; i < 16; i++) {
             const int cl = i * 4 + ty;
             const int64_t c = c0 + cl, r = r0 + tx;
-            tile[cl][tx] = (c < p.cols && r < p.rows) ? __ldg(src + c * p.ld_in + r) : 0.f;
+            float v = (c < p.cols && r < p.rows) ? __ldg(src + c * p.ld_in + r) : 0.f;
+            if (mk && c < p.cols && r < p.rows && !(__ldg(mk + c * p.ld_in + r) > 0.f)) v = 0.f;
+            tile[cl][tx] = v;
         }
         __syncthreads();
         __half* dst = p.out + mat * p.rows * p.ld_out;
@@ -103,14 +120,24 @@ int launch_cast_on(int sm_count, const float* in, __half* out, int64_t rows, int
                    int64_t in_stride1, cudaStream_t stream) {
     if (rows <= 0 || nmat0 <= 0 || nmat1 <= 0) return NZB_OK;
     if (ld_out % 64 != 0 || ld_out < cols) return fail(NZB_ERR_BAD_ARG, "fp16 leading dimension must be a multiple of 64 and >= cols");
-    CastParams p{in, out, rows, cols, ld_in, ld_out, nmat1, in_stride0, in_stride1, nmat0 * nmat1};
+    return launch_cast_masked(sm_count, in, nullptr, out, rows, cols, ld_in, ld_out, transpose, nmat0, nmat1, in_stride0,
+                              in_stride1, stream);
+}
+
+int launch_cast_masked(int sm_count, const float* in, const float* mask, __half* out, int64_t rows, int64_t cols,
+                       int64_t ld_in, int64_t ld_out, int transpose, int64_t nmat0, int64_t nmat1, int64_t in_stride0,
+                       int64_t in_stride1, cudaStream_t stream) {
+    if (rows <= 0 || nmat0 <= 0 || nmat1 <= 0) return NZB_OK;
+    if (ld_out % 64 != 0 || ld_out < cols) return fail(NZB_ERR_BAD_ARG, "fp16 leading dimension must be a multiple of 64 and >= cols");
+    CastParams p{in, out, rows, cols, ld_in, ld_out, nmat1, in_stride0, in_stride1, nmat0 * nmat1, mask};
     if (!transpose) {
         const int64_t total = p.nmat * rows * (ld_out >> 3);
         int64_t blocks = (total + 255) / 256;
         const int64_t cap = (int64_t)sm_count * 16;
         if (blocks > cap) blocks = cap;
         const bool vec = (ld_in % 4 == 0) && (in_stride0 % 4 == 0) && (in_stride1 % 4 == 0) &&
-                         ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+                         ((reinterpret_cast<uintptr_t>(in) & 15) == 0) &&
+                         (!mask || (reinterpret_cast<uintptr_t>(mask) & 15) == 0);
         if (vec) cast_rows_kernel<true><<<(unsigned)blocks, 256, 0, stream>>>(p);
         else cast_rows_kernel<false><<<(unsigned)blocks, 256, 0, stream>>>(p);
     } else {

@@ -75,6 +75,12 @@ int launch_cast_on(int sm_count, const float* in, __half* out, int64_t rows, int
                    int64_t ld_out, int transpose, int64_t nmat0, int64_t nmat1, int64_t in_stride0,
                    int64_t in_stride1, cudaStream_t stream);
 
+// The same staging pass with an optional mask (same layout as `in`): elements whose mask value is
+// not > 0 are staged as zero, which folds ReLU's backward into the operand copy.
+int launch_cast_masked(int sm_count, const float* in, const float* mask, __half* out, int64_t rows, int64_t cols,
+                       int64_t ld_in, int64_t ld_out, int transpose, int64_t nmat0, int64_t nmat1, int64_t in_stride0,
+                       int64_t in_stride1, cudaStream_t stream);
+
 // Resolved view of a descriptor (nzb_api.cu).
 struct Plan {
     int64_t M, N, K, Kp;

@@ -177,3 +177,36 @@ def conv2d_backward_bias(dy, x_shape, w_shape, Kh, Kw, stride, pad, dbias):
     d = _conv_desc(x_shape, w_shape, Kh, Kw, stride, pad)
     C.check(C.lib().nzb_conv2d_backward_bias(ctypes.byref(d), _ptr(dy), _ptr(dbias), _stream()))
     return dbias
+
+
+def _linear_desc(batch, fin, fout, relu):
+    d = C.LinearDesc()
+    d.batch, d.in_features, d.out_features, d.relu = batch, fin, fout, int(relu)
+    return d
+
+
+def _linear_ws(d, device):
+    n = ctypes.c_size_t(0)
+    C.check(C.lib().nzb_linear_workspace_bytes(ctypes.byref(d), ctypes.byref(n)))
+    return _workspace(n.value, device)
+
+
+def linear_forward(x, w, bias=None, relu=False, out=None):
+    """y[b][o] = relu(sum_i w[o][i] x[b][i] + bias[o]); x {B,in}, w {out,in}."""
+    _check_f32_cuda(x, w, bias, out)
+    d = _linear_desc(x.shape[0], x.shape[1], w.shape[0], relu)
+    if out is None:
+        out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+    ws = _linear_ws(d, x.device)
+    C.check(C.lib().nzb_linear_forward(ctypes.byref(d), _ptr(x), _ptr(w), _ptr(bias), _ptr(out), _ptr(ws),
+                                       ws.numel(), _stream()))
+    return out
+
+
+def linear_backward(x, w, y, dy, dx=None, dw=None, dbias=None, relu=False):
+    """dx += dy' w, dw += dy'^T x, dbias += colsum(dy'), dy' = dy * (y > 0) if relu."""
+    _check_f32_cuda(x, w, y, dy, dx, dw, dbias)
+    d = _linear_desc(x.shape[0], x.shape[1], w.shape[0], relu)
+    ws = _linear_ws(d, x.device)
+    C.check(C.lib().nzb_linear_backward(ctypes.byref(d), _ptr(x), _ptr(w), _ptr(y), _ptr(dy), _ptr(dx), _ptr(dw),
+                                        _ptr(dbias), _ptr(ws), ws.numel(), _stream()))
