@@ -26,11 +26,65 @@ def _stale():
     return any(os.path.getmtime(os.path.join(CSRC, f)) > t for f in SOURCES + HEADERS)
 
 
+HOST = os.path.join(HERE, "host")
+HOST_LIB = os.path.join(HERE, "libneuzephyr_host.so")
+HOST_SOURCES = ["Runtime.cpp", "Ops.cpp", "Nodes.cpp", "Graph.cpp", "DataParallel.cpp"]
+CXX = "/usr/bin/g++"
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+
+
+def _host_stale():
+    if not os.path.exists(HOST_LIB):
+        return True
+    t = os.path.getmtime(HOST_LIB)
+    files = [os.path.join(HOST, "src", f) for f in HOST_SOURCES]
+    inc = os.path.join(HOST, "include", "NeuZephyr")
+    files += [os.path.join(inc, f) for f in os.listdir(inc)] + [os.path.join(HERE, "..", "include", "nzb.h")]
+    return any(os.path.getmtime(f) > t for f in files)
+
+
+def host_flags():
+    """Compiler flags a program needs to use the C++ host layer (nz:: API) and libnzb."""
+    return ["-std=c++17", "-O2", "-I" + os.path.join(HOST, "include"), "-I" + os.path.join(HERE, "..", "include"),
+            "-I" + os.path.join(CUDA_HOME, "include")]
+
+
+def host_link_flags(origin_relative=None):
+    """Linker flags for a program using the host layer. origin_relative: path from the program's
+    directory to this package, embedded as an $ORIGIN rpath so the program finds the libraries
+    wherever the tree is copied."""
+    flags = ["-L" + HERE, "-lneuzephyr_host", "-lnzb", "-L" + os.path.join(CUDA_HOME, "lib64"), "-lcudart", "-lnccl",
+             "-Wl,-rpath," + os.path.join(CUDA_HOME, "lib64"), "-lpthread"]
+    flags.append("-Wl,-rpath," + ("$ORIGIN/" + origin_relative if origin_relative else HERE))
+    return flags
+
+
+def build_program(source, output, origin_relative):
+    """Compiles one C++ program against the host layer (used for the C++ tests and tools)."""
+    os.makedirs(os.path.dirname(output), exist_ok=True)
+    if os.path.exists(output) and os.path.getmtime(output) > max(os.path.getmtime(source), os.path.getmtime(HOST_LIB)):
+        return output
+    subprocess.check_call([CXX] + host_flags() + [source, "-o", output] + host_link_flags(origin_relative))
+    return output
+
+
+def build_host(force=False):
+    """Compiles the C++ host layer (nz:: mirror of NeuZephyr's API) into libneuzephyr_host.so."""
+    if not force and not _host_stale():
+        return HOST_LIB
+    cmd = [CXX] + host_flags() + ["-fPIC", "-shared", "-o", HOST_LIB] + \
+        [os.path.join(HOST, "src", f) for f in HOST_SOURCES] + \
+        ["-L" + HERE, "-lnzb", "-L" + os.path.join(CUDA_HOME, "lib64"), "-lcudart", "-lnccl",
+         "-Wl,-rpath,$ORIGIN", "-Wl,-rpath," + os.path.join(CUDA_HOME, "lib64")]
+    subprocess.check_call(cmd)
+    return HOST_LIB
+
+
 def build(force=False, verbose=False):
-    if not force and not _stale():
-        return LIB
-    cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + SOURCES
-    subprocess.check_call(cmd, cwd=CSRC)
+    if force or _stale():
+        cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + SOURCES
+        subprocess.check_call(cmd, cwd=CSRC)
+    build_host(force)
     return LIB
 
 

@@ -1,0 +1,40 @@
+// nz::graph::ComputeGraph: node container, Kahn topological sort, forward / backward /
+// update / zeroGrad loops (mirrors include/NeuZephyr/ComputeGraph.cuh,
+// src/ComputeGraph.cu:258-296, 405-438, 541-547). Serialisation is not part of this path.
+#pragma once
+#include <functional>
+#include <vector>
+
+#include "Nodes.cuh"
+#include "Optimizer.cuh"
+
+namespace nz::graph {
+
+class ComputeGraph {
+public:
+    ComputeGraph() = default;
+    bool inGraph(nodes::Node* node) const;
+    void addNode(nodes::Node* node);
+    void addInput(nodes::io::InputNode* node);
+    void addOutput(nodes::io::OutputNode* node);
+    void topologicalSort();
+    bool isSorted() const { return sorted_; }
+    void forward();
+    void backward();
+    void zeroGrad() const;
+    // steps every node whose output requires a gradient, in insertion order, then zeroes all
+    // gradients (src/Model.cu:20-23, src/ComputeGraph.cu:541-547). `before_step` runs once after
+    // backward and before the first optimizer step (the data-parallel all-reduce hooks in here).
+    void update(opt::Optimizer* optimizer, const std::function<void()>& before_step = nullptr) const;
+    float getLoss() const;
+    const std::vector<nodes::Node*>& getNodes() const { return nodes_; }
+    const std::vector<nodes::io::OutputNode*>& getOutputs() const { return outputs_; }
+
+private:
+    std::vector<nodes::Node*> nodes_, sorted_nodes_;
+    std::vector<nodes::io::InputNode*> inputs_;
+    std::vector<nodes::io::OutputNode*> outputs_;
+    bool sorted_ = false;
+};
+
+}  // namespace nz::graph

@@ -1,0 +1,99 @@
+// NCCL data-parallel communicator of the host layer (one process per GPU).
+#include <NeuZephyr/DataParallel.cuh>
+#include <NeuZephyr/StreamManager.cuh>
+
+#include <nccl.h>
+
+#include <chrono>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <stdexcept>
+#include <thread>
+
+namespace nz::dist {
+
+using SM = cuStrm::StreamManager<float>;
+
+#define NCCL_TRY(call)                                                                        \
+    do {                                                                                      \
+        ncclResult_t r_ = (call);                                                             \
+        if (r_ != ncclSuccess)                                                                \
+            throw std::runtime_error(std::string("NCCL: ") + ncclGetErrorString(r_) + " in " #call); \
+    } while (0)
+
+Communicator::Communicator(int rank, int world, const std::string& id_file, int device, double timeout_s)
+    : rank_(rank), world_(world) {
+    CHECK(cudaSetDevice(device));
+    ncclUniqueId id;
+    if (rank == 0) {
+        NCCL_TRY(ncclGetUniqueId(&id));
+        const std::string tmp = id_file + ".tmp";
+        FILE* f = fopen(tmp.c_str(), "wb");
+        if (!f || fwrite(&id, sizeof(id), 1, f) != 1) throw std::runtime_error("cannot write " + tmp);
+        fclose(f);
+        if (rename(tmp.c_str(), id_file.c_str()) != 0) throw std::runtime_error("cannot publish " + id_file);
+    } else {
+        const auto t0 = std::chrono::steady_clock::now();
+        for (;;) {
+            FILE* f = fopen(id_file.c_str(), "rb");
+            if (f) {
+                const size_t n = fread(&id, sizeof(id), 1, f);
+                fclose(f);
+                if (n == 1) break;
+            }
+            if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > timeout_s)
+                throw std::runtime_error("timed out waiting for the NCCL id file " + id_file);
+            std::this_thread::sleep_for(std::chrono::milliseconds(20));
+        }
+    }
+    ncclComm_t c;
+    NCCL_TRY(ncclCommInitRank(&c, world, id, rank));
+    comm_ = c;
+    cudaStream_t s;
+    CHECK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+    stream_ = s;
+    CHECK(cudaMalloc(&scalar_, sizeof(float)));
+}
+
+Communicator* Communicator::fromEnvironment() {
+    const char* r = getenv("RANK");
+    const char* w = getenv("WORLD_SIZE");
+    if (!r || !w || atoi(w) <= 1) return nullptr;
+    const char* lr = getenv("LOCAL_RANK");
+    const char* port = getenv("MASTER_PORT");
+    const char* idf = getenv("NZ_DP_ID_FILE");
+    std::string file = idf ? idf : std::string("/tmp/nz_dp_") + (port ? port : "0") + ".id";
+    return new Communicator(atoi(r), atoi(w), file, lr ? atoi(lr) : atoi(r));
+}
+
+Communicator::~Communicator() {
+    if (comm_) ncclCommDestroy(static_cast<ncclComm_t>(comm_));
+    if (stream_) cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
+    if (scalar_) cudaFree(scalar_);
+}
+
+void Communicator::allReduceAverage(float* grad, size_t n) {
+    if (world_ <= 1 || n == 0) return;
+    cudaStream_t s = static_cast<cudaStream_t>(stream_);
+    // like any other operation: wait for the gradient's pending writers and readers, run on the
+    // communication stream, publish a writer event so that the optimizer step orders after it
+    SM::Instance().streamWait(grad, s, true);
+    NCCL_TRY(ncclAllReduce(grad, grad, n, ncclFloat32, ncclAvg, static_cast<ncclComm_t>(comm_), s));
+    SM::Instance().recordData(grad, s);
+}
+
+float Communicator::allReduceSumHost(float v) {
+    if (world_ <= 1) return v;
+    cudaStream_t s = static_cast<cudaStream_t>(stream_);
+    CHECK(cudaMemcpyAsync(scalar_, &v, sizeof(float), cudaMemcpyHostToDevice, s));
+    NCCL_TRY(ncclAllReduce(scalar_, scalar_, 1, ncclFloat32, ncclSum, static_cast<ncclComm_t>(comm_), s));
+    float out = 0.f;
+    CHECK(cudaMemcpyAsync(&out, scalar_, sizeof(float), cudaMemcpyDeviceToHost, s));
+    CHECK(cudaStreamSynchronize(s));
+    return out;
+}
+
+void Communicator::barrier() { (void)allReduceSumHost(0.f); }
+
+}  // namespace nz::dist
