@@ -80,6 +80,16 @@ def build_host(force=False):
     return HOST_LIB
 
 
+def build_tools():
+    """Compiles the C++ tools shipped with the host layer into neuzephyr_b200/bin/."""
+    tools = os.path.join(HOST, "tools")
+    out = []
+    for name in sorted(os.listdir(tools)):
+        if name.endswith(".cpp"):
+            out.append(build_program(os.path.join(tools, name), os.path.join(HERE, "bin", name[:-4]), ".."))
+    return out
+
+
 def build(force=False, verbose=False):
     if force or _stale():
         cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + SOURCES

@@ -21,6 +21,9 @@ public:
     // optimizer step on every node that requires a gradient, then zeroGrad. With a
     // data-parallel communicator attached, parameter gradients are averaged over ranks first.
     void update(opt::Optimizer* optimizer);
+    // averages the parameter gradients over the ranks of the attached communicator (no-op without
+    // one); update() calls it, it is public so that gradients can be inspected after the exchange
+    void syncGradients();
     data::Tensor::value_type getLoss() const;
 
     void setFused(bool fused) { fused_ = fused; }
@@ -54,6 +57,7 @@ protected:
 private:
     Node* own(Node* n, bool parameter = false);
     bool fused_ = true;
+    bool grads_synced_ = false;
     dist::Communicator* comm_ = nullptr;
     std::vector<Node*> params_;
 };

@@ -135,12 +135,18 @@ Tensor& Model::forward() {
     computeGraph.forward();
     return *computeGraph.getOutputs().at(0)->output;
 }
-void Model::backward() { computeGraph.backward(); }
+void Model::backward() {
+    computeGraph.backward();
+    grads_synced_ = false;
+}
+void Model::syncGradients() {
+    if (comm_ && comm_->world() > 1 && !grads_synced_)
+        for (Node* p : params_) comm_->allReduceAverage(p->output->grad(), p->output->size());
+    grads_synced_ = true;
+}
 void Model::update(opt::Optimizer* optimizer) {
-    computeGraph.update(optimizer, [this]() {
-        if (comm_ && comm_->world() > 1)
-            for (Node* p : params_) comm_->allReduceAverage(p->output->grad(), p->output->size());
-    });
+    computeGraph.update(optimizer, [this]() { syncGradients(); });
+    grads_synced_ = false;
 }
 Tensor::value_type Model::getLoss() const { return computeGraph.getLoss(); }
 

@@ -1,0 +1,179 @@
+// The README-style segmentation model of the benchmark configuration, on the nz:: host layer:
+//   input {B,3,S,S} -> Conv2d(3->16,3x3,s1,p1) -> ReLU -> Conv2d(16->16,3x3,s1,p1) -> AvgPool2d(5,2)
+//   -> Linear(->16) -> Softmax -> BCE against {B,1,16,1} targets; Adam(0.01, 0.9, 0.999).
+// One process per GPU; with WORLD_SIZE > 1 the batch is sharded over ranks and parameter
+// gradients are averaged with NCCL before the Adam step.
+//
+//   seg_model bench  <global_batch> <size> <steps> <warmup>   one JSON line on rank 0
+//   seg_model check  <global_batch> <size>                    sharded step == full-batch step (rank 0 verifies)
+#include <NeuZephyr/Model.cuh>
+
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <random>
+#include <string>
+#include <vector>
+
+using namespace nz;
+using nz::data::Tensor;
+using nz::nodes::io::InputNode;
+
+class SegModel : public Model {
+public:
+    InputNode input, target;
+    SegModel(size_t batch, size_t size) : input({batch, 3, size, size}), target({batch, 1, 16, 1}) {
+        computeGraph.addInput(&input);
+        computeGraph.addInput(&target);
+        auto x = Conv2d(&input, 16, 3, 3, 1, 1, true, false, /*fuseRelu=*/true);
+        x = Conv2d(x, 16, 3, 3, 1, 1);
+        x = AvgPool2d(x, 5, 2);
+        x = Linear(x, 16);
+        x = Softmax(x);
+        BCELoss(x, &target);
+    }
+};
+
+// Seeded values: uniform(-1,1)-like inputs and Kaiming-uniform weights (bound sqrt(6/fan_in)).
+static void fill_uniform(std::vector<float>& v, float bound, unsigned seed) {
+    std::mt19937 gen(seed);
+    std::uniform_real_distribution<float> d(-bound, bound);
+    for (auto& x : v) x = d(gen);
+}
+static void init_params(SegModel& m, size_t size) {
+    const auto& p = m.parameters();  // w1, b1, w2, b2, wl, bl
+    const size_t pooled = (size - 5) / 2 + 1;
+    const float bounds[6] = {std::sqrt(6.f / 27.f), 0.f, std::sqrt(6.f / 144.f), 0.f,
+                             std::sqrt(6.f / (16.f * pooled * pooled)), 0.f};
+    for (size_t i = 0; i < p.size(); i++) {
+        std::vector<float> w(p[i]->output->size(), 0.f);
+        if (bounds[i] > 0.f) fill_uniform(w, bounds[i], 31 + (unsigned)i);
+        p[i]->dataInject(w.data());
+    }
+    m.graph().zeroGrad();
+}
+static void make_batch(std::vector<float>& x, std::vector<float>& t, size_t batch, size_t size) {
+    x.resize(batch * 3 * size * size);
+    t.resize(batch * 16);
+    fill_uniform(x, 1.f, 30);
+    std::mt19937 gen(34);
+    for (auto& v : t) v = (gen() & 1) ? 1.f : 0.f;
+}
+static double now_ms() {
+    return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
+}
+
+int main(int argc, char** argv) {
+    if (argc < 4) {
+        fprintf(stderr, "usage: seg_model bench|check <global_batch> <size> [steps warmup]\n");
+        return 2;
+    }
+    const std::string mode = argv[1];
+    const size_t B = atoll(argv[2]), S = atoll(argv[3]);
+    const int rank = getenv("RANK") ? atoi(getenv("RANK")) : 0;
+    const int world = getenv("WORLD_SIZE") ? atoi(getenv("WORLD_SIZE")) : 1;
+    const int local = getenv("LOCAL_RANK") ? atoi(getenv("LOCAL_RANK")) : rank;
+    CHECK(cudaSetDevice(local));
+    dist::Communicator* comm = dist::Communicator::fromEnvironment();
+    if (B % world) {
+        fprintf(stderr, "global batch must divide by the world size\n");
+        return 2;
+    }
+    const size_t b = B / world;
+    std::vector<float> x, t;
+    make_batch(x, t, B, S);
+    const size_t xs = 3 * S * S;
+    int rc = 0;
+    {
+        SegModel model(b, S);
+        model.setCommunicator(comm);
+        init_params(model, S);
+        model.input.dataInject(x.data() + rank * b * xs);
+        model.target.dataInject(t.data() + rank * b * 16);
+        opt::Adam adam(0.01f, 0.9f, 0.999f);
+        auto& sm = cuStrm::StreamManager<float>::Instance();
+        if (mode == "check") {
+            model.forward();
+            const float local_loss = model.getLoss();
+            model.backward();
+            model.syncGradients();
+            std::vector<std::vector<float>> grads;
+            for (auto* p : model.parameters()) grads.push_back(p->output->hostGrad());
+            model.update(&adam);
+            sm.sync();
+            const float loss = comm ? comm->allReduceSumHost(local_loss) / world : local_loss;
+            if (rank == 0) {
+                // the same step on the full batch, alone
+                SegModel full(B, S);
+                init_params(full, S);
+                full.input.dataInject(x.data());
+                full.target.dataInject(t.data());
+                opt::Adam adam2(0.01f, 0.9f, 0.999f);
+                full.forward();
+                const float full_loss = full.getLoss();
+                full.backward();
+                std::vector<std::vector<float>> fgrads;
+                for (auto* p : full.parameters()) fgrads.push_back(p->output->hostGrad());
+                full.update(&adam2);
+                sm.sync();
+                double worst_g = 0, worst_p = 0;
+                for (size_t i = 0; i < model.parameters().size(); i++) {
+                    const auto a = model.parameters()[i]->output->hostData();
+                    const auto c = full.parameters()[i]->output->hostData();
+                    double gmax = 0, gnum = 0;
+                    for (size_t k = 0; k < a.size(); k++) gmax = std::max(gmax, std::fabs((double)fgrads[i][k]));
+                    for (size_t k = 0; k < a.size(); k++) {
+                        gnum = std::max(gnum, std::fabs((double)grads[i][k] - fgrads[i][k]));
+                        // Adam's first step moves a weight by lr * sign(g): compare weights only where the
+                        // gradient is well away from zero, so that its sign cannot flip with summation order
+                        if (std::fabs(fgrads[i][k]) > 1e-3 * gmax && std::fabs(fgrads[i][k]) > 1e-4)
+                            worst_p = std::max(worst_p, std::fabs((double)a[k] - c[k]));
+                    }
+                    worst_g = std::max(worst_g, gnum / (gmax > 0 ? gmax : 1));
+                }
+                // gradients are GEMM operands rounded to fp16; a rank's shard sees them scaled by the world
+                // size, which moves values in and out of fp16's subnormal range, hence 2e-3 rather than
+                // fp32 reordering noise
+                const bool ok = worst_g <= 2e-3 && worst_p <= 1e-4 &&
+                                std::fabs(loss - full_loss) <= 1e-4 * std::fabs(full_loss) + 1e-6;
+                printf("{\"mode\": \"check\", \"world\": %d, \"loss_sharded\": %.7f, \"loss_full\": %.7f, "
+                       "\"max_rel_grad_diff\": %.3e, \"max_abs_param_diff\": %.3e, \"ok\": %s}\n",
+                       world, loss, full_loss, worst_g, worst_p, ok ? "true" : "false");
+                rc = ok ? 0 : 1;
+            }
+            if (comm) comm->barrier();
+        } else {
+            const int steps = argc > 4 ? atoi(argv[4]) : 5, warmup = argc > 5 ? atoi(argv[5]) : 2;
+            auto step = [&]() {
+                model.forward();
+                model.backward();
+                model.update(&adam);
+            };
+            for (int i = 0; i < warmup; i++) step();
+            sm.sync();
+            if (comm) comm->barrier();
+            const double t0 = now_ms();
+            for (int i = 0; i < steps; i++) step();
+            sm.sync();
+            CHECK(cudaDeviceSynchronize());
+            double ms = (now_ms() - t0) / steps;
+            if (comm) {
+                // max over ranks: every rank contributes its own time, slowest wins
+                float mine = (float)ms, worst = 0.f;
+                for (int r = 0; r < world; r++) worst = std::max(worst, comm->allReduceSumHost(r == rank ? mine : 0.f));
+                ms = worst;
+            }
+            int status = 0;
+            nzb_device_status(&status);
+            if (rank == 0)
+                printf("{\"mode\": \"bench\", \"world\": %d, \"global_batch\": %zu, \"size\": %zu, \"steps\": %d, "
+                       "\"ms_per_step\": %.4f, \"img_per_s\": %.2f, \"loss_total\": %.6f, \"status\": %d}\n",
+                       world, B, S, steps, ms, B / ms * 1e3, model.getLoss(), status);
+            if (comm) comm->barrier();
+        }
+    }
+    delete comm;
+    return rc;
+}
