@@ -105,6 +105,18 @@ class ClockSampler:
                 "samples": len(rows), "power_w_max": max(r[2] for r in rows) if rows else None}
 
 
+def max_over_ranks(values, device=None):
+    """Element-wise maximum of a list of floats over all ranks of the default process group
+    (identity without one). Timings of a multi-rank run are reported as the slowest rank's."""
+    import torch
+    import torch.distributed as dist
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return [float(v) for v in values]
+    t = torch.tensor(values, dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t.tolist()]
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -220,10 +232,7 @@ def run_ours(args):
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
-    t = torch.tensor([ms, kms, e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms, kms, e2e_ms = [float(x) for x in t.tolist()]
+    ms, kms, e2e_ms = max_over_ranks([ms, kms, e2e_ms], device=dev)
     if rank == 0:
         peak_tf, how = measured_peaks(sustained=args.steps * kms > 100.0)
         achieved = FLOP / (kms * 1e-3) / 1e12
@@ -247,9 +256,84 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline()
+        if world == 1 and not args.no_extras:
+            del A, B, Cd
+            torch.cuda.empty_cache()
+            out["other_workloads"] = other_workloads(dev)
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def _time_ms(fn, iters, warm=2):
+    import torch
+    for _ in range(warm):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def other_workloads(dev):
+    """Short measurements of the other configurations of the path (not the headline metric):
+    Linear 8192x4096x4096 forward+backward, Conv2d N=32 C=64 224^2 -> 128 (3x3, s1, p1) forward /
+    backward-data / backward-weight, and one training step of the segmentation model."""
+    import torch
+    import neuzephyr_b200 as nz
+    out = {}
+    g = torch.Generator(device=dev)
+    g.manual_seed(10)
+    try:
+        Bt, Fi, Fo = 8192, 4096, 4096
+        x = torch.randn((Bt, Fi), device=dev, generator=g)
+        w = (torch.rand((Fo, Fi), device=dev, generator=g) * 2 - 1) * (6.0 / Fi) ** 0.5
+        b = torch.zeros(Fo, device=dev)
+        dy = torch.randn((Bt, Fo), device=dev, generator=g)
+        y = torch.empty((Bt, Fo), device=dev)
+        dx, dw, db = torch.zeros_like(x), torch.zeros_like(w), torch.zeros_like(b)
+        f = _time_ms(lambda: nz.linear_forward(x, w, b, relu=True, out=y), 5)
+        bw = _time_ms(lambda: nz.linear_backward(x, w, y, dy, dx, dw, db, relu=True), 5)
+        out["linear_8192x4096x4096"] = {"forward_ms": f, "backward_ms": bw,
+                                        "tflops": 3 * 2.0 * Bt * Fi * Fo / ((f + bw) * 1e-3) / 1e12}
+        del x, w, dy, y, dx, dw
+    except Exception as e:  # pragma: no cover
+        out["linear_8192x4096x4096"] = {"error": repr(e)[:200]}
+    try:
+        N_, C_, H_, Co, k = 32, 64, 224, 128, 3
+        x = torch.randn((N_, C_, H_, H_), device=dev, generator=g)
+        w = torch.randn((1, 1, C_ * k * k, Co), device=dev, generator=g) * (2.0 / (C_ * k * k)) ** 0.5
+        bias = torch.zeros((1, 1, H_ * H_, Co), device=dev)
+        y = torch.empty((N_, Co, H_, H_), device=dev)
+        dy = torch.randn((N_, Co, H_, H_), device=dev, generator=g)
+        dx, dw = torch.zeros_like(x), torch.zeros_like(w)
+        f = _time_ms(lambda: nz.conv2d_forward(x, w, bias, k, k, 1, 1, out=y), 3)
+        bd = _time_ms(lambda: nz.conv2d_backward_data(dy, w, x.shape, k, k, 1, 1, dx), 3)
+        bwt = _time_ms(lambda: nz.conv2d_backward_weight(x, dy, w.shape, k, k, 1, 1, dw), 3)
+        flop = 2.0 * N_ * H_ * H_ * Co * C_ * k * k
+        out["conv2d_n32_c64_224_co128"] = {"forward_ms": f, "backward_data_ms": bd, "backward_weight_ms": bwt,
+                                           "forward_img_per_s": N_ / f * 1e3,
+                                           "fwd_bwd_img_per_s": N_ / (f + bd + bwt) * 1e3,
+                                           "forward_tflops": flop / f / 1e9,
+                                           "forward_hbm_gbs_algorithmic": 4.0 * (x.numel() + y.numel()) / f / 1e6}
+        del x, y, dy, dx, bias
+        torch.cuda.empty_cache()
+    except Exception as e:  # pragma: no cover
+        out["conv2d_n32_c64_224_co128"] = {"error": repr(e)[:200]}
+    tool = os.path.join(ROOT, "neuzephyr_b200", "bin", "seg_model")
+    if os.path.exists(tool):
+        try:
+            env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+            r = subprocess.run([tool, "bench", "16", "1024", "2", "1"], capture_output=True, text=True, timeout=300,
+                               env=env)
+            out["seg_model_step_batch16_1gpu"] = json.loads(r.stdout.strip().splitlines()[-1])
+        except Exception as e:  # pragma: no cover
+            out["seg_model_step_batch16_1gpu"] = {"error": repr(e)[:200]}
+    return out
 
 
 def run_reference(args):
@@ -299,6 +383,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-extras", action="store_true", help="skip the Linear / Conv2d / model-step measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
