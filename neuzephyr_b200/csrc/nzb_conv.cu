@@ -41,6 +41,9 @@ struct ConvParams {
     int32_t w_per_sample;  // weight matrix index = image index
     int32_t bias_mode;     // NZB_BIAS_NONE, NZB_BIAS_ROW ([Cout]) or NZB_BIAS_MATRIX ([Ho*Wo][Cout])
     int32_t accumulate, relu;
+    // row mode: a tile is a segment of one output row
+    int32_t tiles_per_row, tile_px, win_pitch;  // win_pitch: fp32 elements per window row (TMA box width)
+    uint32_t win_bytes;                         // bytes one window copy delivers
     int64_t total_tiles;
     int* status;
 };
@@ -97,7 +100,7 @@ __device__ __forceinline__ ConvTile decode_conv_tile(const ConvParams& p, int64_
     return t;
 }
 
-template <class Cfg>
+template <class Cfg, bool ACC>
 __global__ void __launch_bounds__(Cfg::THREADS, 1)
 conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvParams p) {
     using namespace ptx;
@@ -228,14 +231,24 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
                 if (p.bias_mode == NZB_BIAS_MATRIX) {
                     // bias is [pixel][channel]: read with lanes along channels (coalesced), transpose in
                     // shared memory so that each lane ends up with its own pixel's row
+                    constexpr int RPI = 32 / Cfg::CHUNK;
                     const int32_t co = co0 + (lane % Cfg::CHUNK);
-#pragma unroll 4
-                    for (int r = lane / Cfg::CHUNK; r < 32; r += 32 / Cfg::CHUNK) {
-                        const int32_t pp = pix0 + r;
-                        bt[r * 33 + (lane % Cfg::CHUNK)] =
-                            (pp < p.HoWo && co < p.Cout) ? __ldg(p.bias + static_cast<int64_t>(pp) * p.Cout + co) : 0.f;
+                    float bv[32 / RPI];
+#pragma unroll
+                    for (int i = 0; i < 32 / RPI; i++) {
+                        const int32_t pp = pix0 + i * RPI + lane / Cfg::CHUNK;
+                        bv[i] = (pp < p.HoWo && co < p.Cout) ? __ldg(p.bias + static_cast<int64_t>(pp) * p.Cout + co) : 0.f;
                     }
+#pragma unroll
+                    for (int i = 0; i < 32 / RPI; i++) bt[(i * RPI + lane / Cfg::CHUNK) * 33 + (lane % Cfg::CHUNK)] = bv[i];
                     __syncwarp();
+                }
+                // values to accumulate onto are fetched together (one memory round trip per chunk)
+                float old[ACC ? Cfg::CHUNK : 1];
+                if constexpr (ACC) {
+#pragma unroll
+                    for (int j = 0; j < Cfg::CHUNK; j++)
+                        old[j] = (pix_ok && co0 + j < p.Cout) ? yb[static_cast<int64_t>(co0 + j) * p.HoWo] : 0.f;
                 }
                 tmem_ld_wait();
                 if (pix_ok) {
@@ -244,12 +257,11 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
                         const int32_t co = co0 + j;
                         if (co < p.Cout) {
                             float x = __uint_as_float(v[j]);
-                            float* dst = yb + static_cast<int64_t>(co) * p.HoWo;
-                            if (p.accumulate) x += *dst;
+                            if constexpr (ACC) x += old[j];
                             if (p.bias_mode == NZB_BIAS_MATRIX) x += bt[lane * 33 + j];
                             else if (p.bias_mode == NZB_BIAS_ROW) x += __ldg(p.bias + co);
                             if (p.relu) x = fmaxf(x, 0.f);
-                            *dst = x;
+                            yb[static_cast<int64_t>(co) * p.HoWo] = x;
                         }
                     }
                 }
@@ -328,6 +340,323 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
                 // orders those generic-proxy writes before the tensor core's async-proxy reads and
                 // publishes the stage. (One proxy fence per stage instead of one per thread: the
                 // fence sits on the causality path between every write and the MMA that reads it.)
+                asm volatile("bar.sync %0, 256;" ::"r"(1 + grp) : "memory");
+                if (wi == 0 && lane == 0) {
+                    fence_proxy_async_smem();
+                    mbar_arrive(&full[s]);
+                }
+            }
+        }
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = NZB_ERR_DEVICE_TIMEOUT;
+        __threadfence_system();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+
+// ---------------------------------------------------------------------------
+// Row mode: the kernel used whenever an output row is at least 32 pixels wide and the input
+// row pitch is a multiple of 16 bytes. A tile is a segment of ONE output row (at most 128
+// pixels), so the input it touches is a small window: Kh input rows x ((pixels-1)*stride + Kw)
+// columns per channel. For every k block, TMA copies that window for the block's channels
+// (a 4-D box of the NCHW fp32 tensor; padding and tails arrive as zeros) into a ring of
+// shared-memory window buffers, several k blocks ahead; the producer warps then expand the
+// taps from shared memory into the tensor core's A tile, rounding to fp16 on the way. Each
+// input element is fetched from global memory once per tile and k block instead of once per
+// tap, no per-element bounds test is left, and global-load latency is off the critical path.
+// ---------------------------------------------------------------------------
+template <int BN_, int STAGES_>
+struct ConvRowCfg {
+    static constexpr int BN = BN_, STAGES = STAGES_;
+    static constexpr int A_BYTES = 128 * 64 * 2;
+    static constexpr int B_BYTES = BN * 64 * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;
+    static constexpr int KTAB_BYTES = 16 * 32 * 4;
+    static constexpr int NWIN = 4;            // window ring depth
+    static constexpr int WIN_BYTES = 16384;   // one window buffer (fp32)
+    static constexpr int SMEM_BYTES =
+        1024 + STAGES * STAGE_BYTES + NWIN * WIN_BYTES + EPI_BYTES + KTAB_BYTES + BAR_BYTES;
+    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+    static constexpr int CHUNK = (BN < 32) ? BN : 32;
+    static constexpr int THREADS = 22 * 32;
+    static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
+};
+
+struct ConvRowTile {
+    int32_t img, ho, wo0, npx, nt;
+};
+__device__ __forceinline__ ConvRowTile decode_row_tile(const ConvParams& p, int64_t tile) {
+    ConvRowTile t;
+    t.nt = static_cast<int32_t>(tile % p.tiles_n);
+    int64_t r = tile / p.tiles_n;
+    const int32_t seg = static_cast<int32_t>(r % p.tiles_per_row);
+    r /= p.tiles_per_row;
+    t.ho = static_cast<int32_t>(r % p.Ho);
+    t.img = static_cast<int32_t>(r / p.Ho);
+    t.wo0 = seg * p.tile_px;
+    t.npx = min(p.tile_px, p.Wo - t.wo0);
+    return t;
+}
+
+template <class Cfg, bool ACC>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                           const ConvParams p) {
+    using namespace ptx;
+    constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES, NWIN = Cfg::NWIN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* win_all = smem + STAGES * Cfg::STAGE_BYTES;
+    float* epi = reinterpret_cast<float*>(win_all + NWIN * Cfg::WIN_BYTES);
+    int* ktab_all = reinterpret_cast<int*>(win_all + NWIN * Cfg::WIN_BYTES + Cfg::EPI_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(win_all + NWIN * Cfg::WIN_BYTES + Cfg::EPI_BYTES + Cfg::KTAB_BYTES);
+    uint64_t* full = bars;                             // [STAGES] weights landed + tap group arrived
+    uint64_t* empty = bars + STAGES;                   // [STAGES]
+    uint64_t* tfull = bars + 2 * STAGES;               // [2]
+    uint64_t* tempty = bars + 2 * STAGES + 2;          // [2]
+    uint64_t* wfull = bars + 2 * STAGES + 4;           // [NWIN] window landed
+    uint64_t* wempty = bars + 2 * STAGES + 4 + NWIN;   // [NWIN] window consumed by the 8 warps of a group
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + 2 * NWIN);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+    const int KHW = p.Kh * p.Kw;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmW);
+        prefetch_tensormap(&tmX);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 2);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 4);
+        }
+        for (int w = 0; w < NWIN; w++) {
+            mbar_init(&wfull[w], 1);
+            mbar_init(&wempty[w], 8);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA: image windows (ahead of use) and weight tiles ----------------
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            const ConvRowTile t = decode_row_tile(p, tile);
+            const int32_t zw = p.w_per_sample ? t.img : 0;
+            const int32_t h_base = t.ho * p.stride - p.pad;
+            const int32_t w_base = t.wo0 * p.stride - p.pad;
+            const int32_t x0 = (w_base >= 0 ? w_base : w_base - 3) / 4 * 4;  // floor to a multiple of 4 elements
+            for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                const uint32_t ws = it % NWIN, wph = (it / NWIN) & 1;
+                if (!mbar_wait_warp(&wempty[ws], wph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&wfull[ws], p.win_bytes);
+                    tma_load_4d(win_all + ws * Cfg::WIN_BYTES, &tmX, x0, h_base, (kb * 64) / KHW, t.img, &wfull[ws]);
+                }
+                __syncwarp();
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&full[s], Cfg::B_BYTES);
+                    tma_load_3d(smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmW, kb * 64, t.nt * BN, zw, &full[s]);
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok && lane == 0) {
+            // one bounded budget for copies still in flight
+            const long long t0 = clock64();
+            const uint32_t first = it > (uint32_t)NWIN ? it - NWIN : 0;
+            for (uint32_t j = first; j < it; j++)
+                while (!mbar_try_wait(&wfull[j % NWIN], (j / NWIN) & 1))
+                    if (clock64() - t0 > kWaitCycleLimit) break;
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue ----------------
+        constexpr uint32_t idesc = make_idesc_conv(128, BN);
+        uint32_t it = 0, tcount = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, tcount++) {
+            const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+            if (!mbar_wait_warp(&tempty[acc], aph ^ 1, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                const uint64_t da = make_sw128_mmajor_desc(sa);
+                const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                const int32_t ksteps = (kb == p.k_blocks - 1) ? p.last_ksteps : 4;
+                if (elect_one()) {
+                    mma_f16_ss(d_tmem, da, db, idesc, kb > 0 ? 1u : 0u);
+                    if (ksteps > 1) mma_f16_ss(d_tmem, da + 128, db + 2, idesc, 1u);
+                    if (ksteps > 2) mma_f16_ss(d_tmem, da + 256, db + 4, idesc, 1u);
+                    if (ksteps > 3) mma_f16_ss(d_tmem, da + 384, db + 6, idesc, 1u);
+                    mma_commit(&empty[s]);
+                }
+                __syncwarp();
+            }
+            if (ok && elect_one()) mma_commit(&tfull[acc]);
+            __syncwarp();
+        }
+    } else if (warp < 6) {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;
+        float* bt = epi + (warp - 2) * 32 * 33;
+        uint32_t tcount = 0;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, tcount++) {
+            const ConvRowTile t = decode_row_tile(p, tile);
+            const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+            if (!mbar_wait_relaxed(&tfull[acc], aph, abort_flag)) break;
+            tc_fence_after();
+            const int32_t m0 = q * 32;
+            const int32_t pix0 = t.ho * p.Wo + t.wo0 + m0;
+            const int32_t pix = pix0 + lane;
+            const bool pix_ok = m0 + lane < t.npx;
+            float* yb = p.Y + (static_cast<int64_t>(t.img) * p.Cout) * p.HoWo + pix;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += Cfg::CHUNK) {
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c0;
+                uint32_t v[Cfg::CHUNK];
+                if constexpr (Cfg::CHUNK == 32) tmem_ld_32x32(taddr, v);
+                else tmem_ld_32x16(taddr, v);
+                const int32_t co0 = t.nt * BN + c0;
+                if (p.bias_mode == NZB_BIAS_MATRIX) {
+                    // bias is [pixel][channel]: read with lanes along channels (coalesced, all loads in
+                    // flight together), transpose through shared memory so each lane gets its pixel's row
+                    constexpr int RPI = 32 / Cfg::CHUNK;  // pixel rows covered per load instruction
+                    const int32_t co = co0 + (lane % Cfg::CHUNK);
+                    float bv[32 / RPI];
+#pragma unroll
+                    for (int i = 0; i < 32 / RPI; i++) {
+                        const int r = i * RPI + lane / Cfg::CHUNK;
+                        bv[i] = (m0 + r < t.npx && co < p.Cout)
+                                    ? __ldg(p.bias + static_cast<int64_t>(pix0 + r) * p.Cout + co) : 0.f;
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32 / RPI; i++) bt[(i * RPI + lane / Cfg::CHUNK) * 33 + (lane % Cfg::CHUNK)] = bv[i];
+                    __syncwarp();
+                }
+                // values to accumulate onto are fetched together (one memory round trip per chunk)
+                float old[ACC ? Cfg::CHUNK : 1];
+                if constexpr (ACC) {
+#pragma unroll
+                    for (int j = 0; j < Cfg::CHUNK; j++)
+                        old[j] = (pix_ok && co0 + j < p.Cout) ? yb[static_cast<int64_t>(co0 + j) * p.HoWo] : 0.f;
+                }
+                tmem_ld_wait();
+                if (pix_ok) {
+#pragma unroll
+                    for (int j = 0; j < Cfg::CHUNK; j++) {
+                        const int32_t co = co0 + j;
+                        if (co < p.Cout) {
+                            float x = __uint_as_float(v[j]);
+                            if constexpr (ACC) x += old[j];
+                            if (p.bias_mode == NZB_BIAS_MATRIX) x += bt[lane * 33 + j];
+                            else if (p.bias_mode == NZB_BIAS_ROW) x += __ldg(p.bias + co);
+                            if (p.relu) x = fmaxf(x, 0.f);
+                            yb[static_cast<int64_t>(co) * p.HoWo] = x;
+                        }
+                    }
+                }
+                __syncwarp();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+    } else {
+        // ---------------- tap expansion: window (fp32, shared) -> A tile (fp16, swizzled) ----------------
+        // Two groups of eight warps; group g serves the k blocks with (it & 1) == g. Inside a group
+        // warp wi owns pixels [32*(wi&3), +32) (one per lane) and k columns [32*(wi>>2), +32).
+        const int pw = warp - 6;
+        const int grp = pw >> 3, wi = pw & 7;
+        const int pq = wi & 3, khalf = wi >> 2;
+        const int BW = p.win_pitch;
+        int* ktab = ktab_all + pw * 32;
+        const int e = 32 * (pq & 1) + lane;
+        const uint32_t chunk = e >> 3, inchunk = (e & 7) * 2;
+        const int mcol = (pq * 32 + lane) * p.stride;  // this lane's pixel as a column offset
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            const ConvRowTile t = decode_row_tile(p, tile);
+            const int32_t w_base = t.wo0 * p.stride - p.pad;
+            const int32_t x0 = (w_base >= 0 ? w_base : w_base - 3) / 4 * 4;
+            const int lane_off = mcol + (w_base - x0);
+            for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                if ((it & 1) != (uint32_t)grp) continue;
+                // window offset of k column j of this warp's 32, or -1 past K
+                {
+                    const int32_t k = kb * 64 + khalf * 32 + lane;
+                    const int32_t c = k / KHW;
+                    const int32_t r = k - c * KHW;
+                    const int32_t kh = r / p.Kw, kw = r - kh * p.Kw;
+                    ktab[lane] = k < p.K ? ((c - (kb * 64) / KHW) * p.Kh + kh) * BW + kw : -1;
+                }
+                __syncwarp();
+                const uint32_t ws = it % NWIN, wph = (it / NWIN) & 1;
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&wfull[ws], wph, abort_flag) || !mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const float* wl = reinterpret_cast<const float*>(win_all + ws * Cfg::WIN_BYTES) + lane_off;
+                uint8_t* sA = smem + s * Cfg::STAGE_BYTES + (pq >> 1) * 8192 + khalf * 4096;
+                float a[32];
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) {
+                    const int4 o = *reinterpret_cast<const int4*>(ktab + j);  // broadcast read
+                    a[j] = o.x >= 0 ? wl[o.x] : 0.f;
+                    a[j + 1] = o.y >= 0 ? wl[o.y] : 0.f;
+                    a[j + 2] = o.z >= 0 ? wl[o.z] : 0.f;
+                    a[j + 3] = o.w >= 0 ? wl[o.w] : 0.f;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&wempty[ws]);  // window may be refilled
+#pragma unroll
+                for (int j = 0; j < 32; j++) {
+                    const uint32_t off = (j >> 3) * 1024 + (j & 7) * 128 + (((chunk ^ (j & 7)) & 7) << 4) + inchunk;
+                    *reinterpret_cast<__half*>(sA + off) = __float2half_rn(a[j]);
+                }
+                // all eight warps of the group have written their part of the stage: one thread orders
+                // those generic-proxy writes before the tensor core's async-proxy reads and publishes it
                 asm volatile("bar.sync %0, 256;" ::"r"(1 + grp) : "memory");
                 if (wi == 0 && lane == 0) {
                     fence_proxy_async_smem();
@@ -508,13 +837,70 @@ static int run_conv_cfg(const ConvRun& r, const __half* W16, int64_t Kp, int64_t
     if (rc != NZB_OK) return rc;
     static bool attr_set = false;
     if (!attr_set) {
-        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_igemm_tcgen05_kernel<Cfg>,
+        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_igemm_tcgen05_kernel<Cfg, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_igemm_tcgen05_kernel<Cfg, true>,
                                           cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
         attr_set = true;
     }
     p.total_tiles = (int64_t)r.N * p.tiles_per_image * p.tiles_n;
     const int64_t grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
-    conv2d_igemm_tcgen05_kernel<Cfg><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, p);
+    if (p.accumulate)
+        conv2d_igemm_tcgen05_kernel<Cfg, true><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, p);
+    else
+        conv2d_igemm_tcgen05_kernel<Cfg, false><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, p);
+    NZB_CUDA_TRY(cudaGetLastError());
+    return NZB_OK;
+}
+
+template <class Cfg>
+static int run_conv_rows_cfg(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN, const DeviceState& ds,
+                             int tiles_per_row, int tile_px, int box_w, int box_c, cudaStream_t stream) {
+    ConvParams p{};
+    p.X = r.X; p.Y = r.Y; p.bias = r.bias;
+    p.C = (int32_t)r.C; p.H = (int32_t)r.H; p.W = (int32_t)r.W; p.Cout = (int32_t)r.Cout;
+    p.Kh = (int32_t)r.Kh; p.Kw = (int32_t)r.Kw; p.stride = (int32_t)r.stride; p.pad = (int32_t)r.pad;
+    p.Ho = (int32_t)r.Ho; p.Wo = (int32_t)r.Wo; p.HoWo = (int32_t)(r.Ho * r.Wo);
+    p.K = (int32_t)(r.C * r.Kh * r.Kw);
+    p.k_blocks = (p.K + 63) / 64;
+    p.last_ksteps = (p.K - (p.k_blocks - 1) * 64 + 15) / 16;
+    p.w_per_sample = r.w_per_sample;
+    p.bias_mode = r.bias ? r.bias_mode : NZB_BIAS_NONE;
+    p.accumulate = r.accumulate; p.relu = r.relu;
+    p.status = ds.status_dev;
+    p.tiles_n = (p.Cout + Cfg::BN - 1) / Cfg::BN;
+    p.tiles_per_row = tiles_per_row; p.tile_px = tile_px; p.win_pitch = box_w;
+    p.win_bytes = (uint32_t)(box_w * r.Kh * box_c * 4);
+    CUtensorMap tmW, tmX;
+    int rc = make_weight_map(&tmW, W16, p.K, Kp, p.Cout, wN, Cfg::BN);
+    if (rc != NZB_OK) return rc;
+    {
+        EncodeTiledFn enc;
+        rc = get_encode_tiled(&enc);
+        if (rc != NZB_OK) return rc;
+        cuuint64_t dims[4] = {(cuuint64_t)r.W, (cuuint64_t)r.H, (cuuint64_t)r.C, (cuuint64_t)r.N};
+        cuuint64_t strides[3] = {(cuuint64_t)r.W * 4, (cuuint64_t)r.H * r.W * 4, (cuuint64_t)r.C * r.H * r.W * 4};
+        cuuint32_t box[4] = {(cuuint32_t)box_w, (cuuint32_t)r.Kh, (cuuint32_t)box_c, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult cr = enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float*>(r.X), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (image window) failed with CUresult %d", (int)cr);
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_rows_tcgen05_kernel<Cfg, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_rows_tcgen05_kernel<Cfg, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    p.total_tiles = (int64_t)r.N * r.Ho * tiles_per_row * p.tiles_n;
+    const int64_t grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
+    if (p.accumulate)
+        conv2d_rows_tcgen05_kernel<Cfg, true><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, p);
+    else
+        conv2d_rows_tcgen05_kernel<Cfg, false><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, p);
     NZB_CUDA_TRY(cudaGetLastError());
     return NZB_OK;
 }
@@ -527,6 +913,29 @@ static int run_conv(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN,
     if (r.Ho * r.Wo > INT32_MAX - 256 || r.C * r.Kh * r.Kw > INT32_MAX - 256 || r.C * r.H * r.W > INT32_MAX)
         return fail(NZB_ERR_UNSUPPORTED, "per-image extent exceeds 2^31");
     if (r.Kh > 31 || r.Kw > 31) return fail(NZB_ERR_UNSUPPORTED, "kernel extent above 31");
+    if (r.Wo >= 32 && r.W % 4 == 0 && (reinterpret_cast<uintptr_t>(r.X) & 15) == 0) {
+        // row mode if the fp32 window of one k block (a TMA box) fits its shared-memory buffer
+        const int tiles_per_row = (int)((r.Wo + 127) / 128);
+        const int tile_px = (int)((r.Wo + tiles_per_row - 1) / tiles_per_row);
+        // columns a tile touches, plus up to 3 for rounding the first column down to 16 bytes,
+        // rounded up to a whole number of 16-byte units; unused tile rows (pixels past the
+        // segment) still read inside the box row they start in or the rows after it
+        int box_w = (int)((tile_px - 1) * r.stride + r.Kw) + 3;
+        box_w = (box_w + 3) / 4 * 4;
+        const int64_t khw = r.Kh * r.Kw;
+        int64_t box_c = (63 + khw - 1) / khw + 1;
+        if (box_c > r.C) box_c = r.C;
+        const int64_t elems = (int64_t)box_w * r.Kh * box_c;
+        const int64_t reach = elems + 128 * r.stride + r.Kw + 4;  // furthest element an unused tile row may read
+        if (box_w <= 256 && r.Kh <= 256 && box_c <= 256 && reach * 4 <= ConvRowCfg<16, 4>::WIN_BYTES * 2 &&
+            elems * 4 <= ConvRowCfg<16, 4>::WIN_BYTES) {
+            if (r.Cout > 128) return run_conv_rows_cfg<ConvRowCfg<256, 2>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+            if (r.Cout > 64) return run_conv_rows_cfg<ConvRowCfg<128, 4>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+            if (r.Cout > 32) return run_conv_rows_cfg<ConvRowCfg<64, 4>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+            if (r.Cout > 16) return run_conv_rows_cfg<ConvRowCfg<32, 4>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+            return run_conv_rows_cfg<ConvRowCfg<16, 4>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+        }
+    }
     if (r.Cout > 128) return run_conv_cfg<ConvCfg<256, 4>>(r, W16, Kp, wN, *ds, stream);
     if (r.Cout > 64) return run_conv_cfg<ConvCfg<128, 6>>(r, W16, Kp, wN, *ds, stream);
     if (r.Cout > 32) return run_conv_cfg<ConvCfg<64, 8>>(r, W16, Kp, wN, *ds, stream);

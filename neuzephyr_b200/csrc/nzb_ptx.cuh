@@ -119,6 +119,17 @@ __device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// 4-D tiled load (used for fp32 image windows {W, H, C, N}); out-of-range elements read as zero.
+// The innermost coordinate must keep x * element size a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* m, int32_t x, int32_t y, int32_t z,
+                                            int32_t w, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(x), "r"(y), "r"(z), "r"(w),
+        "r"(smem_u32(bar))
+        : "memory");
+}
+
 // ---- tensor memory ------------------------------------------------------------
 // Whole-warp instructions (.sync.aligned): call with all 32 lanes converged.
 __device__ __forceinline__ void tmem_alloc(uint32_t* smem_result, uint32_t ncols) {

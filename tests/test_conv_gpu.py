@@ -39,6 +39,14 @@ CASES = [
     (2, 4, 17, 19, 24, 3, 2, 0, False),
     (1, 70, 9, 9, 130, 1, 1, 0, False),
     (2, 2, 40, 40, 300, 3, 1, 0, True),
+    # output rows of 32 pixels or more take the row-mode kernel (shared-memory window per k block)
+    (2, 16, 20, 48, 16, 3, 1, 1, False),
+    (1, 3, 10, 130, 16, 3, 1, 1, False),
+    (2, 8, 9, 64, 24, 3, 2, 1, False),
+    (1, 64, 6, 224, 128, 3, 1, 1, False),
+    (1, 5, 12, 100, 7, 5, 1, 2, False),
+    (1, 70, 5, 40, 130, 1, 1, 0, False),
+    (3, 16, 7, 256, 16, 3, 1, 1, True),
 ]
 
 
