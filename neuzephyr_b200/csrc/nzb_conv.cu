@@ -381,7 +381,8 @@ struct ConvRowCfg {
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_BYTES = 256;
     static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;
-    static constexpr int KTAB_BYTES = 16 * 32 * 4;
+    static constexpr int KTAB_ENTRIES = 4096;  // window offset of every k (whole contraction), built once
+    static constexpr int KTAB_BYTES = KTAB_ENTRIES * 4;
     static constexpr int NWIN = 4;            // window ring depth
     static constexpr int WIN_BYTES = 16384;   // one window buffer (fp32)
     static constexpr int SMEM_BYTES =
@@ -438,7 +439,7 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
         prefetch_tensormap(&tmW);
         prefetch_tensormap(&tmX);
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(&full[s], 2);
+            mbar_init(&full[s], 9);
             mbar_init(&empty[s], 1);
         }
         for (int a = 0; a < 2; a++) {
@@ -455,6 +456,14 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
     if (warp == 1) {
         tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
         tmem_relinquish();
+    }
+    // window offset of every k of the (64-padded) contraction: ((c - first channel of k's block) * Kh + kh)
+    // * pitch + kw; columns past K get -1. Built once; the tap loop only reads it.
+    for (int k = threadIdx.x; k < p.k_blocks * 64; k += Cfg::THREADS) {
+        const int c = k / KHW;
+        const int r = k - c * KHW;
+        const int kh = r / p.Kw, kw = r - kh * p.Kw;
+        ktab_all[k] = k < p.K ? ((c - ((k >> 6) << 6) / KHW) * p.Kh + kh) * p.win_pitch + kw : -1;
     }
     tc_fence_before();
     __syncthreads();
@@ -608,11 +617,14 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
         const int pw = warp - 6;
         const int grp = pw >> 3, wi = pw & 7;
         const int pq = wi & 3, khalf = wi >> 2;
-        const int BW = p.win_pitch;
-        int* ktab = ktab_all + pw * 32;
         const int e = 32 * (pq & 1) + lane;
         const uint32_t chunk = e >> 3, inchunk = (e & 7) * 2;
+        // byte offset of this lane's element inside each of the 8 rows of a 1024-byte atom (swizzled)
+        uint32_t rowoff[8];
+#pragma unroll
+        for (int r = 0; r < 8; r++) rowoff[r] = r * 128 + (((chunk ^ r) & 7) << 4) + inchunk;
         const int mcol = (pq * 32 + lane) * p.stride;  // this lane's pixel as a column offset
+        const bool k_tail = (p.K & 63) != 0;
         uint32_t it = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
@@ -622,15 +634,6 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
             const int lane_off = mcol + (w_base - x0);
             for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
                 if ((it & 1) != (uint32_t)grp) continue;
-                // window offset of k column j of this warp's 32, or -1 past K
-                {
-                    const int32_t k = kb * 64 + khalf * 32 + lane;
-                    const int32_t c = k / KHW;
-                    const int32_t r = k - c * KHW;
-                    const int32_t kh = r / p.Kw, kw = r - kh * p.Kw;
-                    ktab[lane] = k < p.K ? ((c - (kb * 64) / KHW) * p.Kh + kh) * BW + kw : -1;
-                }
-                __syncwarp();
                 const uint32_t ws = it % NWIN, wph = (it / NWIN) & 1;
                 const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
                 if (!mbar_wait_warp(&wfull[ws], wph, abort_flag) || !mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
@@ -638,30 +641,38 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
                     break;
                 }
                 const float* wl = reinterpret_cast<const float*>(win_all + ws * Cfg::WIN_BYTES) + lane_off;
+                const int* kt = ktab_all + kb * 64 + khalf * 32;
                 uint8_t* sA = smem + s * Cfg::STAGE_BYTES + (pq >> 1) * 8192 + khalf * 4096;
                 float a[32];
+                if (k_tail && kb == p.k_blocks - 1) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) {
-                    const int4 o = *reinterpret_cast<const int4*>(ktab + j);  // broadcast read
-                    a[j] = o.x >= 0 ? wl[o.x] : 0.f;
-                    a[j + 1] = o.y >= 0 ? wl[o.y] : 0.f;
-                    a[j + 2] = o.z >= 0 ? wl[o.z] : 0.f;
-                    a[j + 3] = o.w >= 0 ? wl[o.w] : 0.f;
+                    for (int j = 0; j < 32; j += 4) {
+                        const int4 o = *reinterpret_cast<const int4*>(kt + j);  // broadcast read
+                        a[j] = o.x >= 0 ? wl[o.x] : 0.f;
+                        a[j + 1] = o.y >= 0 ? wl[o.y] : 0.f;
+                        a[j + 2] = o.z >= 0 ? wl[o.z] : 0.f;
+                        a[j + 3] = o.w >= 0 ? wl[o.w] : 0.f;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        const int4 o = *reinterpret_cast<const int4*>(kt + j);
+                        a[j] = wl[o.x];
+                        a[j + 1] = wl[o.y];
+                        a[j + 2] = wl[o.z];
+                        a[j + 3] = wl[o.w];
+                    }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&wempty[ws]);  // window may be refilled
 #pragma unroll
-                for (int j = 0; j < 32; j++) {
-                    const uint32_t off = (j >> 3) * 1024 + (j & 7) * 128 + (((chunk ^ (j & 7)) & 7) << 4) + inchunk;
-                    *reinterpret_cast<__half*>(sA + off) = __float2half_rn(a[j]);
-                }
-                // all eight warps of the group have written their part of the stage: one thread orders
-                // those generic-proxy writes before the tensor core's async-proxy reads and publishes it
-                asm volatile("bar.sync %0, 256;" ::"r"(1 + grp) : "memory");
-                if (wi == 0 && lane == 0) {
-                    fence_proxy_async_smem();
-                    mbar_arrive(&full[s]);
-                }
+                for (int j = 0; j < 32; j++)
+                    *reinterpret_cast<__half*>(sA + (j >> 3) * 1024 + rowoff[j & 7]) = __float2half_rn(a[j]);
+                // order this warp's generic-proxy writes before the tensor core's async-proxy reads,
+                // then publish its part of the stage (8 warps + the weight copy complete the barrier)
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&full[s]);
             }
         }
     }
@@ -913,7 +924,7 @@ static int run_conv(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN,
     if (r.Ho * r.Wo > INT32_MAX - 256 || r.C * r.Kh * r.Kw > INT32_MAX - 256 || r.C * r.H * r.W > INT32_MAX)
         return fail(NZB_ERR_UNSUPPORTED, "per-image extent exceeds 2^31");
     if (r.Kh > 31 || r.Kw > 31) return fail(NZB_ERR_UNSUPPORTED, "kernel extent above 31");
-    if (r.Wo >= 32 && r.W % 4 == 0 && (reinterpret_cast<uintptr_t>(r.X) & 15) == 0) {
+    if (r.Wo >= 32 && r.W % 4 == 0 && round_up(r.C * r.Kh * r.Kw, 64) <= ConvRowCfg<16, 4>::KTAB_ENTRIES && (reinterpret_cast<uintptr_t>(r.X) & 15) == 0) {
         // row mode if the fp32 window of one k block (a TMA box) fits its shared-memory buffer
         const int tiles_per_row = (int)((r.Wo + 127) / 128);
         const int tile_px = (int)((r.Wo + tiles_per_row - 1) / tiles_per_row);
