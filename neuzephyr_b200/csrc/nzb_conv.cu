@@ -18,7 +18,7 @@
 //   Epilogue: lanes are consecutive pixels, so each channel is written to NCHW with
 //     coalesced stores straight from registers, after bias (per pixel x channel matrix as in
 //     NeuZephyr, or per channel) / accumulate / ReLU.
-// CTA = 704 threads: warp 0 weight TMA, warp 1 MMA issue + tensor-memory owner, warps 2-5
+// (Generic kernel) CTA = 704 threads: warp 0 weight TMA, warp 1 MMA issue + tensor-memory owner, warps 2-5
 // epilogue, warps 6-21 A-tile producers in two groups of eight that fill alternate ring
 // stages (every lane keeps 32 gathers in flight, so global-load latency overlaps between
 // the groups). Persistent over (image, pixel tile, channel tile).
@@ -243,25 +243,31 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
                     for (int i = 0; i < 32 / RPI; i++) bt[(i * RPI + lane / Cfg::CHUNK) * 33 + (lane % Cfg::CHUNK)] = bv[i];
                     __syncwarp();
                 }
-                // values to accumulate onto are fetched together (one memory round trip per chunk)
-                float old[ACC ? Cfg::CHUNK : 1];
-                if constexpr (ACC) {
-#pragma unroll
-                    for (int j = 0; j < Cfg::CHUNK; j++)
-                        old[j] = (pix_ok && co0 + j < p.Cout) ? yb[static_cast<int64_t>(co0 + j) * p.HoWo] : 0.f;
-                }
                 tmem_ld_wait();
-                if (pix_ok) {
+                // values to accumulate onto are fetched 16 at a time (one memory round trip per group,
+                // and few enough registers that the producer warps' budget is not squeezed)
+                constexpr int G = Cfg::CHUNK < 16 ? Cfg::CHUNK : 16;
 #pragma unroll
-                    for (int j = 0; j < Cfg::CHUNK; j++) {
-                        const int32_t co = co0 + j;
-                        if (co < p.Cout) {
-                            float x = __uint_as_float(v[j]);
-                            if constexpr (ACC) x += old[j];
-                            if (p.bias_mode == NZB_BIAS_MATRIX) x += bt[lane * 33 + j];
-                            else if (p.bias_mode == NZB_BIAS_ROW) x += __ldg(p.bias + co);
-                            if (p.relu) x = fmaxf(x, 0.f);
-                            yb[static_cast<int64_t>(co) * p.HoWo] = x;
+                for (int g0 = 0; g0 < Cfg::CHUNK; g0 += G) {
+                    float old[ACC ? G : 1];
+                    if constexpr (ACC) {
+#pragma unroll
+                        for (int j = 0; j < G; j++)
+                            old[j] = (pix_ok && co0 + g0 + j < p.Cout)
+                                         ? yb[static_cast<int64_t>(co0 + g0 + j) * p.HoWo] : 0.f;
+                    }
+                    if (pix_ok) {
+#pragma unroll
+                        for (int j = 0; j < G; j++) {
+                            const int32_t co = co0 + g0 + j;
+                            if (co < p.Cout) {
+                                float x = __uint_as_float(v[g0 + j]);
+                                if constexpr (ACC) x += old[j];
+                                if (p.bias_mode == NZB_BIAS_MATRIX) x += bt[lane * 33 + g0 + j];
+                                else if (p.bias_mode == NZB_BIAS_ROW) x += __ldg(p.bias + co);
+                                if (p.relu) x = fmaxf(x, 0.f);
+                                yb[static_cast<int64_t>(co) * p.HoWo] = x;
+                            }
                         }
                     }
                 }
@@ -373,7 +379,7 @@ conv2d_igemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const ConvP
 // input element is fetched from global memory once per tile and k block instead of once per
 // tap, no per-element bounds test is left, and global-load latency is off the critical path.
 // ---------------------------------------------------------------------------
-template <int BN_, int STAGES_>
+template <int BN_, int STAGES_, int NWIN_>
 struct ConvRowCfg {
     static constexpr int BN = BN_, STAGES = STAGES_;
     static constexpr int A_BYTES = 128 * 64 * 2;
@@ -383,13 +389,13 @@ struct ConvRowCfg {
     static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;
     static constexpr int KTAB_ENTRIES = 4096;  // window offset of every k (whole contraction), built once
     static constexpr int KTAB_BYTES = KTAB_ENTRIES * 4;
-    static constexpr int NWIN = 4;            // window ring depth
+    static constexpr int NWIN = NWIN_;        // window ring depth (windows are fetched this far ahead)
     static constexpr int WIN_BYTES = 16384;   // one window buffer (fp32)
     static constexpr int SMEM_BYTES =
         1024 + STAGES * STAGE_BYTES + NWIN * WIN_BYTES + EPI_BYTES + KTAB_BYTES + BAR_BYTES;
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
     static constexpr int CHUNK = (BN < 32) ? BN : 32;
-    static constexpr int THREADS = 22 * 32;
+    static constexpr int THREADS = 23 * 32;
     static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 };
@@ -471,12 +477,38 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
     const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
-        // ---------------- TMA: image windows (ahead of use) and weight tiles ----------------
+        // ---------------- TMA: weight tiles ----------------
         uint32_t it = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
             const ConvRowTile t = decode_row_tile(p, tile);
             const int32_t zw = p.w_per_sample ? t.img : 0;
+            for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    mbar_arrive_expect_tx(&full[s], Cfg::B_BYTES);
+                    tma_load_3d(smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmW, kb * 64, t.nt * BN, zw, &full[s]);
+                }
+                __syncwarp();
+            }
+        }
+        if (!ok && lane == 0) {
+            const long long t0 = clock64();
+            const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
+            for (uint32_t j = first; j < it; j++)
+                while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1))
+                    if (clock64() - t0 > kWaitCycleLimit) break;
+        }
+    } else if (warp == 22) {
+        // ---------------- TMA: image windows, up to NWIN k blocks ahead of their use ----------------
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            const ConvRowTile t = decode_row_tile(p, tile);
             const int32_t h_base = t.ho * p.stride - p.pad;
             const int32_t w_base = t.wo0 * p.stride - p.pad;
             const int32_t x0 = (w_base >= 0 ? w_base : w_base - 3) / 4 * 4;  // floor to a multiple of 4 elements
@@ -489,16 +521,6 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
                 if (elect_one()) {
                     mbar_arrive_expect_tx(&wfull[ws], p.win_bytes);
                     tma_load_4d(win_all + ws * Cfg::WIN_BYTES, &tmX, x0, h_base, (kb * 64) / KHW, t.img, &wfull[ws]);
-                }
-                __syncwarp();
-                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
-                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
-                    ok = false;
-                    break;
-                }
-                if (elect_one()) {
-                    mbar_arrive_expect_tx(&full[s], Cfg::B_BYTES);
-                    tma_load_3d(smem + s * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmW, kb * 64, t.nt * BN, zw, &full[s]);
                 }
                 __syncwarp();
             }
@@ -582,25 +604,31 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
                     for (int i = 0; i < 32 / RPI; i++) bt[(i * RPI + lane / Cfg::CHUNK) * 33 + (lane % Cfg::CHUNK)] = bv[i];
                     __syncwarp();
                 }
-                // values to accumulate onto are fetched together (one memory round trip per chunk)
-                float old[ACC ? Cfg::CHUNK : 1];
-                if constexpr (ACC) {
-#pragma unroll
-                    for (int j = 0; j < Cfg::CHUNK; j++)
-                        old[j] = (pix_ok && co0 + j < p.Cout) ? yb[static_cast<int64_t>(co0 + j) * p.HoWo] : 0.f;
-                }
                 tmem_ld_wait();
-                if (pix_ok) {
+                // values to accumulate onto are fetched 16 at a time (one memory round trip per group,
+                // and few enough registers that the producer warps' budget is not squeezed)
+                constexpr int G = Cfg::CHUNK < 16 ? Cfg::CHUNK : 16;
 #pragma unroll
-                    for (int j = 0; j < Cfg::CHUNK; j++) {
-                        const int32_t co = co0 + j;
-                        if (co < p.Cout) {
-                            float x = __uint_as_float(v[j]);
-                            if constexpr (ACC) x += old[j];
-                            if (p.bias_mode == NZB_BIAS_MATRIX) x += bt[lane * 33 + j];
-                            else if (p.bias_mode == NZB_BIAS_ROW) x += __ldg(p.bias + co);
-                            if (p.relu) x = fmaxf(x, 0.f);
-                            yb[static_cast<int64_t>(co) * p.HoWo] = x;
+                for (int g0 = 0; g0 < Cfg::CHUNK; g0 += G) {
+                    float old[ACC ? G : 1];
+                    if constexpr (ACC) {
+#pragma unroll
+                        for (int j = 0; j < G; j++)
+                            old[j] = (pix_ok && co0 + g0 + j < p.Cout)
+                                         ? yb[static_cast<int64_t>(co0 + g0 + j) * p.HoWo] : 0.f;
+                    }
+                    if (pix_ok) {
+#pragma unroll
+                        for (int j = 0; j < G; j++) {
+                            const int32_t co = co0 + g0 + j;
+                            if (co < p.Cout) {
+                                float x = __uint_as_float(v[g0 + j]);
+                                if constexpr (ACC) x += old[j];
+                                if (p.bias_mode == NZB_BIAS_MATRIX) x += bt[lane * 33 + g0 + j];
+                                else if (p.bias_mode == NZB_BIAS_ROW) x += __ldg(p.bias + co);
+                                if (p.relu) x = fmaxf(x, 0.f);
+                                yb[static_cast<int64_t>(co) * p.HoWo] = x;
+                            }
                         }
                     }
                 }
@@ -924,7 +952,7 @@ static int run_conv(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN,
     if (r.Ho * r.Wo > INT32_MAX - 256 || r.C * r.Kh * r.Kw > INT32_MAX - 256 || r.C * r.H * r.W > INT32_MAX)
         return fail(NZB_ERR_UNSUPPORTED, "per-image extent exceeds 2^31");
     if (r.Kh > 31 || r.Kw > 31) return fail(NZB_ERR_UNSUPPORTED, "kernel extent above 31");
-    if (r.Wo >= 32 && r.W % 4 == 0 && round_up(r.C * r.Kh * r.Kw, 64) <= ConvRowCfg<16, 4>::KTAB_ENTRIES && (reinterpret_cast<uintptr_t>(r.X) & 15) == 0) {
+    if (r.Wo >= 32 && r.W % 4 == 0 && round_up(r.C * r.Kh * r.Kw, 64) <= ConvRowCfg<16, 4, 6>::KTAB_ENTRIES && (reinterpret_cast<uintptr_t>(r.X) & 15) == 0) {
         // row mode if the fp32 window of one k block (a TMA box) fits its shared-memory buffer
         const int tiles_per_row = (int)((r.Wo + 127) / 128);
         const int tile_px = (int)((r.Wo + tiles_per_row - 1) / tiles_per_row);
@@ -938,13 +966,13 @@ static int run_conv(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN,
         if (box_c > r.C) box_c = r.C;
         const int64_t elems = (int64_t)box_w * r.Kh * box_c;
         const int64_t reach = elems + 128 * r.stride + r.Kw + 4;  // furthest element an unused tile row may read
-        if (box_w <= 256 && r.Kh <= 256 && box_c <= 256 && reach * 4 <= ConvRowCfg<16, 4>::WIN_BYTES * 2 &&
-            elems * 4 <= ConvRowCfg<16, 4>::WIN_BYTES) {
-            if (r.Cout > 128) return run_conv_rows_cfg<ConvRowCfg<256, 2>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
-            if (r.Cout > 64) return run_conv_rows_cfg<ConvRowCfg<128, 4>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
-            if (r.Cout > 32) return run_conv_rows_cfg<ConvRowCfg<64, 4>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
-            if (r.Cout > 16) return run_conv_rows_cfg<ConvRowCfg<32, 4>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
-            return run_conv_rows_cfg<ConvRowCfg<16, 4>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+        if (box_w <= 256 && r.Kh <= 256 && box_c <= 256 && reach * 4 <= ConvRowCfg<16, 4, 6>::WIN_BYTES * 2 &&
+            elems * 4 <= ConvRowCfg<16, 4, 6>::WIN_BYTES) {
+            if (r.Cout > 128) return run_conv_rows_cfg<ConvRowCfg<256, 2, 5>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+            if (r.Cout > 64) return run_conv_rows_cfg<ConvRowCfg<128, 3, 6>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+            if (r.Cout > 32) return run_conv_rows_cfg<ConvRowCfg<64, 4, 6>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+            if (r.Cout > 16) return run_conv_rows_cfg<ConvRowCfg<32, 4, 6>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
+            return run_conv_rows_cfg<ConvRowCfg<16, 4, 6>>(r, W16, Kp, wN, *ds, tiles_per_row, tile_px, box_w, (int)box_c, stream);
         }
     }
     if (r.Cout > 128) return run_conv_cfg<ConvCfg<256, 4>>(r, W16, Kp, wN, *ds, stream);
