@@ -750,52 +750,83 @@ __global__ void __launch_bounds__(256) flip_weights_kernel(__half* __restrict__ 
 // buffer, transposes it and runs GEMMBackwardParallel: src/Nodes.cu:177-181.)
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) im2col_f16_kmajor_kernel(__half* __restrict__ out, const float* __restrict__ x,
-                                                                int64_t C, int64_t H, int64_t W, int64_t Kh, int64_t Kw,
-                                                                int64_t stride, int64_t pad, int64_t Ho, int64_t Wo,
-                                                                int64_t b0, int64_t nb, int64_t K, int64_t Qp) {
-    const int64_t HoWo = Ho * Wo, Q = nb * HoWo;
-    const int64_t pairs = (Q + 1) >> 1;
-    const int64_t total = K * pairs;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t k = i / pairs;
-        const int64_t q0 = (i - k * pairs) << 1;
-        const int64_t c = k / (Kh * Kw), r = k % (Kh * Kw);
-        const int64_t kh = r / Kw, kw = r % Kw;
-        float v[2];
+                                                                int C, int H, int W, int Kh, int Kw, int stride,
+                                                                int pad, int Ho, int Wo, int64_t b0, int nb, int K,
+                                                                int64_t Qp) {
+    // blockIdx.y = k row (one (c, kh, kw) per block row); a thread produces 8 consecutive q
+    // (one 16-byte store), walking (image, ho, wo) incrementally.
+    const int k = blockIdx.y;
+    const int c = k / (Kh * Kw), r = k % (Kh * Kw);
+    const int kh = r / Kw, kw = r % Kw;
+    const int HoWo = Ho * Wo;
+    const int64_t Q = (int64_t)nb * HoWo;
+    __half* orow = out + (int64_t)k * Qp;
+    for (int64_t q0 = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 8; q0 < Q;
+         q0 += (int64_t)gridDim.x * blockDim.x * 8) {
+        int bl = (int)(q0 / HoWo);
+        const int pp = (int)(q0 - (int64_t)bl * HoWo);
+        int ho = pp / Wo, wo = pp - ho * Wo;
+        float v[8];
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int64_t q = q0 + j;
+        for (int j = 0; j < 8; j++) {
             v[j] = 0.f;
-            if (q < Q) {
-                const int64_t bl = q / HoWo, pp = q - bl * HoWo;
-                const int64_t h = (pp / Wo) * stride - pad + kh, w = (pp % Wo) * stride - pad + kw;
-                if (h >= 0 && h < H && w >= 0 && w < W) v[j] = __ldg(x + (((b0 + bl) * C + c) * H + h) * W + w);
+            if (q0 + j < Q) {
+                const int h = ho * stride - pad + kh, w = wo * stride - pad + kw;
+                if ((unsigned)h < (unsigned)H && (unsigned)w < (unsigned)W)
+                    v[j] = __ldg(x + (((b0 + bl) * C + c) * (int64_t)H + h) * W + w);
+            }
+            if (++wo == Wo) {
+                wo = 0;
+                if (++ho == Ho) {
+                    ho = 0;
+                    bl++;
+                }
             }
         }
-        *reinterpret_cast<__half2*>(out + k * Qp + q0) = __floats2half2_rn(v[0], v[1]);
+        uint4 o;
+        __half2 t;
+        t = __floats2half2_rn(v[0], v[1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2half2_rn(v[2], v[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2half2_rn(v[4], v[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2half2_rn(v[6], v[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+        *reinterpret_cast<uint4*>(orow + q0) = o;  // q0 % 8 == 0 and Qp % 64 == 0: aligned, inside the row
     }
 }
 
 __global__ void __launch_bounds__(256) dy_f16_kmajor_kernel(__half* __restrict__ out, const float* __restrict__ dy,
-                                                            int64_t Cout, int64_t HoWo, int64_t b0, int64_t nb,
-                                                            int64_t Qp) {
-    const int64_t Q = nb * HoWo;
-    const int64_t pairs = (Q + 1) >> 1;
-    const int64_t total = Cout * pairs;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t co = i / pairs;
-        const int64_t q0 = (i - co * pairs) << 1;
-        float v[2];
+                                                            int Cout, int HoWo, int64_t b0, int nb, int64_t Qp) {
+    const int co = blockIdx.y;
+    const int64_t Q = (int64_t)nb * HoWo;
+    __half* orow = out + (int64_t)co * Qp;
+    const bool vec = (HoWo % 8 == 0) && ((reinterpret_cast<uintptr_t>(dy) & 15) == 0);
+    for (int64_t q0 = (blockIdx.x * (int64_t)blockDim.x + threadIdx.x) * 8; q0 < Q;
+         q0 += (int64_t)gridDim.x * blockDim.x * 8) {
+        float v[8];
+        if (vec) {
+            const int bl = (int)(q0 / HoWo);
+            const int pp = (int)(q0 - (int64_t)bl * HoWo);
+            const float* src = dy + ((b0 + bl) * Cout + co) * (int64_t)HoWo + pp;
+            const float4 a = __ldg(reinterpret_cast<const float4*>(src));
+            const float4 b = __ldg(reinterpret_cast<const float4*>(src + 4));
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
 #pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int64_t q = q0 + j;
-            v[j] = 0.f;
-            if (q < Q) {
-                const int64_t bl = q / HoWo, pp = q - bl * HoWo;
-                v[j] = __ldg(dy + ((b0 + bl) * Cout + co) * HoWo + pp);
+            for (int j = 0; j < 8; j++) {
+                const int64_t q = q0 + j;
+                v[j] = 0.f;
+                if (q < Q) {
+                    const int64_t bl = q / HoWo, pp = q - bl * HoWo;
+                    v[j] = __ldg(dy + ((b0 + bl) * Cout + co) * (int64_t)HoWo + pp);
+                }
             }
         }
-        *reinterpret_cast<__half2*>(out + co * Qp + q0) = __floats2half2_rn(v[0], v[1]);
+        uint4 o;
+        __half2 t;
+        t = __floats2half2_rn(v[0], v[1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2half2_rn(v[2], v[3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2half2_rn(v[4], v[5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+        t = __floats2half2_rn(v[6], v[7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+        *reinterpret_cast<uint4*>(orow + q0) = o;
     }
 }
 
@@ -1116,15 +1147,22 @@ int nzb_conv2d_backward_weight(const nzb_conv_desc* d, const float* x, const flo
         const int64_t Q = n * HoWo, Qp = round_up(Q, 64);
         __half* colT = reinterpret_cast<__half*>(workspace);
         __half* dyT = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(workspace) + round_up(K * Qp * 2, 256));
-        const int64_t cap = (int64_t)ds->sm_count * 32;
-        int64_t t1 = K * ((Q + 1) / 2), t2 = d->Cout * ((Q + 1) / 2);
-        int64_t g1 = (t1 + 255) / 256, g2 = (t2 + 255) / 256;
-        if (g1 > cap) g1 = cap;
-        if (g2 > cap) g2 = cap;
-        im2col_f16_kmajor_kernel<<<(unsigned)g1, 256, 0, s>>>(colT, x, d->C, d->H, d->W, d->Kh, d->Kw, d->stride,
-                                                             d->pad, Ho, Wo, b0, n, K, Qp);
+        // grid.x covers the contraction in units of 8 per thread, grid.y = the row (k or channel)
+        int64_t gx = (Q / 8 + 255) / 256;
+        const int64_t capx = ((int64_t)ds->sm_count * 32 + K - 1) / K;
+        if (gx > capx) gx = capx;
+        if (gx < 1) gx = 1;
+        if (K > 65535 || d->Cout > 65535) return fail(NZB_ERR_UNSUPPORTED, "more than 65535 weight rows or channels");
+        im2col_f16_kmajor_kernel<<<dim3((unsigned)gx, (unsigned)K), 256, 0, s>>>(
+            colT, x, (int)d->C, (int)d->H, (int)d->W, (int)d->Kh, (int)d->Kw, (int)d->stride, (int)d->pad, (int)Ho,
+            (int)Wo, b0, (int)n, (int)K, Qp);
         NZB_CUDA_TRY(cudaGetLastError());
-        dy_f16_kmajor_kernel<<<(unsigned)g2, 256, 0, s>>>(dyT, dy, d->Cout, HoWo, b0, n, Qp);
+        int64_t gx2 = (Q / 8 + 255) / 256;
+        const int64_t capx2 = ((int64_t)ds->sm_count * 32 + d->Cout - 1) / d->Cout;
+        if (gx2 > capx2) gx2 = capx2;
+        if (gx2 < 1) gx2 = 1;
+        dy_f16_kmajor_kernel<<<dim3((unsigned)gx2, (unsigned)d->Cout), 256, 0, s>>>(dyT, dy, (int)d->Cout, (int)HoWo, b0,
+                                                                                   (int)n, Qp);
         NZB_CUDA_TRY(cudaGetLastError());
         GemmLaunch g{};
         g.A16 = colT; g.B16 = dyT; g.nA = 1; g.nB = 1;
