@@ -80,10 +80,18 @@ int make_plan(const nzb_gemm_desc* d, Plan* pl) {
     pl->nA1 = (e1 > 1 && d->strideA[1] != 0) ? e1 : 1;
     pl->nB0 = (e0 > 1 && d->strideB[0] != 0) ? e0 : 1;
     pl->nB1 = (e1 > 1 && d->strideB[1] != 0) ? e1 : 1;
-    pl->a_bytes = (size_t)round_up(pl->nA0 * pl->nA1 * pl->M * pl->Kp * 2, 256);
-    pl->b_bytes = (size_t)round_up(pl->nB0 * pl->nB1 * pl->N * pl->Kp * 2, 256);
+    pl->Mp = round_up(d->M > 0 ? d->M : 1, kOperandKAlign);
+    pl->Np = round_up(d->N > 0 ? d->N : 1, kOperandKAlign);
     GemmLaunch& g = pl->g;
     g = GemmLaunch{};
+    // A stored K x M and B stored K x N keep their layout (MN-major copies); a narrow right
+    // operand is transposed instead, because an MN-major tile is at least 64 columns wide.
+    g.a_mn = d->transA ? 1 : 0;
+    g.b_mn = (!d->transB && d->N > 32) ? 1 : 0;
+    g.lda16 = pl->Mp;
+    g.ldb16 = pl->Np;
+    pl->a_bytes = (size_t)round_up(pl->nA0 * pl->nA1 * (g.a_mn ? d->K * pl->Mp : pl->M * pl->Kp) * 2, 256);
+    pl->b_bytes = (size_t)round_up(pl->nB0 * pl->nB1 * (g.b_mn ? d->K * pl->Np : pl->N * pl->Kp) * 2, 256);
     g.nA = pl->nA0 * pl->nA1;
     g.nB = pl->nB0 * pl->nB1;
     g.M = d->M; g.N = d->N; g.K = d->K; g.Kp = pl->Kp;
@@ -106,6 +114,29 @@ int make_plan(const nzb_gemm_desc* d, Plan* pl) {
     return NZB_OK;
 }
 
+int stage_operands(Plan* pl, const nzb_gemm_desc* d, const float* A, const float* B, __half* A16, __half* B16,
+                   int sm_count, cudaStream_t stream) {
+    GemmLaunch& g = pl->g;
+    int rc;
+    if (g.a_mn)  // stored K x M: keep rows = k
+        rc = launch_cast_on(sm_count, A, A16, d->K, d->M, d->lda, pl->Mp, 0, pl->nA0, pl->nA1, d->strideA[0],
+                            d->strideA[1], stream);
+    else  // stored M x K
+        rc = launch_cast_on(sm_count, A, A16, d->M, d->K, d->lda, pl->Kp, 0, pl->nA0, pl->nA1, d->strideA[0],
+                            d->strideA[1], stream);
+    if (rc != NZB_OK) return rc;
+    if (g.b_mn)  // stored K x N: keep rows = k
+        rc = launch_cast_on(sm_count, B, B16, d->K, d->N, d->ldb, pl->Np, 0, pl->nB0, pl->nB1, d->strideB[0],
+                            d->strideB[1], stream);
+    else  // stored N x K: plain; stored K x N with few columns: transpose into N rows of K
+        rc = launch_cast_on(sm_count, B, B16, d->N, d->K, d->ldb, pl->Kp, d->transB ? 0 : 1, pl->nB0, pl->nB1,
+                            d->strideB[0], d->strideB[1], stream);
+    if (rc != NZB_OK) return rc;
+    g.A16 = A16;
+    g.B16 = B16;
+    return NZB_OK;
+}
+
 static int run_gemm(const nzb_gemm_desc* d, const float* A, const float* B, float* C, const float* bias, void* ws,
                     size_t ws_bytes, cudaStream_t stream) {
     Plan pl;
@@ -119,16 +150,11 @@ static int run_gemm(const nzb_gemm_desc* d, const float* A, const float* B, floa
     if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(NZB_ERR_WORKSPACE, "workspace must be 256-byte aligned");
     __half* A16 = reinterpret_cast<__half*>(ws);
     __half* B16 = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(ws) + pl.a_bytes);
-    // op(A) rows = M, contraction along columns. Stored M x K -> plain cast; stored K x M -> transpose.
-    rc = launch_cast(A, A16, d->M, d->K, d->lda, pl.Kp, d->transA ? 1 : 0, pl.nA0, pl.nA1, d->strideA[0],
-                     d->strideA[1], stream);
+    DeviceState* ds;
+    rc = get_device_state(&ds);
     if (rc != NZB_OK) return rc;
-    // B' holds N rows of K: stored K x N -> transpose; stored N x K -> plain cast.
-    rc = launch_cast(B, B16, d->N, d->K, d->ldb, pl.Kp, d->transB ? 0 : 1, pl.nB0, pl.nB1, d->strideB[0],
-                     d->strideB[1], stream);
+    rc = stage_operands(&pl, d, A, B, A16, B16, ds->sm_count, stream);
     if (rc != NZB_OK) return rc;
-    pl.g.A16 = A16;
-    pl.g.B16 = B16;
     pl.g.C = C;
     pl.g.bias = bias;
     return launch_gemm(pl.g, stream);
@@ -219,6 +245,7 @@ int nzb_gemm_f16(const nzb_gemm_desc* desc, const void* A16, const void* B16, in
     if (ldk < d.K || ldk % 8 != 0) return fail(NZB_ERR_BAD_ARG, "ldk must be >= K and a multiple of 8");
     if ((reinterpret_cast<uintptr_t>(A16) | reinterpret_cast<uintptr_t>(B16)) & 15) return fail(NZB_ERR_BAD_ARG, "fp16 operands must be 16-byte aligned");
     pl.g.Kp = ldk;
+    pl.g.a_mn = pl.g.b_mn = 0;  // this entry point takes K-major copies
     pl.g.A16 = reinterpret_cast<const __half*>(A16);
     pl.g.B16 = reinterpret_cast<const __half*>(B16);
     pl.g.C = C;

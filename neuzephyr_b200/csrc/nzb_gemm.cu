@@ -3,7 +3,10 @@
 //
 // Stands in for GeneralMatrixMulTensorKernel and its Cutting / CuttingAndCompress
 // passes (NeuZephyr src/OperationKernels.cu:821-883) behind the batched drivers
-// (:914-1144). Operands arrive as K-major fp16 copies: A' [nA][M][Kp], B' [nB][N][Kp].
+// (:914-1144). Operands arrive as fp16 copies, each either K-major (A' [nA][M][Kp],
+// B' [nB][N][Kp]) or MN-major (A' [nA][K][Mp], B' [nB][K][Np], i.e. the source's own
+// row-major layout when it is stored with the contraction along rows), so a transposed
+// operand costs no transposing pass: the tensor core reads either layout.
 //
 // CTA layout (192 threads, persistent over a static round-robin tile list):
 //   warp 0    TMA producer (one lane)
@@ -36,6 +39,7 @@ struct GemmParams {
     int32_t vec4;         // C (and bias) allow aligned float4 access
     int32_t group_m;      // m-tiles per rasterisation group
     int32_t splits;       // CTAs sharing one output tile along the contraction (results added atomically)
+    int32_t a_mn, b_mn;   // operand copy is stored [k][m] / [k][n] (contiguous along the output dimension)
     int64_t total_tiles;
     int* status;
 };
@@ -77,6 +81,48 @@ __device__ __forceinline__ TileCoord decode_tile(const GemmParams& p, int64_t ti
     t.b1 = static_cast<int32_t>(ob % p.out_e1);
     return t;
 }
+
+
+// Operand tile loads for one k block. K-major: one box of `rows` x 64 k. MN-major: rows/64
+// boxes of 64 (m or n) x 64 k, 8192 bytes apart, which is the layout the MN-major
+// descriptor below walks (leading byte offset 8192, 1024 bytes per 8-k group).
+template <int ROWS>
+__device__ __forceinline__ void load_operand(uint8_t* dst, const CUtensorMap* tm, int32_t mn, int32_t k0, int32_t row0,
+                                             int32_t z, uint64_t* bar) {
+    using namespace ptx;
+    if (mn) {
+#pragma unroll
+        for (int j = 0; j < ROWS / 64; j++) tma_load_3d(dst + j * 8192, tm, row0 + j * 64, k0, z, bar);
+    } else {
+        tma_load_3d(dst, tm, k0, row0, z, bar);
+    }
+}
+template <int ROWS>
+__device__ __forceinline__ void load_operand_pair(uint8_t* dst, const CUtensorMap* tm, int32_t mn, int32_t k0,
+                                                  int32_t row0, int32_t z, uint32_t leader_bar) {
+    using namespace ptx;
+    if (mn) {
+#pragma unroll
+        for (int j = 0; j < ROWS / 64; j++) tma_load_3d_pair(dst + j * 8192, tm, row0 + j * 64, k0, z, leader_bar);
+    } else {
+        tma_load_3d_pair(dst, tm, k0, row0, z, leader_bar);
+    }
+}
+
+// Descriptor bits above the start address for a SWIZZLE_128B operand tile.
+//   K-major: rows of 128 bytes, 8-row groups 1024 bytes apart (leading offset unused: 1).
+//   MN-major: 64-element blocks 8192 bytes apart (leading), 8-k groups 1024 bytes apart (stride).
+__device__ __forceinline__ uint64_t desc_high_bits(int32_t mn) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>(mn ? (8192 >> 4) : 1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+// Descriptor address units (16 bytes) per 16-wide k step: 32 bytes along a K-major row,
+// 16 rows of 128 bytes in an MN-major tile.
+__device__ __forceinline__ uint32_t desc_kstep(int32_t mn) { return mn ? 128u : 2u; }
 
 // Drains one finished accumulator quarter (32 tensor-memory lanes x BN columns, owned by
 // this warp) through the warp's shared staging buffer into coalesced global stores, applying
@@ -243,8 +289,8 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 if (elect_one()) {
                     uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
                     mbar_arrive_expect_tx(&full[s], Cfg::STAGE_BYTES);
-                    tma_load_3d(sa, &tmA, kb * 64, t.mt * 128, za, &full[s]);
-                    tma_load_3d(sa + Cfg::A_BYTES, &tmB, kb * 64, t.nt * BN, zb, &full[s]);
+                    load_operand<128>(sa, &tmA, p.a_mn, kb * 64, t.mt * 128, za, &full[s]);
+                    load_operand<BN>(sa + Cfg::A_BYTES, &tmB, p.b_mn, kb * 64, t.nt * BN, zb, &full[s]);
                 }
                 __syncwarp();
                 if (++kb == p.k_blocks) {
@@ -268,7 +314,9 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer (whole warp runs the loop, one elected lane issues) ----------------
-        constexpr uint32_t idesc = make_idesc_f16_f32(128, BN);
+        const uint32_t idesc = make_idesc_f16_f32(128, BN) | (p.a_mn ? 1u << 15 : 0u) | (p.b_mn ? 1u << 16 : 0u);
+        const uint64_t hi_a = desc_high_bits(p.a_mn), hi_b = desc_high_bits(p.b_mn);
+        const uint32_t ka = desc_kstep(p.a_mn), kb_step = desc_kstep(p.b_mn);
         uint32_t it = 0, tcount = 0;
         bool ok = true;
         for (int64_t item = blockIdx.x; item < total_items && ok; item += gridDim.x, tcount++) {
@@ -288,16 +336,15 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
                 }
                 tc_fence_after();
                 const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                const uint64_t da = make_sw128_kmajor_desc(sa);
-                const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                const uint64_t da = hi_a | ((sa & 0x3ffff) >> 4);
+                const uint64_t db = hi_b | (((sa + Cfg::A_BYTES) & 0x3ffff) >> 4);
                 const int32_t ksteps = (kb == p.k_blocks - 1) ? p.last_ksteps : 4;
                 if (++kb == p.k_blocks) kb = 0;
                 if (elect_one()) {
-                    // one k step = 16 halves = 32 bytes = 2 descriptor address units
                     mma_f16_ss(d_tmem, da, db, idesc, kk > kk0 ? 1u : 0u);
-                    if (ksteps > 1) mma_f16_ss(d_tmem, da + 2, db + 2, idesc, 1u);
-                    if (ksteps > 2) mma_f16_ss(d_tmem, da + 4, db + 4, idesc, 1u);
-                    if (ksteps > 3) mma_f16_ss(d_tmem, da + 6, db + 6, idesc, 1u);
+                    if (ksteps > 1) mma_f16_ss(d_tmem, da + ka, db + kb_step, idesc, 1u);
+                    if (ksteps > 2) mma_f16_ss(d_tmem, da + 2 * ka, db + 2 * kb_step, idesc, 1u);
+                    if (ksteps > 3) mma_f16_ss(d_tmem, da + 3 * ka, db + 3 * kb_step, idesc, 1u);
                     mma_commit(&empty[s]);
                 }
                 __syncwarp();
@@ -431,8 +478,8 @@ gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
                             uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
                             const uint32_t leader_full = map_to_cta(smem_u32(&full[s]), 0);
                             if (rank == 0) mbar_arrive_expect_tx(&full[s], 2 * Cfg::STAGE_BYTES);
-                            tma_load_3d_pair(sa, &tmA, kb * 64, row_a, za, leader_full);
-                            tma_load_3d_pair(sa + Cfg::A_BYTES, &tmB, kb * 64, row_b, zb, leader_full);
+                            load_operand_pair<128>(sa, &tmA, p.a_mn, kb * 64, row_a, za, leader_full);
+                            load_operand_pair<128>(sa + Cfg::A_BYTES, &tmB, p.b_mn, kb * 64, row_b, zb, leader_full);
                         }
                         __syncwarp();
                     }
@@ -452,7 +499,9 @@ gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
     } else if (warp == 1) {
         if (rank == 0) {
             // ---------------- MMA issuer (leader only; whole warp runs the loop) ----------------
-            constexpr uint32_t idesc = make_idesc_f16_f32(256, BN);
+            const uint32_t idesc = make_idesc_f16_f32(256, BN) | (p.a_mn ? 1u << 15 : 0u) | (p.b_mn ? 1u << 16 : 0u);
+            const uint64_t hi_a = desc_high_bits(p.a_mn), hi_b = desc_high_bits(p.b_mn);
+            const uint32_t ka = desc_kstep(p.a_mn), kb_step = desc_kstep(p.b_mn);
             uint32_t it = 0, tcount = 0;
             bool ok = true;
             for (int64_t tile = pair; tile < p.total_tiles && ok; tile += npairs, tcount++) {
@@ -469,15 +518,15 @@ gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
                     }
                     tc_fence_after();
                     const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
-                    const uint64_t da = make_sw128_kmajor_desc(sa);
-                    const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                    const uint64_t da = hi_a | ((sa & 0x3ffff) >> 4);
+                    const uint64_t db = hi_b | (((sa + Cfg::A_BYTES) & 0x3ffff) >> 4);
                     const int32_t ksteps = (kb == p.k_blocks - 1) ? p.last_ksteps : 4;
                     if (++kb == p.k_blocks) kb = 0;
                     if (elect_one()) {
                         mma_f16_ss_pair(d_tmem, da, db, idesc, kk > 0 ? 1u : 0u);
-                        if (ksteps > 1) mma_f16_ss_pair(d_tmem, da + 2, db + 2, idesc, 1u);
-                        if (ksteps > 2) mma_f16_ss_pair(d_tmem, da + 4, db + 4, idesc, 1u);
-                        if (ksteps > 3) mma_f16_ss_pair(d_tmem, da + 6, db + 6, idesc, 1u);
+                        if (ksteps > 1) mma_f16_ss_pair(d_tmem, da + ka, db + kb_step, idesc, 1u);
+                        if (ksteps > 2) mma_f16_ss_pair(d_tmem, da + 2 * ka, db + 2 * kb_step, idesc, 1u);
+                        if (ksteps > 3) mma_f16_ss_pair(d_tmem, da + 3 * ka, db + 3 * kb_step, idesc, 1u);
                         mma_commit_pair(&empty[s]);
                     }
                     __syncwarp();
@@ -539,12 +588,35 @@ static int make_operand_map(CUtensorMap* map, const __half* base, int64_t K, int
     return NZB_OK;
 }
 
+// MN-major operand copy [nmat][K][ld]: dimension 0 runs along m (or n), boxes are 64 x 64.
+static int make_operand_map_mn(CUtensorMap* map, const __half* base, int64_t K, int64_t extent, int64_t ld,
+                               int64_t nmat) {
+    EncodeTiledFn enc;
+    int rc = get_encode_tiled(&enc);
+    if (rc != NZB_OK) return rc;
+    cuuint64_t dims[3] = {(cuuint64_t)extent, (cuuint64_t)K, (cuuint64_t)nmat};
+    cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)K * (cuuint64_t)ld * 2};
+    cuuint32_t box[3] = {64, 64, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<__half*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return NZB_OK;
+}
+
+static int make_maps(const GemmLaunch& g, CUtensorMap* tmA, CUtensorMap* tmB, int box_n) {
+    int rc = g.a_mn ? make_operand_map_mn(tmA, g.A16, g.K, g.M, g.lda16, g.nA)
+                    : make_operand_map(tmA, g.A16, g.K, g.Kp, g.M, g.nA, 128);
+    if (rc != NZB_OK) return rc;
+    return g.b_mn ? make_operand_map_mn(tmB, g.B16, g.K, g.N, g.ldb16, g.nB)
+                  : make_operand_map(tmB, g.B16, g.K, g.Kp, g.N, g.nB, box_n);
+}
+
 template <class Cfg>
 static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds, cudaStream_t stream) {
     CUtensorMap tmA, tmB;
-    int rc = make_operand_map(&tmA, g.A16, g.K, g.Kp, g.M, g.nA, 128);
-    if (rc != NZB_OK) return rc;
-    rc = make_operand_map(&tmB, g.B16, g.K, g.Kp, g.N, g.nB, Cfg::BN);
+    int rc = make_maps(g, &tmA, &tmB, Cfg::BN);
     if (rc != NZB_OK) return rc;
     p.tiles_n = (int32_t)((g.N + Cfg::BN - 1) / Cfg::BN);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * p.out_e0 * p.out_e1;
@@ -583,9 +655,7 @@ static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds,
 
 static int launch_pair(const GemmLaunch& g, GemmParams& p, const DeviceState& ds, cudaStream_t stream) {
     CUtensorMap tmA, tmB;
-    int rc = make_operand_map(&tmA, g.A16, g.K, g.Kp, g.M, g.nA, 128);
-    if (rc != NZB_OK) return rc;
-    rc = make_operand_map(&tmB, g.B16, g.K, g.Kp, g.N, g.nB, 128);
+    int rc = make_maps(g, &tmA, &tmB, 128);
     if (rc != NZB_OK) return rc;
     p.tiles_m = (int32_t)((g.M + 255) / 256);
     p.tiles_n = (int32_t)((g.N + 255) / 256);
@@ -647,6 +717,10 @@ int launch_gemm_on(const GemmLaunch& g, const DeviceState& dstate, cudaStream_t 
         v4 = v4 && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0) && (g.bias_ld % 4 == 0);
     p.vec4 = v4 ? 1 : 0;
     p.group_m = 16;
+    p.a_mn = g.a_mn ? 1 : 0;
+    p.b_mn = g.b_mn ? 1 : 0;
+    if (g.a_mn && (g.lda16 < g.M || g.lda16 % 8 != 0)) return fail(NZB_ERR_BAD_ARG, "MN-major A copy needs a leading dimension >= M and a multiple of 8");
+    if (g.b_mn && (g.ldb16 < g.N || g.ldb16 % 8 != 0)) return fail(NZB_ERR_BAD_ARG, "MN-major B copy needs a leading dimension >= N and a multiple of 8");
 
     {
         // few tiles and a long contraction: the single-CTA kernel can split k across CTAs
@@ -658,7 +732,8 @@ int launch_gemm_on(const GemmLaunch& g, const DeviceState& dstate, cudaStream_t 
 
     if (g.N > 128) return launch_cfg<GemmCfg<256, 4>>(g, p, *ds, stream);
     if (g.N > 64) return launch_cfg<GemmCfg<128, 6>>(g, p, *ds, stream);
-    if (g.N > 32) return launch_cfg<GemmCfg<64, 8>>(g, p, *ds, stream);
+    // an MN-major B tile is loaded in boxes of 64 columns: narrower outputs use the 64-wide tile
+    if (g.N > 32 || g.b_mn) return launch_cfg<GemmCfg<64, 8>>(g, p, *ds, stream);
     if (g.N > 16) return launch_cfg<GemmCfg<32, 8>>(g, p, *ds, stream);
     return launch_cfg<GemmCfg<16, 8>>(g, p, *ds, stream);
 }

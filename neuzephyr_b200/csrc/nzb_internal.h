@@ -66,6 +66,10 @@ struct GemmLaunch {
     int64_t bias_ld;
     int32_t accumulate, relu;
     int32_t force_single_cta;  // keep the 128 x BN single-CTA kernel even where the CTA-pair kernel applies
+    // MN-major copies: A' [nA][K][lda16] (contiguous along m) / B' [nB][K][ldb16] (contiguous along n)
+    // instead of the K-major layout above; the leading dimension is a multiple of 8 halves.
+    int32_t a_mn, b_mn;
+    int64_t lda16, ldb16;
 };
 int launch_gemm(const GemmLaunch& g, cudaStream_t stream);
 // Same launches with the device facts supplied by the caller instead of looked up
@@ -84,10 +88,15 @@ int launch_cast_masked(int sm_count, const float* in, const float* mask, __half*
 // Resolved view of a descriptor (nzb_api.cu).
 struct Plan {
     int64_t M, N, K, Kp;
+    int64_t Mp, Np;  // leading dimensions of MN-major copies
     int64_t nA0, nA1, nB0, nB1;  // matrices in the fp16 copies along each batch dimension
     size_t a_bytes, b_bytes;
     GemmLaunch g;
 };
 int make_plan(const nzb_gemm_desc* d, Plan* pl);
+// Stages both fp32 operands of a planned GEMM as fp16 copies (two row-preserving casts; a
+// transposing pass only for a K x N right operand with N <= 32) and fills pl->g.A16 / B16.
+int stage_operands(Plan* pl, const nzb_gemm_desc* d, const float* A, const float* B, __half* A16, __half* B16,
+                   int sm_count, cudaStream_t stream);
 
 }  // namespace nzb

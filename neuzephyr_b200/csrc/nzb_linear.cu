@@ -4,7 +4,9 @@
 // kernel launch per sample (src/OperationKernels.cu:977-999). Here the batch is a GEMM
 // dimension: Y[N x out] = X[N x in] * W^T (+ bias, ReLU) in one launch, and the backward
 //   dX += dY' * W,  dW += dY'^T * X,  db += column sums of dY',  dY' = dY * (Y > 0)
-// runs on the same kernel family with the ReLU mask folded into the operand staging.
+// runs on the same kernel family with the ReLU mask folded into the operand staging. The
+// three fp16 copies (dY', W, X) keep their row-major layout: each GEMM reads them K-major or
+// MN-major as its contraction requires, so no operand is transposed in memory.
 #include <cuda_fp16.h>
 
 #include "nzb_internal.h"
@@ -41,7 +43,7 @@ __global__ void __launch_bounds__(256) bias_grad_rows_kernel(float* __restrict__
 struct LinearSizes {
     int64_t B, In, Out, Inp, Outp, Bp;
     size_t x16, w16, total_fwd;           // forward: X [B][Inp], W [Out][Inp]
-    size_t dy16, dyT16, wT16, xT16, total_bwd;
+    size_t dy16, total_bwd;               // backward: dY' [B][Outp] plus the two above
 };
 static void linear_sizes(const nzb_linear_desc* d, LinearSizes* z) {
     z->B = d->batch; z->In = d->in_features; z->Out = d->out_features;
@@ -49,11 +51,8 @@ static void linear_sizes(const nzb_linear_desc* d, LinearSizes* z) {
     z->x16 = (size_t)round_up(z->B * z->Inp * 2, 256);
     z->w16 = (size_t)round_up(z->Out * z->Inp * 2, 256);
     z->total_fwd = z->x16 + z->w16;
-    z->dy16 = (size_t)round_up(z->B * z->Outp * 2, 256);    // dY' [B][Outp]     (A of dX)
-    z->wT16 = (size_t)round_up(z->In * z->Outp * 2, 256);   // W^T [In][Outp]    (B of dX)
-    z->dyT16 = (size_t)round_up(z->Out * z->Bp * 2, 256);   // dY'^T [Out][Bp]   (A of dW)
-    z->xT16 = (size_t)round_up(z->In * z->Bp * 2, 256);     // X^T [In][Bp]      (B of dW)
-    z->total_bwd = z->dy16 + z->wT16 + z->dyT16 + z->xT16;
+    z->dy16 = (size_t)round_up(z->B * z->Outp * 2, 256);
+    z->total_bwd = z->dy16 + z->w16 + z->x16;
 }
 
 static int check_linear(const nzb_linear_desc* d) {
@@ -114,9 +113,8 @@ int nzb_linear_backward(const nzb_linear_desc* d, const float* x, const float* w
     const float* mask = d->relu ? y : nullptr;
     uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
     __half* dy16 = reinterpret_cast<__half*>(base);
-    __half* wT16 = reinterpret_cast<__half*>(base + z.dy16);
-    __half* dyT16 = reinterpret_cast<__half*>(base + z.dy16 + z.wT16);
-    __half* xT16 = reinterpret_cast<__half*>(base + z.dy16 + z.wT16 + z.dyT16);
+    __half* w16 = reinterpret_cast<__half*>(base + z.dy16);
+    __half* x16 = reinterpret_cast<__half*>(base + z.dy16 + z.w16);
     if (dbias) {
         const int64_t strips = (z.Out + 31) / 32;
         int64_t slices = ((int64_t)ds->sm_count * 8 + strips - 1) / strips;
@@ -126,15 +124,17 @@ int nzb_linear_backward(const nzb_linear_desc* d, const float* x, const float* w
         bias_grad_rows_kernel<<<(unsigned)(strips * slices), 256, 0, s>>>(dbias, dy, mask, z.B, z.Out, rpb);
         NZB_CUDA_TRY(cudaGetLastError());
     }
+    // dY' [B][Outp]: K-major left operand of dX (k = Out) and MN-major left operand of dW (k = B)
+    rc = launch_cast_masked(ds->sm_count, dy, mask, dy16, z.B, z.Out, z.Out, z.Outp, 0, 1, 1, 0, 0, s);
+    if (rc != NZB_OK) return rc;
     if (dx) {
-        // dX[B x In] += dY'[B x Out] * W[Out x In]: A = dY' (rows B, k = Out), B' = W^T [In][Out]
-        rc = launch_cast_masked(ds->sm_count, dy, mask, dy16, z.B, z.Out, z.Out, z.Outp, 0, 1, 1, 0, 0, s);
-        if (rc != NZB_OK) return rc;
-        rc = launch_cast_masked(ds->sm_count, w, nullptr, wT16, z.In, z.Out, z.In, z.Outp, 1, 1, 1, 0, 0, s);
+        // dX[B x In] += dY'[B x Out] * W[Out x In]: W as stored is the MN-major right operand
+        rc = launch_cast_masked(ds->sm_count, w, nullptr, w16, z.Out, z.In, z.In, z.Inp, 0, 1, 1, 0, 0, s);
         if (rc != NZB_OK) return rc;
         GemmLaunch g{};
-        g.A16 = dy16; g.B16 = wT16; g.nA = g.nB = 1;
+        g.A16 = dy16; g.B16 = w16; g.nA = g.nB = 1;
         g.M = z.B; g.N = z.In; g.K = z.Out; g.Kp = z.Outp;
+        g.b_mn = 1; g.ldb16 = z.Inp;
         g.C = dx; g.ldc = z.In;
         g.out_e[0] = g.out_e[1] = g.red_e[0] = g.red_e[1] = 1;
         g.accumulate = 1;
@@ -142,14 +142,14 @@ int nzb_linear_backward(const nzb_linear_desc* d, const float* x, const float* w
         if (rc != NZB_OK) return rc;
     }
     if (dw) {
-        // dW[Out x In] += dY'^T[Out x B] * X[B x In]: A = dY'^T (rows Out, k = B), B' = X^T [In][B]
-        rc = launch_cast_masked(ds->sm_count, dy, mask, dyT16, z.Out, z.B, z.Out, z.Bp, 1, 1, 1, 0, 0, s);
-        if (rc != NZB_OK) return rc;
-        rc = launch_cast_masked(ds->sm_count, x, nullptr, xT16, z.In, z.B, z.In, z.Bp, 1, 1, 1, 0, 0, s);
+        // dW[Out x In] += dY'^T[Out x B] * X[B x In]: both operands as stored, contraction along rows
+        rc = launch_cast_masked(ds->sm_count, x, nullptr, x16, z.B, z.In, z.In, z.Inp, 0, 1, 1, 0, 0, s);
         if (rc != NZB_OK) return rc;
         GemmLaunch g{};
-        g.A16 = dyT16; g.B16 = xT16; g.nA = g.nB = 1;
+        g.A16 = dy16; g.B16 = x16; g.nA = g.nB = 1;
         g.M = z.Out; g.N = z.In; g.K = z.B; g.Kp = z.Bp;
+        g.a_mn = 1; g.lda16 = z.Outp;
+        g.b_mn = 1; g.ldb16 = z.Inp;
         g.C = dw; g.ldc = z.In;
         g.out_e[0] = g.out_e[1] = g.red_e[0] = g.red_e[1] = 1;
         g.accumulate = 1;

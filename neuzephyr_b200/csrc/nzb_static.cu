@@ -95,17 +95,11 @@ int nzb_gemm_static(const nzb_gemm_desc* desc, const float* A, const float* B, f
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     __half* A16 = reinterpret_cast<__half*>(st->scratch);
     __half* B16 = reinterpret_cast<__half*>(static_cast<unsigned char*>(st->scratch) + pl.a_bytes);
-    rc = launch_cast_on(st->sm_count, A, A16, desc->M, desc->K, desc->lda, pl.Kp, desc->transA ? 1 : 0, pl.nA0,
-                        pl.nA1, desc->strideA[0], desc->strideA[1], s);
-    if (rc != NZB_OK) return rc;
-    rc = launch_cast_on(st->sm_count, B, B16, desc->N, desc->K, desc->ldb, pl.Kp, desc->transB ? 0 : 1, pl.nB0,
-                        pl.nB1, desc->strideB[0], desc->strideB[1], s);
+    rc = stage_operands(&pl, desc, A, B, A16, B16, st->sm_count, s);
     if (rc != NZB_OK) return rc;
     DeviceState ds;
     ds.sm_count = st->sm_count;
     ds.status_dev = st->status;
-    pl.g.A16 = A16;
-    pl.g.B16 = B16;
     pl.g.C = C;
     pl.g.bias = bias;
     return launch_gemm_on(pl.g, ds, s);

@@ -74,10 +74,13 @@ def test_config1_seed0_1024(nz):
     assert e_r <= TOL_ROUNDED and e_raw <= TOL_RAW
 
 
+@pytest.mark.parametrize("M,N,K", [(150, 90, 210), (300, 520, 130), (64, 40, 100), (1, 33, 70), (257, 24, 65),
+                                   (520, 300, 1000)])
 @pytest.mark.parametrize("tA,tB", [(False, False), (True, False), (False, True), (True, True)])
-def test_gemm_transposed_operands(nz, tA, tB):
-    M, N, K = 150, 90, 210
-    rng = np.random.default_rng(42)
+def test_gemm_transposed_operands(nz, tA, tB, M, N, K):
+    """Every storage combination: stored K x M / K x N operands are read MN-major by the tensor core
+    (no transposing pass), N <= 32 takes the transposing staging pass."""
+    rng = np.random.default_rng(42 + M)
     A = rng.normal(0, 1, (M, K)).astype(np.float32)
     B = rng.normal(0, 1, (K, N)).astype(np.float32)
     As = np.ascontiguousarray(A.T) if tA else A
