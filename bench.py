@@ -30,7 +30,15 @@ CPU_SAMPLE_ROWS = 4096  # rows of C computed by the CPU baseline per step
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch at this size, from the ncu
 # capture summarised in profiles/gemm_f16_tcgen05_8192x8192x8192.md (algorithmic: 512 MB).
-NCU_DRAM_BYTES_PER_LAUNCH = 1.28e9
+NCU_DRAM_BYTES_PER_LAUNCH = 1.37e9
+
+
+def measured_hbm_gbs():
+    """Measured STREAM-style copy bandwidth of this pool's B200s, else the earlier pool figure."""
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:
+        return 6650.0
 
 
 def measured_peaks(sustained):
@@ -256,10 +264,15 @@ def run_ours(args):
         }
         if world == 1 and not args.no_cpu:
             out["cpu_baseline"] = cpu_baseline()
-        if world == 1 and not args.no_extras:
-            del A, B, Cd
-            torch.cuda.empty_cache()
-            out["other_workloads"] = other_workloads(dev)
+    if not args.no_extras:
+        # every rank takes part: the convolution runs on each rank's own images, the model step
+        # shards one global batch over the ranks with an NCCL gradient all-reduce
+        del A, B, Cd, hA, hB, hC
+        torch.cuda.empty_cache()
+        extras = other_workloads(dev, rank, world, local)
+        if rank == 0:
+            out["other_workloads"] = extras
+    if rank == 0:
         print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -279,11 +292,14 @@ def _time_ms(fn, iters, warm=2):
     return e0.elapsed_time(e1) / iters
 
 
-def other_workloads(dev):
+def other_workloads(dev, rank=0, world=1, local=0):
     """Short measurements of the other configurations of the path (not the headline metric):
     Linear 8192x4096x4096 forward+backward, Conv2d N=32 C=64 224^2 -> 128 (3x3, s1, p1) forward /
-    backward-data / backward-weight, and one training step of the segmentation model."""
+    backward-data / backward-weight per rank (weak scaling: every rank has its own 32 images, times
+    are the max over ranks), and one training step of the segmentation model at global batch 64
+    sharded over the ranks (strong scaling, NCCL gradient all-reduce)."""
     import torch
+    import torch.distributed as dist
     import neuzephyr_b200 as nz
     out = {}
     g = torch.Generator(device=dev)
@@ -311,28 +327,45 @@ def other_workloads(dev):
         y = torch.empty((N_, Co, H_, H_), device=dev)
         dy = torch.randn((N_, Co, H_, H_), device=dev, generator=g)
         dx, dw = torch.zeros_like(x), torch.zeros_like(w)
-        f = _time_ms(lambda: nz.conv2d_forward(x, w, bias, k, k, 1, 1, out=y), 3)
-        bd = _time_ms(lambda: nz.conv2d_backward_data(dy, w, x.shape, k, k, 1, 1, dx), 3)
-        bwt = _time_ms(lambda: nz.conv2d_backward_weight(x, dy, w.shape, k, k, 1, 1, dw), 3)
+        f = _time_ms(lambda: nz.conv2d_forward(x, w, bias, k, k, 1, 1, out=y), 5)
+        bd = _time_ms(lambda: nz.conv2d_backward_data(dy, w, x.shape, k, k, 1, 1, dx), 5)
+        bwt = _time_ms(lambda: nz.conv2d_backward_weight(x, dy, w.shape, k, k, 1, 1, dw), 5)
+        f, bd, bwt = max_over_ranks([f, bd, bwt], device=dev)
         flop = 2.0 * N_ * H_ * H_ * Co * C_ * k * k
-        out["conv2d_n32_c64_224_co128"] = {"forward_ms": f, "backward_data_ms": bd, "backward_weight_ms": bwt,
-                                           "forward_img_per_s": N_ / f * 1e3,
-                                           "fwd_bwd_img_per_s": N_ / (f + bd + bwt) * 1e3,
-                                           "forward_tflops": flop / f / 1e9,
-                                           "forward_hbm_gbs_algorithmic": 4.0 * (x.numel() + y.numel()) / f / 1e6}
+        out["conv2d_n32_c64_224_co128"] = {"images_per_rank": N_, "n_gpus": world, "scaling": "weak",
+                                           "forward_ms": f, "backward_data_ms": bd, "backward_weight_ms": bwt,
+                                           "forward_img_per_s": world * N_ / f * 1e3,
+                                           "fwd_bwd_img_per_s": world * N_ / (f + bd + bwt) * 1e3,
+                                           "forward_tflops_per_gpu": flop / f / 1e9,
+                                           "forward_hbm_gbs_algorithmic_per_gpu":
+                                               4.0 * (x.numel() + y.numel() + bias.numel()) / f / 1e6,
+                                           "forward_hbm_frac_of_measured": 4.0 * (x.numel() + y.numel() + bias.numel())
+                                               / f / 1e6 / measured_hbm_gbs()}
         del x, y, dy, dx, bias
         torch.cuda.empty_cache()
     except Exception as e:  # pragma: no cover
         out["conv2d_n32_c64_224_co128"] = {"error": repr(e)[:200]}
     tool = os.path.join(ROOT, "neuzephyr_b200", "bin", "seg_model")
     if os.path.exists(tool):
+        key = "seg_model_step_batch64"
         try:
-            env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
-            r = subprocess.run([tool, "bench", "16", "1024", "2", "1"], capture_output=True, text=True, timeout=300,
+            # the tool's ranks find each other through a file holding the NCCL id: name it uniquely
+            nonce = [int.from_bytes(os.urandom(4), "little")]
+            if world > 1:
+                dist.broadcast_object_list(nonce, src=0)
+            id_file = "/tmp/nz_dp_bench_%08x.id" % nonce[0]
+            env = dict(os.environ)
+            env.update({"RANK": str(rank), "WORLD_SIZE": str(world), "LOCAL_RANK": str(local),
+                        "NZ_DP_ID_FILE": id_file})
+            r = subprocess.run([tool, "bench", "64", "1024", "2", "1"], capture_output=True, text=True, timeout=600,
                                env=env)
-            out["seg_model_step_batch16_1gpu"] = json.loads(r.stdout.strip().splitlines()[-1])
+            if rank == 0:
+                out[key] = json.loads(r.stdout.strip().splitlines()[-1])
+                out[key]["scaling"] = "strong"
+                if os.path.exists(id_file):
+                    os.remove(id_file)
         except Exception as e:  # pragma: no cover
-            out["seg_model_step_batch16_1gpu"] = {"error": repr(e)[:200]}
+            out[key] = {"error": repr(e)[:200]}
     return out
 
 

@@ -36,13 +36,20 @@ def test_workspace_sizing_and_validation():
     d.batch[0] = d.batch[1] = 1
     n = ctypes.c_size_t(0)
     assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.OK
-    kp = 192
-    assert n.value == (127 * kp * 2 + 255) // 256 * 256 + (129 * kp * 2 + 255) // 256 * 256
+    # A (M x K) is staged K-major [M][Kp]; B (K x N, N > 32) keeps its layout, MN-major [K][Np]
+    kp, np_ = 192, 192
+    assert n.value == (127 * kp * 2 + 255) // 256 * 256 + (131 * np_ * 2 + 255) // 256 * 256
     d.batch[0], d.batch[1] = 4, 3
     d.strideA[0], d.strideA[1] = 3 * 127 * 131, 127 * 131
     d.strideB[0], d.strideB[1] = 0, 131 * 129
     assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.OK
+    assert n.value == (12 * 127 * kp * 2 + 255) // 256 * 256 + (3 * 131 * np_ * 2 + 255) // 256 * 256
+    d.transB = 1  # B stored N x K: K-major copy [N][Kp]
+    d.ldb = 131
+    assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.OK
     assert n.value == (12 * 127 * kp * 2 + 255) // 256 * 256 + (3 * 129 * kp * 2 + 255) // 256 * 256
+    d.transB = 0
+    d.ldb = 129
     d.ldc = 5
     assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.ERR_BAD_ARG
     assert b"leading dimension" in L.nzb_last_error_string()
