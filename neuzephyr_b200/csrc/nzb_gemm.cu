@@ -40,6 +40,7 @@ struct GemmParams {
     int32_t group_m;      // m-tiles per rasterisation group
     int32_t splits;       // CTAs sharing one output tile along the contraction (results added atomically)
     int32_t a_mn, b_mn;   // operand copy is stored [k][m] / [k][n] (contiguous along the output dimension)
+    int32_t trans_out;    // the kernel computes C^T (operands swapped by the host): element (r, c) goes to C[c][r]
     int64_t total_tiles;
     int* status;
 };
@@ -129,7 +130,7 @@ __device__ __forceinline__ uint32_t desc_kstep(int32_t mn) { return mn ? 128u : 
 // accumulate / bias / ReLU. tmem_acc addresses lane quarter and first column.
 template <class Cfg>
 __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t tmem_acc, float* stage, int lane,
-                                                  float* Cb, int32_t row0, int32_t col_tile) {
+                                                  float* Cb, int32_t row0, int32_t col_tile, bool first_split = true) {
     using namespace ptx;
     constexpr int BN = Cfg::BN;
 #pragma unroll 1
@@ -202,7 +203,15 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
                     float x = stage[r * Cfg::EPI_STRIDE + cl];
                     float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
                     if (p.splits > 1) {
-                        atomicAdd(cp, x);  // partial sum of one k slice; C was zeroed or holds the addend
+                        // partial sum of one k slice; C was zeroed or holds the addend. The slice that
+                        // starts the contraction also contributes the bias.
+                        if (first_split) {
+                            if (p.bias_mode == NZB_BIAS_ROW) x += p.bias[gc];
+                            else if (p.bias_mode == NZB_BIAS_COL) x += p.bias[gr];
+                            else if (p.bias_mode == NZB_BIAS_MATRIX)
+                                x += p.bias[static_cast<int64_t>(gr) * p.bias_ld + gc];
+                        }
+                        atomicAdd(cp, x);
                         continue;
                     }
                     if (p.accumulate) x += *cp;
@@ -216,6 +225,56 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
             }
         }
         __syncwarp();
+    }
+}
+
+
+// Transposed drain for the swapped-operand form used when the caller's M is tiny: this
+// kernel's rows are the caller's columns, so the 32 lanes of a warp (32 consecutive rows
+// here) write 32 consecutive floats of one caller row -- coalesced without staging.
+// p.M / p.N are this kernel's (swapped) extents; p.ldc, bias and bias_ld are the caller's.
+template <class Cfg>
+__device__ __forceinline__ void drain_accumulator_transposed(const GemmParams& p, uint32_t tmem_acc, int lane, float* Cb,
+                                                             int32_t row0, int32_t col_tile, bool first_split) {
+    using namespace ptx;
+    constexpr int BN = Cfg::BN;
+    constexpr int G = 16;
+    const int32_t gr = row0 + lane;  // caller's column
+    const bool row_ok = gr < p.M;
+#pragma unroll 1
+    for (int c0 = 0; c0 < BN; c0 += G) {
+        if (col_tile + c0 >= p.N) break;  // warp-uniform
+        uint32_t v[G];
+        tmem_ld_32x16(tmem_acc + c0, v);
+        tmem_ld_wait();
+        float old[G];
+        if (p.accumulate && p.splits == 1) {
+#pragma unroll
+            for (int j = 0; j < G; j++) {
+                const int32_t gc = col_tile + c0 + j;  // caller's row
+                old[j] = (row_ok && gc < p.N) ? Cb[static_cast<int64_t>(gc) * p.ldc + gr] : 0.f;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < G; j++) {
+            const int32_t gc = col_tile + c0 + j;
+            if (!row_ok || gc >= p.N) continue;
+            float x = __uint_as_float(v[j]);
+            float* cp = Cb + static_cast<int64_t>(gc) * p.ldc + gr;
+            const bool with_bias = p.splits == 1 || first_split;
+            if (with_bias) {
+                if (p.bias_mode == NZB_BIAS_ROW) x += p.bias[gr];
+                else if (p.bias_mode == NZB_BIAS_COL) x += p.bias[gc];
+                else if (p.bias_mode == NZB_BIAS_MATRIX) x += p.bias[static_cast<int64_t>(gc) * p.bias_ld + gr];
+            }
+            if (p.splits > 1) {
+                atomicAdd(cp, x);
+                continue;
+            }
+            if (p.accumulate) x += old[j];
+            if (p.relu) x = fmaxf(x, 0.f);
+            *cp = x;
+        }
     }
 }
 
@@ -365,8 +424,12 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
             float* Cb = p.C + t.b0 * p.c_stride0 + t.b1 * p.c_stride1;
             const int32_t row0 = t.mt * 128 + q * 32;
             const int32_t col_tile = t.nt * BN;
-            drain_accumulator<Cfg>(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, stage, lane, Cb,
-                                   row0, col_tile);
+            if (p.trans_out)
+                drain_accumulator_transposed<Cfg>(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, lane,
+                                                  Cb, row0, col_tile, item % p.splits == 0);
+            else
+                drain_accumulator<Cfg>(p, tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN, stage, lane, Cb,
+                                       row0, col_tile, item % p.splits == 0);
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&tempty[acc]);
@@ -627,10 +690,11 @@ static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds,
         attr_set = true;
     }
     // Few output tiles but a long contraction: share each tile among several CTAs along k and
-    // add the partial sums atomically (only without bias / ReLU, which need the full sum).
+    // add the partial sums atomically (the first slice adds the bias; not with ReLU, which needs
+    // the full sum).
     p.splits = 1;
     const int64_t k_iters = (int64_t)p.red_e0 * p.red_e1 * p.k_blocks;
-    if (p.total_tiles * 2 <= ds.sm_count && k_iters >= 16 && p.bias_mode == NZB_BIAS_NONE && !p.relu) {
+    if (p.total_tiles * 2 <= ds.sm_count && k_iters >= 16 && !p.relu) {
         int64_t sp = ds.sm_count / p.total_tiles;
         if (sp > k_iters / 8) sp = k_iters / 8;
         if (sp > 1) {
@@ -641,7 +705,8 @@ static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds,
                 for (int32_t b0 = 0; b0 < p.out_e0; b0++)
                     for (int32_t b1 = 0; b1 < p.out_e1; b1++)
                         NZB_CUDA_TRY(cudaMemset2DAsync(p.C + b0 * p.c_stride0 + b1 * p.c_stride1, (size_t)p.ldc * 4, 0,
-                                                       (size_t)p.N * 4, (size_t)p.M, stream));
+                                                       (size_t)(p.trans_out ? p.M : p.N) * 4,
+                                                       (size_t)(p.trans_out ? p.N : p.M), stream));
             }
         }
     }
@@ -683,9 +748,26 @@ int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
     return launch_gemm_on(g, *ds, stream);
 }
 
-int launch_gemm_on(const GemmLaunch& g, const DeviceState& dstate, cudaStream_t stream) {
+int launch_gemm_on(const GemmLaunch& g_in, const DeviceState& dstate, cudaStream_t stream) {
     const DeviceState* ds = &dstate;
-    if (g.M <= 0 || g.N <= 0) return NZB_OK;
+    if (g_in.M <= 0 || g_in.N <= 0) return NZB_OK;
+    // A tile is 128 rows tall: with a handful of rows and a wide output almost all of the tile
+    // (and of the epilogue) would be padding. Compute C^T instead -- the operands trade places,
+    // which costs nothing because either one may be K-major or MN-major -- and let the
+    // epilogue write the transposed tile.
+    GemmLaunch g = g_in;
+    const bool swap = g_in.M <= 32 && g_in.N >= 4 * g_in.M && g_in.N > 64;
+    if (swap) {
+        g.A16 = g_in.B16; g.B16 = g_in.A16;
+        g.nA = g_in.nB; g.nB = g_in.nA;
+        g.M = g_in.N; g.N = g_in.M;
+        g.a_mn = g_in.b_mn; g.b_mn = g_in.a_mn;
+        g.lda16 = g_in.ldb16; g.ldb16 = g_in.lda16;
+        for (int k = 0; k < 2; k++) {
+            g.a_mul[k] = g_in.b_mul[k];
+            g.b_mul[k] = g_in.a_mul[k];
+        }
+    }
     if (g.K <= 0) return fail(NZB_ERR_UNSUPPORTED, "K = 0 is not supported");
     if (g.M > INT32_MAX - 256 || g.N > INT32_MAX - 256 || g.K > INT32_MAX - 256 || g.nA > INT32_MAX ||
         g.nB > INT32_MAX)
@@ -719,6 +801,7 @@ int launch_gemm_on(const GemmLaunch& g, const DeviceState& dstate, cudaStream_t 
     p.group_m = 16;
     p.a_mn = g.a_mn ? 1 : 0;
     p.b_mn = g.b_mn ? 1 : 0;
+    p.trans_out = swap ? 1 : 0;
     if (g.a_mn && (g.lda16 < g.M || g.lda16 % 8 != 0)) return fail(NZB_ERR_BAD_ARG, "MN-major A copy needs a leading dimension >= M and a multiple of 8");
     if (g.b_mn && (g.ldb16 < g.N || g.ldb16 % 8 != 0)) return fail(NZB_ERR_BAD_ARG, "MN-major B copy needs a leading dimension >= N and a multiple of 8");
 
@@ -726,8 +809,8 @@ int launch_gemm_on(const GemmLaunch& g, const DeviceState& dstate, cudaStream_t 
         // few tiles and a long contraction: the single-CTA kernel can split k across CTAs
         const int64_t tiles1 = (int64_t)p.tiles_m * ((g.N + 255) / 256) * p.out_e0 * p.out_e1;
         const int64_t k_iters = (int64_t)p.red_e0 * p.red_e1 * p.k_blocks;
-        const bool want_split = tiles1 * 2 <= ds->sm_count && k_iters >= 64 && p.bias_mode == NZB_BIAS_NONE && !p.relu;
-        if (g.N > 128 && g.M > 128 && !g.force_single_cta && !want_split) return launch_pair(g, p, *ds, stream);
+        const bool want_split = tiles1 * 2 <= ds->sm_count && k_iters >= 64 && !p.relu;
+        if (g.N > 128 && g.M > 128 && !g.force_single_cta && !want_split && !swap) return launch_pair(g, p, *ds, stream);
     }
 
     if (g.N > 128) return launch_cfg<GemmCfg<256, 4>>(g, p, *ds, stream);

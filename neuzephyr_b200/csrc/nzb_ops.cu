@@ -200,6 +200,62 @@ __global__ void __launch_bounds__(256) avgpool_backward_kernel(float* __restrict
     }
 }
 
+
+// 32-bit-index forms of the two pooling kernels for planes below 2^31 elements: blockIdx.y
+// walks the (batch, channel) planes, so a thread only splits a plane offset into (h, w).
+__global__ void __launch_bounds__(256) avgpool_plane_kernel(float* __restrict__ out, const float* __restrict__ in,
+                                                            int pool, int stride, int pad, int H, int W, int Ho,
+                                                            int Wo, int planes) {
+    const int per = Ho * Wo;
+    for (int bc = blockIdx.y; bc < planes; bc += gridDim.y) {
+        const float* src = in + (int64_t)bc * H * W;
+        float* dst = out + (int64_t)bc * per;
+        for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < per; idx += gridDim.x * blockDim.x) {
+            const int h = idx / Wo, w = idx - h * Wo;
+            const int h0 = h * stride - pad, w0 = w * stride - pad;
+            const int i0 = max(h0, 0), i1 = min(h0 + pool, H), j0 = max(w0, 0), j1 = min(w0 + pool, W);
+            float s = 0.f;
+            for (int i = i0; i < i1; i++) {
+                const float* row = src + (int64_t)i * W;
+                for (int j = j0; j < j1; j++) s += __ldg(row + j);
+            }
+            const int cnt = (i1 - i0) * (j1 - j0);
+            dst[idx] = cnt > 0 ? s / (float)cnt : 0.f;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(256) avgpool_backward_plane_kernel(float* __restrict__ gin,
+                                                                     const float* __restrict__ gout, int pool,
+                                                                     int stride, int pad, int H, int W, int Ho, int Wo,
+                                                                     int planes) {
+    const int per = H * W;
+    const float full = (float)(pool * pool);
+    for (int bc = blockIdx.y; bc < planes; bc += gridDim.y) {
+        const float* g = gout + (int64_t)bc * Ho * Wo;
+        float* dst = gin + (int64_t)bc * per;
+        for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < per; idx += gridDim.x * blockDim.x) {
+            const int hi = idx / W, wi = idx - hi * W;
+            // windows h with h*stride - pad <= hi <= h*stride - pad + pool - 1
+            const int hn = hi + pad - pool + stride, wn = wi + pad - pool + stride;
+            const int h_lo = hn <= 0 ? 0 : hn / stride, w_lo = wn <= 0 ? 0 : wn / stride;
+            const int h_hi = min((hi + pad) / stride, Ho - 1), w_hi = min((wi + pad) / stride, Wo - 1);
+            float s = 0.f;
+            for (int h = h_lo; h <= h_hi; h++) {
+                const int hs = h * stride - pad;
+                const int ch = min(hs + pool, H) - max(hs, 0);
+                const float* grow = g + (int64_t)h * Wo;
+                for (int w = w_lo; w <= w_hi; w++) {
+                    const int ws = w * stride - pad;
+                    const int cw = min(ws + pool, W) - max(ws, 0);
+                    s += __ldg(grow + w) / (pad ? (float)(ch * cw) : full);
+                }
+            }
+            dst[idx] += s;
+        }
+    }
+}
+
 // ---- softmax over each matrix of n elements (:477-523; Tensor::expSum) -----------------------
 // One warp per matrix for n <= 1024 * 32; larger n loops. exp(x - max) / sum: the same value
 // as the reference's exp(x) / sum(exp(x)) whenever the latter does not overflow.
@@ -431,6 +487,17 @@ int nzb_avgpool(float* out, const float* in, int64_t pool, int64_t stride, int64
     NZB_OPS_PROLOGUE();
     const int64_t total = batches * channels * H_out * W_out;
     if (total == 0) return NZB_OK;
+    if (H_in * W_in < INT32_MAX && batches * channels < INT32_MAX && pool < 65536 && stride < 65536 && pad < 65536) {
+        const int64_t per = H_out * W_out, planes = batches * channels;
+        int64_t gx = (per + 255) / 256;
+        const int64_t capx = ((int64_t)ds->sm_count * 16 + planes - 1) / planes;
+        if (gx > capx) gx = capx;
+        const int64_t gy = planes < 65535 ? planes : 65535;
+        avgpool_plane_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, s>>>(out, in, (int)pool, (int)stride, (int)pad,
+                                                                             (int)H_in, (int)W_in, (int)H_out,
+                                                                             (int)W_out, (int)planes);
+        NZB_OPS_EPILOGUE();
+    }
     avgpool_kernel<<<grid_for(total, 256, ds->sm_count), 256, 0, s>>>(out, in, pool, stride, pad, H_in, W_in, H_out,
                                                                       W_out, total);
     NZB_OPS_EPILOGUE();
@@ -443,6 +510,16 @@ int nzb_avgpool_backward(float* gin, const float* gout, int64_t pool, int64_t st
     NZB_OPS_PROLOGUE();
     const int64_t total = batches * channels * H_in * W_in;
     if (total == 0) return NZB_OK;
+    if (H_in * W_in < INT32_MAX && batches * channels < INT32_MAX && pool < 65536 && stride < 65536 && pad < 65536) {
+        const int64_t per = H_in * W_in, planes = batches * channels;
+        int64_t gx = (per + 255) / 256;
+        const int64_t capx = ((int64_t)ds->sm_count * 16 + planes - 1) / planes;
+        if (gx > capx) gx = capx;
+        const int64_t gy = planes < 65535 ? planes : 65535;
+        avgpool_backward_plane_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, s>>>(
+            gin, gout, (int)pool, (int)stride, (int)pad, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+        NZB_OPS_EPILOGUE();
+    }
     avgpool_backward_kernel<<<grid_for(total, 256, ds->sm_count), 256, 0, s>>>(gin, gout, pool, stride, pad, H_in,
                                                                                W_in, H_out, W_out, total);
     NZB_OPS_EPILOGUE();

@@ -22,10 +22,16 @@ public:
     void forward();
     void backward();
     void zeroGrad() const;
-    // steps every node whose output requires a gradient, in insertion order, then zeroes all
-    // gradients (src/Model.cu:20-23, src/ComputeGraph.cu:541-547). `before_step` runs once after
-    // backward and before the first optimizer step (the data-parallel all-reduce hooks in here).
+    // Optimizer step, in insertion order, on the nodes whose output requires a gradient
+    // (src/ComputeGraph.cu:541-547); gradients are left as they are (Model::update zeroes them,
+    // src/Model.cu:20-23). `before_step` runs once after backward and before the first optimizer
+    // step (the data-parallel all-reduce hooks in here).
+    // The reference also steps every intermediate node (activations), whose values the next
+    // forward() overwrites: that is several full passes over the largest tensors of the model
+    // for no effect on training, so it is off by default. stepIntermediateNodes(true) restores
+    // it for code that reads a hidden node's output between update() and the next forward().
     void update(opt::Optimizer* optimizer, const std::function<void()>& before_step = nullptr) const;
+    void stepIntermediateNodes(bool on) { step_intermediates_ = on; }
     float getLoss() const;
     const std::vector<nodes::Node*>& getNodes() const { return nodes_; }
     const std::vector<nodes::io::OutputNode*>& getOutputs() const { return outputs_; }
@@ -35,6 +41,7 @@ private:
     std::vector<nodes::io::InputNode*> inputs_;
     std::vector<nodes::io::OutputNode*> outputs_;
     bool sorted_ = false;
+    bool step_intermediates_ = false;
 };
 
 }  // namespace nz::graph

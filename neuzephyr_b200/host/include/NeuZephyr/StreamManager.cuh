@@ -5,18 +5,24 @@
 // round-robin under a mutex; every operation first makes its stream wait on the pending
 // events of the pointers it touches and afterwards records an event keyed by the pointers it
 // wrote; syncData(ptr) blocks the host until a pointer has no pending work; sync() drains
-// every stream; allocation and release are stream-ordered.
+// every stream; allocation and release do not block the host and are ordered with the work
+// on the buffer.
 // Deliberate differences: readers are tracked as well as writers (the reference orders a
 // freeAsync only after writers, so a buffer can be released under a kernel still reading
 // it); malloc takes a byte count and allocates exactly that (the reference multiplies by
 // sizeof(T) a second time); events are retired by polling instead of one host callback per
-// launch.
+// launch; released blocks go to a size-keyed cache owned by the manager instead of back
+// to the driver (the reference calls cudaMallocAsync / cudaFreeAsync per tensor, whose pool,
+// with buffers allocated and released on 16 rotating streams, re-maps memory every training
+// step). A cached block keeps the pending events of its last owner, so whoever gets it next
+// is ordered after that owner's kernels by the same per-pointer event mechanism.
 #pragma once
 #include <cuda_runtime.h>
 
 #include <cstddef>
 #include <functional>
 #include <initializer_list>
+#include <map>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -75,6 +81,10 @@ public:
     void* scratch(size_t bytes, cudaStream_t stream);
     void releaseScratch(void* p, cudaStream_t stream);
 
+    // hands every cached block back to the driver (after draining all streams)
+    void trim();
+    size_t cachedBytes();
+
 private:
     StreamManager(size_t n_streams, size_t n_events);
     struct Pending {
@@ -88,6 +98,12 @@ private:
     std::mutex mu_;
     std::unordered_map<const void*, Pending> pending_;
     EventPool events_;
+
+    void* allocBlock(size_t bytes);
+    void releaseBlock(void* p);
+    std::multimap<size_t, void*> cache_;         // free blocks by size
+    std::unordered_map<void*, size_t> live_;     // blocks handed out
+    size_t cached_bytes_ = 0;
 };
 
 extern template class StreamManager<float>;

@@ -68,8 +68,7 @@ void ComputeGraph::zeroGrad() const {
 void ComputeGraph::update(opt::Optimizer* optimizer, const std::function<void()>& before_step) const {
     if (before_step) before_step();
     for (Node* n : nodes_)
-        if (n->output->requiresGrad()) optimizer->step(n);
-    zeroGrad();
+        if (n->output->requiresGrad() && (step_intermediates_ || n->inputs.empty())) optimizer->step(n);
 }
 float ComputeGraph::getLoss() const {
     if (outputs_.empty()) throw std::runtime_error("No output node");
@@ -146,6 +145,7 @@ void Model::syncGradients() {
 }
 void Model::update(opt::Optimizer* optimizer) {
     computeGraph.update(optimizer, [this]() { syncGradients(); });
+    computeGraph.zeroGrad();
     grads_synced_ = false;
 }
 Tensor::value_type Model::getLoss() const { return computeGraph.getLoss(); }

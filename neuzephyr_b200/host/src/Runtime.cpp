@@ -36,10 +36,9 @@ StreamManager<T>::StreamManager(size_t n_streams, size_t n_events) : events_(n_e
 }
 template <typename T>
 StreamManager<T>::~StreamManager() {
-    for (auto s : streams_) {
-        cudaStreamSynchronize(s);
-        cudaStreamDestroy(s);
-    }
+    for (auto s : streams_) cudaStreamSynchronize(s);
+    for (auto& kv : cache_) cudaFree(kv.second);
+    for (auto s : streams_) cudaStreamDestroy(s);
 }
 template <typename T>
 cudaStream_t StreamManager<T>::getStream() {
@@ -132,24 +131,71 @@ cudaStream_t StreamManager<T>::run(std::initializer_list<const void*> writes,
     return s;
 }
 template <typename T>
+void* StreamManager<T>::allocBlock(size_t bytes) {
+    bytes = (std::max<size_t>(bytes, 1) + 511) / 512 * 512;
+    // a cached block may be somewhat larger than asked: up to 2x for small ones, 1/8 over for large
+    const size_t limit = bytes < (size_t(1) << 20) ? 2 * bytes : bytes + bytes / 8;
+    {
+        std::lock_guard<std::mutex> lk(mu_);
+        auto it = cache_.lower_bound(bytes);
+        if (it != cache_.end() && it->first <= limit) {
+            void* p = it->second;
+            live_[p] = it->first;
+            cached_bytes_ -= it->first;
+            cache_.erase(it);
+            return p;
+        }
+    }
+    void* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes);
+    if (e == cudaErrorMemoryAllocation) {
+        cudaGetLastError();
+        trim();
+        e = cudaMalloc(&p, bytes);
+    }
+    CHECK(e);
+    std::lock_guard<std::mutex> lk(mu_);
+    live_[p] = bytes;
+    return p;
+}
+template <typename T>
+void StreamManager<T>::releaseBlock(void* p) {
+    std::lock_guard<std::mutex> lk(mu_);
+    auto it = live_.find(p);
+    if (it == live_.end()) return;  // not handed out by this manager
+    cache_.emplace(it->second, p);
+    cached_bytes_ += it->second;
+    live_.erase(it);
+    // the block's pending events stay in pending_: its next owner waits on them
+}
+template <typename T>
+void StreamManager<T>::trim() {
+    sync();
+    std::lock_guard<std::mutex> lk(mu_);
+    for (auto& kv : cache_) {
+        auto it = pending_.find(kv.second);
+        if (it != pending_.end()) {
+            for (auto e : it->second.writers) events_.release(e);
+            for (auto e : it->second.readers) events_.release(e);
+            pending_.erase(it);
+        }
+        CHECK(cudaFree(kv.second));
+    }
+    cache_.clear();
+    cached_bytes_ = 0;
+}
+template <typename T>
+size_t StreamManager<T>::cachedBytes() {
+    std::lock_guard<std::mutex> lk(mu_);
+    return cached_bytes_;
+}
+template <typename T>
 void StreamManager<T>::malloc(T** ptr, size_t bytes) {
-    cudaStream_t s = getStream();
-    CHECK(cudaMallocAsync(reinterpret_cast<void**>(ptr), bytes ? bytes : 4, s));
-    recordData(*ptr, s);
+    *ptr = static_cast<T*>(allocBlock(bytes));
 }
 template <typename T>
 void StreamManager<T>::free(T* ptr) {
-    if (!ptr) return;
-    cudaStream_t s = getStream();
-    streamWait(ptr, s, true);  // after writers AND readers
-    CHECK(cudaFreeAsync(ptr, s));
-    std::lock_guard<std::mutex> lk(mu_);
-    auto it = pending_.find(ptr);
-    if (it != pending_.end()) {
-        for (auto e : it->second.writers) events_.release(e);
-        for (auto e : it->second.readers) events_.release(e);
-        pending_.erase(it);
-    }
+    if (ptr) releaseBlock(ptr);
 }
 template <typename T>
 void StreamManager<T>::memset(T* ptr, int value, size_t bytes) {
@@ -170,13 +216,15 @@ void StreamManager<T>::memcpy(void* dst, const void* src, size_t bytes, cudaMemc
 }
 template <typename T>
 void* StreamManager<T>::scratch(size_t bytes, cudaStream_t stream) {
-    void* p = nullptr;
-    CHECK(cudaMallocAsync(&p, bytes ? bytes : 256, stream));
+    void* p = allocBlock(bytes ? bytes : 256);
+    streamWait(p, stream, true);  // after whatever the block's previous owner left pending
     return p;
 }
 template <typename T>
 void StreamManager<T>::releaseScratch(void* p, cudaStream_t stream) {
-    if (p) CHECK(cudaFreeAsync(p, stream));
+    if (!p) return;
+    recordData(p, stream);
+    releaseBlock(p);
 }
 
 template class StreamManager<float>;

@@ -6,6 +6,7 @@
 //
 //   seg_model bench  <global_batch> <size> <steps> <warmup>   one JSON line on rank 0
 //   seg_model check  <global_batch> <size>                    sharded step == full-batch step (rank 0 verifies)
+//   seg_model phases <global_batch> <size> <steps> <warmup>   as bench, preceded by a line with forward / backward / update times
 #include <NeuZephyr/Model.cuh>
 
 #include <chrono>
@@ -153,6 +154,30 @@ int main(int argc, char** argv) {
             };
             for (int i = 0; i < warmup; i++) step();
             sm.sync();
+            if (mode == "phases") {
+                // forward / backward / update timed apart, each closed by a full synchronisation
+                double tf = 0, tb = 0, tu = 0;
+                for (int i = 0; i < steps; i++) {
+                    CHECK(cudaDeviceSynchronize());
+                    const double a = now_ms();
+                    model.forward();
+                    sm.sync();
+                    CHECK(cudaDeviceSynchronize());
+                    const double b2 = now_ms();
+                    model.backward();
+                    sm.sync();
+                    CHECK(cudaDeviceSynchronize());
+                    const double c = now_ms();
+                    model.update(&adam);
+                    sm.sync();
+                    CHECK(cudaDeviceSynchronize());
+                    const double d = now_ms();
+                    tf += b2 - a; tb += c - b2; tu += d - c;
+                }
+                if (rank == 0)
+                    printf("{\"mode\": \"phases\", \"world\": %d, \"global_batch\": %zu, \"size\": %zu, \"forward_ms\": %.3f, "
+                           "\"backward_ms\": %.3f, \"update_ms\": %.3f}\n", world, B, S, tf / steps, tb / steps, tu / steps);
+            }
             if (comm) comm->barrier();
             const double t0 = now_ms();
             for (int i = 0; i < steps; i++) step();

@@ -475,6 +475,55 @@ TEST(Model, LossDecreasesOverSteps) {
     EXPECT_TRUE(last < first);
 }
 
+TEST(Model, UpdateStepsParametersOnlyUnlessAsked) {
+    // The reference steps every node that requires a gradient (src/ComputeGraph.cu:541-547),
+    // activations included; here that is opt-in because forward() overwrites them anyway.
+    for (int all = 0; all < 2; all++) {
+        SegModel m(2, 12, true);
+        auto x = uniform(2 * 3 * 12 * 12, -1, 1, 60);
+        std::vector<float> tg(2 * 16, 1.f);
+        m.input.dataInject(x.begin(), x.end());
+        m.target.dataInject(tg.begin(), tg.end());
+        for (auto* p : m.parameters()) {
+            auto w = uniform(p->output->size(), -0.1f, 0.1f, 61);
+            p->dataInject(w.begin(), w.end());
+        }
+        m.graph().zeroGrad();
+        m.graph().stepIntermediateNodes(all != 0);
+        m.forward();
+        m.backward();
+        const auto hidden_before = m.out->inputs[0]->output->hostData();  // the Linear node's output
+        const auto w_before = m.parameters()[0]->output->hostData();
+        opt::Adam adam(0.01f, 0.9f, 0.999f);
+        m.update(&adam);
+        const auto hidden_after = m.out->inputs[0]->output->hostData();
+        const auto w_after = m.parameters()[0]->output->hostData();
+        bool hidden_same = true, w_same = true;
+        for (size_t i = 0; i < hidden_before.size(); i++) hidden_same &= (hidden_before[i] == hidden_after[i]);
+        for (size_t i = 0; i < w_before.size(); i++) w_same &= (w_before[i] == w_after[i]);
+        EXPECT_TRUE(!w_same);
+        EXPECT_EQ(hidden_same, all == 0);
+    }
+    // ComputeGraph::update leaves gradients alone; Model::update zeroes them (src/Model.cu:20-23)
+    SegModel m(2, 12, true);
+    auto x = uniform(2 * 3 * 12 * 12, -1, 1, 62);
+    std::vector<float> tg(2 * 16, 0.f);
+    m.input.dataInject(x.begin(), x.end());
+    m.target.dataInject(tg.begin(), tg.end());
+    for (auto* p : m.parameters()) {
+        auto w = uniform(p->output->size(), -0.1f, 0.1f, 63);
+        p->dataInject(w.begin(), w.end());
+    }
+    m.graph().zeroGrad();
+    m.forward();
+    m.backward();
+    opt::Adam adam(0.01f, 0.9f, 0.999f);
+    m.graph().update(&adam);
+    bool any = false;
+    for (float v : m.parameters()[0]->output->hostGrad()) any |= (v != 0.f);
+    EXPECT_TRUE(any);
+}
+
 TEST(StreamManager, OrderingAndSync) {
     auto& sm = cuStrm::StreamManager<float>::Instance();
     EXPECT_EQ(sm.streamCount(), (size_t)16);

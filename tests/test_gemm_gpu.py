@@ -113,6 +113,42 @@ def test_gemm_epilogue_bias_relu_accumulate(nz):
     check_status(nz)
 
 
+@pytest.mark.parametrize("M,N,K", [(16, 5000, 16), (7, 300, 5000), (32, 129, 100), (1, 4096, 4096), (3, 70, 33),
+                                   (16, 16, 40000)])
+@pytest.mark.parametrize("tA,tB", [(False, False), (True, True)])
+def test_gemm_tiny_m_and_split_k_epilogues(nz, M, N, K, tA, tB):
+    """A few rows against a wide output run with the operands swapped and a transposed epilogue; few
+    tiles with a long contraction are shared among CTAs along k (the first slice adds the bias)."""
+    from neuzephyr_b200 import _capi as C
+    rng = np.random.default_rng(M * 7919 + N + K)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    As = dev(np.ascontiguousarray(A.T) if tA else A)
+    Bs = dev(np.ascontiguousarray(B.T) if tB else B)
+    ref = O.gemm_f64(A, B, True)
+    # one accumulator chain over a very long contraction carries fp32 accumulation error that grows with K
+    tol = max(TOL_ROUNDED, 5e-9 * K)
+    brow = rng.normal(0, 1, N).astype(np.float32)
+    bcol = rng.normal(0, 1, M).astype(np.float32)
+    bmat = rng.normal(0, 1, (M, N)).astype(np.float32)
+    got = nz.gemm(As, Bs, transA=tA, transB=tB).cpu().numpy()
+    assert emax(got, ref) <= tol
+    got = nz.gemm(As, Bs, transA=tA, transB=tB, bias=dev(brow), bias_mode=C.BIAS_ROW).cpu().numpy()
+    assert emax(got, ref + brow[None, :]) <= tol
+    got = nz.gemm(As, Bs, transA=tA, transB=tB, bias=dev(bcol), bias_mode=C.BIAS_COL, relu=True).cpu().numpy()
+    assert emax(got, np.maximum(ref + bcol[:, None], 0)) <= tol
+    got = nz.gemm(As, Bs, transA=tA, transB=tB, bias=dev(bmat), bias_mode=C.BIAS_MATRIX).cpu().numpy()
+    assert emax(got, ref + bmat) <= tol
+    c0 = rng.normal(0, 1, (M, N)).astype(np.float32)
+    out = dev(c0)
+    nz.gemm(As, Bs, transA=tA, transB=tB, out=out, accumulate=True)
+    assert emax(out.cpu().numpy(), ref + c0) <= tol
+    out = dev(c0)
+    nz.gemm(As, Bs, transA=tA, transB=tB, out=out, accumulate=True, bias=dev(brow), bias_mode=C.BIAS_ROW)
+    assert emax(out.cpu().numpy(), ref + c0 + brow[None, :]) <= tol
+    check_status(nz)
+
+
 def test_reference_kat_matmul_forward(nz):
     """TensorCore.TensorCoreGEMMTest / NodeBasic.MatMulForward literals; integers are exact in fp16."""
     g = GOLD["matmul_forward"]
