@@ -718,6 +718,347 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
 }
 
 // ---------------------------------------------------------------------------
+// TMA im2col mode (stride 1, Kh and Kw <= 4, output rows of at least 32 pixels): the
+// tensor core's A tile is delivered by TMA alone, no thread touches it.
+//
+// The input is staged once per call as Kw fp16 copies, copy kw holding the image shifted
+// left by kw - pad columns with the horizontal padding written as zeros:
+//   XS[kw][img][c][h][w'] = half(X[img][c][h][w' + kw - pad])        (row pitch Wp, 16-byte multiple)
+// With that, the im2col slice for tap column kw, channels [16*cb, +16), all Kh tap rows and
+// 64 consecutive output pixels of output row ho is the dense box
+//   XS[kw][img][16*cb .. +16][ho - pad .. + Kh][wo0 .. + 64]
+// of a 5-D tensor map: 16*Kh rows (k = ci*Kh + kh) of 64 pixels, which with SWIZZLE_128B is
+// exactly the M-major operand layout of tcgen05.mma (vertical padding = TMA zero fill). A
+// k block is one (kw, cb) pair; the contraction order is k' = ((kw*CB + cb)*16 + ci)*Kh + kh
+// and the weights are staged in that order (channels padded to a multiple of 16 with zeros,
+// every block padded to 64 columns).
+//
+// CTA = 192 threads: warp 0 TMA (two image boxes + one weight box per stage), warp 1 MMA,
+// warps 2-5 epilogue straight into NCHW. Narrow channel tiles leave room for two CTAs per SM.
+// ---------------------------------------------------------------------------
+struct ConvTmaParams {
+    float* Y;
+    const float* bias;
+    int32_t Cout, Kh, Kw, pad;
+    int32_t Ho, Wo, HoWo;
+    int32_t cblks;     // ceil(C / 16)
+    int32_t k_blocks;  // Kw * cblks
+    int32_t tiles_per_row, tiles_n;
+    int32_t w_per_sample, img0;  // img0: first image of this chunk (index into Y / weights; XS is chunk-local)
+    int32_t bias_mode, relu;
+    uint32_t stage_tx;  // bytes one stage's three copies deliver
+    int64_t total_tiles;
+    int* status;
+};
+
+template <int BN_, int STAGES_, int MINB_>
+struct ConvTmaCfg {
+    static constexpr int BN = BN_, STAGES = STAGES_, MIN_BLOCKS = MINB_;
+    static constexpr int A_BYTES = 2 * 8192;  // two 64-pixel blocks of up to 64 k rows
+    static constexpr int B_BYTES = BN * 64 * 2;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
+    static constexpr int CHUNK = (BN < 32) ? BN : 32;
+    static constexpr int THREADS = 6 * 32;
+    static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+    static_assert((SMEM_BYTES + 1024) * MINB_ <= 233472, "exceeds the 228 KB shared memory of an sm_100 SM");
+    static_assert(TMEM_COLS * MINB_ <= 512, "exceeds the tensor memory of an SM");
+};
+
+struct ConvTmaTile {
+    int32_t img, ho, wo0, npx, nt;
+};
+__device__ __forceinline__ ConvTmaTile decode_tma_tile(const ConvTmaParams& p, int64_t tile) {
+    ConvTmaTile t;
+    t.nt = static_cast<int32_t>(tile % p.tiles_n);
+    int64_t r = tile / p.tiles_n;
+    const int32_t seg = static_cast<int32_t>(r % p.tiles_per_row);
+    r /= p.tiles_per_row;
+    t.ho = static_cast<int32_t>(r % p.Ho);
+    t.img = static_cast<int32_t>(r / p.Ho);
+    t.wo0 = seg * 128;
+    t.npx = min(128, p.Wo - t.wo0);
+    return t;
+}
+
+template <class Cfg, bool ACC>
+__global__ void __launch_bounds__(Cfg::THREADS, Cfg::MIN_BLOCKS)
+conv2d_tma_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX,
+                          const ConvTmaParams p) {
+    using namespace ptx;
+    constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    float* epi = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* tfull = bars + 2 * STAGES;
+    uint64_t* tempty = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmW);
+        prefetch_tensormap(&tmX);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tfull[a], 1);
+            mbar_init(&tempty[a], 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA: image boxes and weight tiles ----------------
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+            const ConvTmaTile t = decode_tma_tile(p, tile);
+            const int32_t zw = p.w_per_sample ? p.img0 + t.img : 0;
+            int32_t kw = 0, cb = 0;
+            for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
+                    mbar_arrive_expect_tx(&full[s], p.stage_tx);
+                    tma_load_5d(sa, &tmX, t.wo0, t.ho - p.pad, cb * 16, t.img, kw, &full[s]);
+                    tma_load_5d(sa + 8192, &tmX, t.wo0 + 64, t.ho - p.pad, cb * 16, t.img, kw, &full[s]);
+                    tma_load_3d(sa + Cfg::A_BYTES, &tmW, kb * 64, t.nt * BN, zw, &full[s]);
+                }
+                __syncwarp();
+                if (++cb == p.cblks) {
+                    cb = 0;
+                    kw++;
+                }
+            }
+        }
+        if (!ok && lane == 0) {
+            const long long t0 = clock64();
+            const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
+            for (uint32_t j = first; j < it; j++)
+                while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1))
+                    if (clock64() - t0 > kWaitCycleLimit) break;
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue: Kh steps of 16 k rows per block ----------------
+        constexpr uint32_t idesc = make_idesc_conv(128, BN);
+        uint32_t it = 0, tcount = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, tcount++) {
+            const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+            if (!mbar_wait_warp(&tempty[acc], aph ^ 1, abort_flag)) break;
+            tc_fence_after();
+            const uint32_t d_tmem = tmem_base + acc * BN;
+            for (int32_t kb = 0; kb < p.k_blocks; kb++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                const uint64_t da = make_sw128_mmajor_desc(sa);
+                const uint64_t db = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                if (elect_one()) {
+                    mma_f16_ss(d_tmem, da, db, idesc, kb > 0 ? 1u : 0u);
+                    if (p.Kh > 1) mma_f16_ss(d_tmem, da + 128, db + 2, idesc, 1u);
+                    if (p.Kh > 2) mma_f16_ss(d_tmem, da + 256, db + 4, idesc, 1u);
+                    if (p.Kh > 3) mma_f16_ss(d_tmem, da + 384, db + 6, idesc, 1u);
+                    mma_commit(&empty[s]);
+                }
+                __syncwarp();
+            }
+            if (ok && elect_one()) mma_commit(&tfull[acc]);
+            __syncwarp();
+        }
+    } else {
+        // ---------------- epilogue: lanes are pixels, one coalesced store per channel ----------------
+        const int q = warp & 3;
+        float* bt = epi + (warp - 2) * 32 * 33;
+        uint32_t tcount = 0;
+        for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, tcount++) {
+            const ConvTmaTile t = decode_tma_tile(p, tile);
+            const uint32_t acc = tcount & 1, aph = (tcount >> 1) & 1;
+            if (!mbar_wait_relaxed(&tfull[acc], aph, abort_flag)) break;
+            tc_fence_after();
+            const int32_t m0 = q * 32;
+            const int32_t pix0 = t.ho * p.Wo + t.wo0 + m0;
+            const int32_t pix = pix0 + lane;
+            const bool pix_ok = m0 + lane < t.npx;
+            float* yb = p.Y + (static_cast<int64_t>(p.img0 + t.img) * p.Cout) * p.HoWo + pix;
+            if (m0 < t.npx) {  // warp-uniform: this quarter of the tile holds pixels
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += Cfg::CHUNK) {
+                    const int32_t co0 = t.nt * BN + c0;
+                    if (co0 >= p.Cout) break;
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c0;
+                    uint32_t v[Cfg::CHUNK];
+                    if constexpr (Cfg::CHUNK == 32) tmem_ld_32x32(taddr, v);
+                    else tmem_ld_32x16(taddr, v);
+                    if (p.bias_mode == NZB_BIAS_MATRIX) {
+                        // bias is [pixel][channel]: read with lanes along channels (coalesced), transpose
+                        // through shared memory so that each lane gets its own pixel's row
+                        constexpr int RPI = 32 / Cfg::CHUNK;
+                        const int32_t co = co0 + (lane % Cfg::CHUNK);
+                        float bv[32 / RPI];
+#pragma unroll
+                        for (int i = 0; i < 32 / RPI; i++) {
+                            const int r = i * RPI + lane / Cfg::CHUNK;
+                            bv[i] = (m0 + r < t.npx && co < p.Cout)
+                                        ? __ldg(p.bias + static_cast<int64_t>(pix0 + r) * p.Cout + co) : 0.f;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 32 / RPI; i++)
+                            bt[(i * RPI + lane / Cfg::CHUNK) * 33 + (lane % Cfg::CHUNK)] = bv[i];
+                        __syncwarp();
+                    }
+                    tmem_ld_wait();
+                    // Straight-line inner loops: every mode decision is taken once per group of 16
+                    // channels, not per element (a branch per element costs more than the store).
+                    constexpr int G = Cfg::CHUNK < 16 ? Cfg::CHUNK : 16;
+                    const float floor_v = p.relu ? 0.f : -INFINITY;
+#pragma unroll
+                    for (int g0 = 0; g0 < Cfg::CHUNK; g0 += G) {
+                        if (!pix_ok || co0 + g0 >= p.Cout) continue;
+                        const bool whole = co0 + g0 + G <= p.Cout;
+                        float* yg = yb + static_cast<int64_t>(co0 + g0) * p.HoWo;
+                        float add[G];
+                        if (p.bias_mode == NZB_BIAS_MATRIX) {
+#pragma unroll
+                            for (int j = 0; j < G; j++) add[j] = bt[lane * 33 + g0 + j];
+                        } else if (p.bias_mode == NZB_BIAS_ROW) {
+#pragma unroll
+                            for (int j = 0; j < G; j++) add[j] = __ldg(p.bias + min(co0 + g0 + j, p.Cout - 1));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < G; j++) add[j] = 0.f;
+                        }
+                        if constexpr (ACC) {
+                            if (whole) {
+#pragma unroll
+                                for (int j = 0; j < G; j++) add[j] += yg[static_cast<int64_t>(j) * p.HoWo];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < G; j++)
+                                    if (co0 + g0 + j < p.Cout) add[j] += yg[static_cast<int64_t>(j) * p.HoWo];
+                            }
+                        }
+                        if (whole) {
+#pragma unroll
+                            for (int j = 0; j < G; j++)
+                                yg[static_cast<int64_t>(j) * p.HoWo] = fmaxf(__uint_as_float(v[g0 + j]) + add[j], floor_v);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < G; j++)
+                                if (co0 + g0 + j < p.Cout)
+                                    yg[static_cast<int64_t>(j) * p.HoWo] =
+                                        fmaxf(__uint_as_float(v[g0 + j]) + add[j], floor_v);
+                        }
+                    }
+                    __syncwarp();
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = NZB_ERR_DEVICE_TIMEOUT;
+        __threadfence_system();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// Input staging for the TMA im2col mode: Kw shifted fp16 copies, 8 output columns per thread
+// (one 16-byte store per copy). rows = images * C * H of this chunk.
+template <int KW>
+__global__ void __launch_bounds__(256) shift_copies_kernel(__half* __restrict__ xs, const float* __restrict__ x,
+                                                           int64_t rows, int W, int Wp, int pad) {
+    const int W8 = Wp >> 3;
+    const int64_t total = rows * W8;
+    const int64_t copy_stride = rows * Wp;
+    for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < total; u += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t row = u / W8;
+        const int w0 = (int)(u - row * W8) * 8;
+        const float* src = x + row * W;
+        float v[8 + KW - 1];
+#pragma unroll
+        for (int j = 0; j < 8 + KW - 1; j++) {
+            const int w = w0 + j - pad;
+            v[j] = (unsigned)w < (unsigned)W ? __ldg(src + w) : 0.f;
+        }
+#pragma unroll
+        for (int kw = 0; kw < KW; kw++) {
+            uint4 o;
+            __half2 t;
+            t = __floats2half2_rn(v[kw], v[kw + 1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+            t = __floats2half2_rn(v[kw + 2], v[kw + 3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+            t = __floats2half2_rn(v[kw + 4], v[kw + 5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+            t = __floats2half2_rn(v[kw + 6], v[kw + 7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+            *reinterpret_cast<uint4*>(xs + kw * copy_stride + row * Wp + w0) = o;
+        }
+    }
+}
+
+// Weight staging for the TMA im2col mode, forward (flip = 0) and backward-data (flip = 1) forms.
+//   out[wb][r][k'],  k' = (kw*CB + cb)*64 + ci*Kh + kh,  cin = cb*16 + ci  (zero for cin >= Cin and
+//   for the columns 16*Kh..63 of every block: a block is one aligned 128-byte row segment, so a
+//   weight tile costs the TMA unit one request per row)
+//   forward:  r = co,  cin = c:   w[wb][(c*Kh + kh)*Kw + kw][co]
+//   backward: r = c,   cin = co:  w[wb][(c*Kh + (Kh-1-kh))*Kw + (Kw-1-kw)][co]
+// with w = {wN, 1, C*Kh*Kw, Cout} as the reference stores it.
+__global__ void __launch_bounds__(256) tma_weights_kernel(__half* __restrict__ out, const float* __restrict__ w,
+                                                          int64_t C, int64_t Cout, int64_t Kh, int64_t Kw, int64_t wN,
+                                                          int flip) {
+    const int64_t Cin = flip ? Cout : C, R = flip ? C : Cout;
+    const int64_t CB = (Cin + 15) / 16, Kt = Kw * CB * 64;
+    const int64_t total = wN * R * Kt;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t k = i % Kt, r = (i / Kt) % R, wb = i / (Kt * R);
+        const int64_t j = k % 64, blk = k / 64;
+        const int64_t kh = j % Kh, ci = j / Kh, cb = blk % CB, kw = blk / CB;
+        const int64_t cin = cb * 16 + ci;
+        float v = 0.f;
+        if (ci < 16 && cin < Cin) {
+            const int64_t c = flip ? r : cin, co = flip ? cin : r;
+            const int64_t kh2 = flip ? Kh - 1 - kh : kh, kw2 = flip ? Kw - 1 - kw : kw;
+            v = __ldg(w + wb * C * Kh * Kw * Cout + ((c * Kh + kh2) * Kw + kw2) * Cout + co);
+        }
+        out[i] = __float2half_rn(v);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Weight staging for backward-data: W2[c][co*Kh*Kw + kh'*Kw + kw'] =
 //   half(W[wb][(c*Kh + (Kh-1-kh'))*Kw + (Kw-1-kw')][co])  -- the flipped-tap kernel whose
 // forward convolution over dY is the gradient with respect to the input.
@@ -767,19 +1108,40 @@ __global__ void __launch_bounds__(256) im2col_f16_kmajor_kernel(__half* __restri
         const int pp = (int)(q0 - (int64_t)bl * HoWo);
         int ho = pp / Wo, wo = pp - ho * Wo;
         float v[8];
+        if (wo + 8 <= Wo && q0 + 8 <= Q) {
+            // all eight pixels lie in one output row: one row pointer, column checks only at the edges
+            const int h = ho * stride - pad + kh, w0 = wo * stride - pad + kw;
+            if ((unsigned)h >= (unsigned)H) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) {
-            v[j] = 0.f;
-            if (q0 + j < Q) {
-                const int h = ho * stride - pad + kh, w = wo * stride - pad + kw;
-                if ((unsigned)h < (unsigned)H && (unsigned)w < (unsigned)W)
-                    v[j] = __ldg(x + (((b0 + bl) * C + c) * (int64_t)H + h) * W + w);
+                for (int j = 0; j < 8; j++) v[j] = 0.f;
+            } else {
+                const float* row = x + (((b0 + bl) * C + c) * (int64_t)H + h) * W;
+                if (w0 >= 0 && w0 + 7 * stride < W) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) v[j] = __ldg(row + w0 + j * stride);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) {
+                        const int w = w0 + j * stride;
+                        v[j] = (unsigned)w < (unsigned)W ? __ldg(row + w) : 0.f;
+                    }
+                }
             }
-            if (++wo == Wo) {
-                wo = 0;
-                if (++ho == Ho) {
-                    ho = 0;
-                    bl++;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                v[j] = 0.f;
+                if (q0 + j < Q) {
+                    const int h = ho * stride - pad + kh, w = wo * stride - pad + kw;
+                    if ((unsigned)h < (unsigned)H && (unsigned)w < (unsigned)W)
+                        v[j] = __ldg(x + (((b0 + bl) * C + c) * (int64_t)H + h) * W + w);
+                }
+                if (++wo == Wo) {
+                    wo = 0;
+                    if (++ho == Ho) {
+                        ho = 0;
+                        bl++;
+                    }
                 }
             }
         }
@@ -1013,6 +1375,146 @@ static int run_conv(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN,
     return run_conv_cfg<ConvCfg<16, 8>>(r, W16, Kp, wN, *ds, stream);
 }
 
+// ---- TMA im2col mode: planning and launch ----------------------------------------------------
+struct TmaPlan {
+    bool ok;
+    int64_t Kt;         // staged contraction length: Kw * ceil(Cin/16) blocks of 64 (16 * Kh used)
+    int64_t Wp;         // row pitch of the shifted copies (elements)
+    int64_t w_bytes;    // staged weights
+    int64_t per_image;  // shifted copies of one image
+    int64_t nchunk;     // images staged and convolved per pass
+};
+// Cin, Hin, Win: the tensor the taps slide over; R: output channels; Ho, Wo: output extent.
+static TmaPlan tma_plan(int64_t N, int64_t Cin, int64_t Hin, int64_t Win, int64_t R, int64_t Kh, int64_t Kw,
+                        int64_t stride, int64_t Ho, int64_t Wo, int64_t wN) {
+    TmaPlan t{};
+    t.ok = stride == 1 && Kh <= 4 && Kw <= 4 && Wo >= 32 && N > 0 && Hin < (int64_t(1) << 30) && Win < (int64_t(1) << 30);
+    const int64_t cb = (Cin + 15) / 16;
+    t.Kt = Kw * cb * 64;
+    t.Wp = round_up(Wo, 64);  // rows start on 128-byte lines: one TMA request per box row
+    t.w_bytes = round_up(wN * R * t.Kt * 2, 256);
+    t.per_image = round_up(Kw * Cin * Hin * t.Wp * 2, 256);
+    const int64_t budget = int64_t(1) << 30;
+    int64_t n = budget / (t.per_image > 0 ? t.per_image : 1);
+    if (n < 1) n = 1;
+    if (n > N) n = N > 0 ? N : 1;
+    t.nchunk = n;
+    if (t.Kt > INT32_MAX - 256 || Cin > INT32_MAX || R > INT32_MAX) t.ok = false;
+    return t;
+}
+
+// Y {N, R, Ho, Wo} (op)= conv(X {N, Cin, Hin, Win}, w) with stride 1; flip selects the backward-data form of
+// the weights (w is always the layer's {wN, 1, C*Kh*Kw, Cout} tensor). ws holds plan.w_bytes + nchunk * per_image.
+struct ConvTmaRun {
+    const float* X;
+    float* Y;
+    const float* bias;
+    const float* w;
+    int64_t N, Cin, Hin, Win, R, Kh, Kw, pad, Ho, Wo;
+    int64_t layerC, layerCout;  // the layer's own channel counts (weight tensor extents)
+    int32_t w_per_sample, bias_mode, accumulate, relu, flip;
+};
+
+template <class Cfg>
+static int run_conv_tma_cfg(const ConvTmaRun& r, const TmaPlan& pl, void* ws, const DeviceState& ds, cudaStream_t stream) {
+    EncodeTiledFn enc;
+    int rc = get_encode_tiled(&enc);
+    if (rc != NZB_OK) return rc;
+    const int64_t wN = r.w_per_sample ? r.N : 1;
+    __half* W16 = reinterpret_cast<__half*>(ws);
+    __half* XS = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(ws) + pl.w_bytes);
+    {
+        const int64_t total = wN * r.R * pl.Kt;
+        int64_t blocks = (total + 255) / 256;
+        if (blocks > (int64_t)ds.sm_count * 16) blocks = (int64_t)ds.sm_count * 16;
+        tma_weights_kernel<<<(unsigned)blocks, 256, 0, stream>>>(W16, r.w, r.layerC, r.layerCout, r.Kh, r.Kw, wN, r.flip);
+        NZB_CUDA_TRY(cudaGetLastError());
+    }
+    CUtensorMap tmW;
+    {
+        cuuint64_t dims[3] = {(cuuint64_t)pl.Kt, (cuuint64_t)r.R, (cuuint64_t)wN};
+        cuuint64_t strides[2] = {(cuuint64_t)pl.Kt * 2, (cuuint64_t)r.R * pl.Kt * 2};
+        cuuint32_t box[3] = {64, (cuuint32_t)Cfg::BN, 1};
+        cuuint32_t estr[3] = {1, 1, 1};
+        CUresult cr = enc(&tmW, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, W16, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)cr);
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_tma_tcgen05_kernel<Cfg, false>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_tma_tcgen05_kernel<Cfg, true>,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    ConvTmaParams p{};
+    p.Y = r.Y; p.bias = r.bias;
+    p.Cout = (int32_t)r.R; p.Kh = (int32_t)r.Kh; p.Kw = (int32_t)r.Kw; p.pad = (int32_t)r.pad;
+    p.Ho = (int32_t)r.Ho; p.Wo = (int32_t)r.Wo; p.HoWo = (int32_t)(r.Ho * r.Wo);
+    p.cblks = (int32_t)((r.Cin + 15) / 16);
+    p.k_blocks = p.Kw * p.cblks;
+    p.tiles_per_row = (int32_t)((r.Wo + 127) / 128);
+    p.tiles_n = (p.Cout + Cfg::BN - 1) / Cfg::BN;
+    p.w_per_sample = r.w_per_sample;
+    p.bias_mode = r.bias ? r.bias_mode : NZB_BIAS_NONE;
+    p.relu = r.relu;
+    p.stage_tx = (uint32_t)(2 * 64 * r.Kh * 16 * 2 + Cfg::B_BYTES);
+    p.status = ds.status_dev;
+    for (int64_t img0 = 0; img0 < r.N; img0 += pl.nchunk) {
+        const int64_t n = r.N - img0 < pl.nchunk ? r.N - img0 : pl.nchunk;
+        const int64_t rows = n * r.Cin * r.Hin;
+        {
+            const int64_t total = rows * (pl.Wp / 8);
+            int64_t blocks = (total + 255) / 256;
+            if (blocks > (int64_t)ds.sm_count * 32) blocks = (int64_t)ds.sm_count * 32;
+            const float* src = r.X + img0 * r.Cin * r.Hin * r.Win;
+            switch (r.Kw) {
+                case 1: shift_copies_kernel<1><<<(unsigned)blocks, 256, 0, stream>>>(XS, src, rows, (int)r.Win, (int)pl.Wp, (int)r.pad); break;
+                case 2: shift_copies_kernel<2><<<(unsigned)blocks, 256, 0, stream>>>(XS, src, rows, (int)r.Win, (int)pl.Wp, (int)r.pad); break;
+                case 3: shift_copies_kernel<3><<<(unsigned)blocks, 256, 0, stream>>>(XS, src, rows, (int)r.Win, (int)pl.Wp, (int)r.pad); break;
+                default: shift_copies_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(XS, src, rows, (int)r.Win, (int)pl.Wp, (int)r.pad); break;
+            }
+            NZB_CUDA_TRY(cudaGetLastError());
+        }
+        CUtensorMap tmX;
+        {
+            const cuuint64_t row_b = (cuuint64_t)pl.Wp * 2;
+            cuuint64_t dims[5] = {(cuuint64_t)pl.Wp, (cuuint64_t)r.Hin, (cuuint64_t)r.Cin, (cuuint64_t)n, (cuuint64_t)r.Kw};
+            cuuint64_t strides[4] = {row_b, row_b * r.Hin, row_b * r.Hin * r.Cin, row_b * r.Hin * r.Cin * n};
+            cuuint32_t box[5] = {64, (cuuint32_t)r.Kh, 16, 1, 1};
+            cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+            CUresult cr = enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, XS, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (shifted copies) failed with CUresult %d", (int)cr);
+        }
+        p.img0 = (int32_t)img0;
+        p.total_tiles = n * r.Ho * p.tiles_per_row * p.tiles_n;
+        const int64_t cap = (int64_t)ds.sm_count * Cfg::MIN_BLOCKS;
+        const int64_t grid = p.total_tiles < cap ? p.total_tiles : cap;
+        if (r.accumulate)
+            conv2d_tma_tcgen05_kernel<Cfg, true><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, p);
+        else
+            conv2d_tma_tcgen05_kernel<Cfg, false><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmW, tmX, p);
+        NZB_CUDA_TRY(cudaGetLastError());
+    }
+    return NZB_OK;
+}
+
+static int run_conv_tma(const ConvTmaRun& r, const TmaPlan& pl, void* ws, cudaStream_t stream) {
+    DeviceState* ds;
+    int rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    if (r.Ho * r.Wo > INT32_MAX - 256 || r.N * r.Ho > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "per-image extent exceeds 2^31");
+    if (r.R > 128) return run_conv_tma_cfg<ConvTmaCfg<256, 4, 1>>(r, pl, ws, *ds, stream);
+    if (r.R > 64) return run_conv_tma_cfg<ConvTmaCfg<128, 6, 1>>(r, pl, ws, *ds, stream);
+    if (r.R > 32) return run_conv_tma_cfg<ConvTmaCfg<64, 3, 2>>(r, pl, ws, *ds, stream);
+    if (r.R > 16) return run_conv_tma_cfg<ConvTmaCfg<32, 4, 2>>(r, pl, ws, *ds, stream);
+    return run_conv_tma_cfg<ConvTmaCfg<16, 5, 2>>(r, pl, ws, *ds, stream);
+}
+
 static int check_conv_desc(const nzb_conv_desc* d, int64_t* Ho, int64_t* Wo) {
     if (!d) return fail(NZB_ERR_BAD_ARG, "descriptor is null");
     if (d->N < 0 || d->C < 1 || d->H < 1 || d->W < 1 || d->Cout < 1 || d->Kh < 1 || d->Kw < 1 || d->stride < 1 ||
@@ -1061,6 +1563,11 @@ int nzb_conv2d_workspace_bytes(const nzb_conv_desc* d, size_t* bytes_out) {
     const int64_t g = weight_grad_stage_bytes(d, Ho * Wo, nullptr);
     int64_t m = f > b ? f : b;
     if (g > m) m = g;
+    // TMA im2col mode: staged weights + the shifted fp16 copies of a chunk of images
+    const TmaPlan tf = tma_plan(d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, Ho, Wo, wN);
+    if (tf.ok && tf.w_bytes + tf.nchunk * tf.per_image > m) m = tf.w_bytes + tf.nchunk * tf.per_image;
+    const TmaPlan tb = tma_plan(d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W, wN);
+    if (tb.ok && tb.w_bytes + tb.nchunk * tb.per_image > m) m = tb.w_bytes + tb.nchunk * tb.per_image;
     *bytes_out = (size_t)round_up(m, 256);
     return NZB_OK;
 }
@@ -1079,6 +1586,14 @@ int nzb_conv2d_forward(const nzb_conv_desc* d, const float* x, const float* w, c
     if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(NZB_ERR_WORKSPACE, "workspace must be 256-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int64_t wN = d->weights_per_sample ? d->N : 1;
+    {
+        const TmaPlan tp = tma_plan(d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, Ho, Wo, wN);
+        if (tp.ok) {
+            ConvTmaRun r{x, y, bias, w, d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->pad, Ho, Wo, d->C, d->Cout,
+                         d->weights_per_sample ? 1 : 0, d->bias_mode, d->accumulate ? 1 : 0, d->relu ? 1 : 0, 0};
+            return run_conv_tma(r, tp, workspace, s);
+        }
+    }
     const int64_t K = d->C * d->Kh * d->Kw, Kp = round_up(K, kOperandKAlign);
     __half* W16 = reinterpret_cast<__half*>(workspace);
     // w is {wN, 1, K, Cout} row-major: stage as [wN][Cout][Kp] (transpose + round)
@@ -1108,6 +1623,15 @@ int nzb_conv2d_backward_data(const nzb_conv_desc* d, const float* dy, const floa
     if (rc != NZB_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int64_t wN = d->weights_per_sample ? d->N : 1;
+    {
+        // dX {N, C, H, W} += conv(dY {N, Cout, Ho, Wo}, flipped weights, pad' = Kh - 1 - pad, stride 1)
+        const TmaPlan tp = tma_plan(d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W, wN);
+        if (tp.ok) {
+            ConvTmaRun r{dy, dx, nullptr, w, d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->Kh - 1 - d->pad, d->H, d->W,
+                         d->C, d->Cout, d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, 1, 0, 1};
+            return run_conv_tma(r, tp, workspace, s);
+        }
+    }
     const int64_t K2 = d->Cout * d->Kh * d->Kw, Kp2 = round_up(K2, kOperandKAlign);
     __half* W16 = reinterpret_cast<__half*>(workspace);
     {

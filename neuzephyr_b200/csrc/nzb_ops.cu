@@ -225,10 +225,13 @@ __global__ void __launch_bounds__(256) avgpool_plane_kernel(float* __restrict__ 
     }
 }
 
+// STRIDE > 0 fixes the stride at compile time (shifts instead of divisions); 0 = any stride.
+template <int STRIDE>
 __global__ void __launch_bounds__(256) avgpool_backward_plane_kernel(float* __restrict__ gin,
                                                                      const float* __restrict__ gout, int pool,
-                                                                     int stride, int pad, int H, int W, int Ho, int Wo,
-                                                                     int planes) {
+                                                                     int stride_rt, int pad, int H, int W, int Ho,
+                                                                     int Wo, int planes) {
+    const int stride = STRIDE > 0 ? STRIDE : stride_rt;
     const int per = H * W;
     const float full = (float)(pool * pool);
     for (int bc = blockIdx.y; bc < planes; bc += gridDim.y) {
@@ -241,14 +244,25 @@ __global__ void __launch_bounds__(256) avgpool_backward_plane_kernel(float* __re
             const int h_lo = hn <= 0 ? 0 : hn / stride, w_lo = wn <= 0 ? 0 : wn / stride;
             const int h_hi = min((hi + pad) / stride, Ho - 1), w_hi = min((wi + pad) / stride, Wo - 1);
             float s = 0.f;
-            for (int h = h_lo; h <= h_hi; h++) {
-                const int hs = h * stride - pad;
-                const int ch = min(hs + pool, H) - max(hs, 0);
-                const float* grow = g + (int64_t)h * Wo;
-                for (int w = w_lo; w <= w_hi; w++) {
-                    const int ws = w * stride - pad;
-                    const int cw = min(ws + pool, W) - max(ws, 0);
-                    s += __ldg(grow + w) / (pad ? (float)(ch * cw) : full);
+            if (pad == 0) {
+                // every window is complete: one divisor. The terms are summed before the division
+                // (the reference adds gout / pool^2 term by term, atomically and in no fixed order;
+                // both are within an ulp or two of the exact sum).
+                for (int h = h_lo; h <= h_hi; h++) {
+                    const float* grow = g + (int64_t)h * Wo;
+                    for (int w = w_lo; w <= w_hi; w++) s += __ldg(grow + w);
+                }
+                s = s / full;
+            } else {
+                for (int h = h_lo; h <= h_hi; h++) {
+                    const int hs = h * stride - pad;
+                    const int ch = min(hs + pool, H) - max(hs, 0);
+                    const float* grow = g + (int64_t)h * Wo;
+                    for (int w = w_lo; w <= w_hi; w++) {
+                        const int ws = w * stride - pad;
+                        const int cw = min(ws + pool, W) - max(ws, 0);
+                        s += __ldg(grow + w) / (float)(ch * cw);
+                    }
                 }
             }
             dst[idx] += s;
@@ -516,8 +530,16 @@ int nzb_avgpool_backward(float* gin, const float* gout, int64_t pool, int64_t st
         const int64_t capx = ((int64_t)ds->sm_count * 16 + planes - 1) / planes;
         if (gx > capx) gx = capx;
         const int64_t gy = planes < 65535 ? planes : 65535;
-        avgpool_backward_plane_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, s>>>(
-            gin, gout, (int)pool, (int)stride, (int)pad, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+        const dim3 grid((unsigned)gx, (unsigned)gy);
+        if (stride == 1)
+            avgpool_backward_plane_kernel<1><<<grid, 256, 0, s>>>(gin, gout, (int)pool, 1, (int)pad, (int)H_in, (int)W_in,
+                                                                  (int)H_out, (int)W_out, (int)planes);
+        else if (stride == 2)
+            avgpool_backward_plane_kernel<2><<<grid, 256, 0, s>>>(gin, gout, (int)pool, 2, (int)pad, (int)H_in, (int)W_in,
+                                                                  (int)H_out, (int)W_out, (int)planes);
+        else
+            avgpool_backward_plane_kernel<0><<<grid, 256, 0, s>>>(gin, gout, (int)pool, (int)stride, (int)pad, (int)H_in,
+                                                                  (int)W_in, (int)H_out, (int)W_out, (int)planes);
         NZB_OPS_EPILOGUE();
     }
     avgpool_backward_kernel<<<grid_for(total, 256, ds->sm_count), 256, 0, s>>>(gin, gout, pool, stride, pad, H_in,

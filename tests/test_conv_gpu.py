@@ -47,6 +47,12 @@ CASES = [
     (1, 5, 12, 100, 7, 5, 1, 2, False),
     (1, 70, 5, 40, 130, 1, 1, 0, False),
     (3, 16, 7, 256, 16, 3, 1, 1, True),
+    # stride 1 with taps up to 4x4 and rows of 32+ pixels: the TMA im2col kernel (shifted fp16 copies);
+    # odd widths, channel counts that are not multiples of 16, several tiles per row, every pad
+    (2, 40, 9, 35, 20, 3, 1, 0, False),
+    (1, 6, 8, 70, 33, 2, 1, 1, False),
+    (1, 20, 9, 60, 65, 4, 1, 2, False),
+    (1, 3, 5, 300, 16, 3, 1, 2, False),
 ]
 
 
