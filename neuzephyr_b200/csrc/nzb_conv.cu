@@ -758,8 +758,7 @@ struct ConvTmaCfg {
     static constexpr int B_BYTES = BN * 64 * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int BAR_BYTES = 256;
-    static constexpr int EPI_BYTES = 4 * 32 * 33 * 4;
-    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
     static constexpr int CHUNK = (BN < 32) ? BN : 32;
     static constexpr int THREADS = 6 * 32;
@@ -771,14 +770,17 @@ struct ConvTmaCfg {
 struct ConvTmaTile {
     int32_t img, ho, wo0, npx, nt;
 };
-__device__ __forceinline__ ConvTmaTile decode_tma_tile(const ConvTmaParams& p, int64_t tile) {
+__device__ __forceinline__ ConvTmaTile decode_tma_tile(const ConvTmaParams& p, int64_t tile64) {
+    // the host keeps total_tiles below 2^31: 32-bit divisions (a 64-bit one costs hundreds of cycles)
     ConvTmaTile t;
-    t.nt = static_cast<int32_t>(tile % p.tiles_n);
-    int64_t r = tile / p.tiles_n;
-    const int32_t seg = static_cast<int32_t>(r % p.tiles_per_row);
-    r /= p.tiles_per_row;
-    t.ho = static_cast<int32_t>(r % p.Ho);
-    t.img = static_cast<int32_t>(r / p.Ho);
+    const uint32_t tile = static_cast<uint32_t>(tile64);
+    uint32_t r = tile / (uint32_t)p.tiles_n;
+    t.nt = static_cast<int32_t>(tile - r * (uint32_t)p.tiles_n);
+    const uint32_t r2 = r / (uint32_t)p.tiles_per_row;
+    const int32_t seg = static_cast<int32_t>(r - r2 * (uint32_t)p.tiles_per_row);
+    const uint32_t r3 = r2 / (uint32_t)p.Ho;
+    t.ho = static_cast<int32_t>(r2 - r3 * (uint32_t)p.Ho);
+    t.img = static_cast<int32_t>(r3);
     t.wo0 = seg * 128;
     t.npx = min(128, p.Wo - t.wo0);
     return t;
@@ -792,8 +794,7 @@ conv2d_tma_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
     constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    float* epi = reinterpret_cast<float*>(smem + STAGES * Cfg::STAGE_BYTES);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES + Cfg::EPI_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
     uint64_t* tfull = bars + 2 * STAGES;
@@ -897,7 +898,6 @@ conv2d_tma_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
     } else {
         // ---------------- epilogue: lanes are pixels, one coalesced store per channel ----------------
         const int q = warp & 3;
-        float* bt = epi + (warp - 2) * 32 * 33;
         uint32_t tcount = 0;
         for (int64_t tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, tcount++) {
             const ConvTmaTile t = decode_tma_tile(p, tile);
@@ -915,67 +915,60 @@ conv2d_tma_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                     const int32_t co0 = t.nt * BN + c0;
                     if (co0 >= p.Cout) break;
                     const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c0;
+                    // Addends first (bias and, when accumulating, the values already in Y): they do not
+                    // depend on the accumulator, so their memory latency overlaps the tensor-memory load.
+                    // Every mode decision is taken once per chunk, not per element (a branch per element
+                    // costs more than the store it guards).
+                    float add[Cfg::CHUNK];
+                    const bool whole = co0 + Cfg::CHUNK <= p.Cout;
+                    float* yg = yb + static_cast<int64_t>(co0) * p.HoWo;
+                    if (p.bias_mode == NZB_BIAS_MATRIX) {
+                        // bias is [pixel][channel]: this lane's pixel owns CHUNK consecutive floats
+                        const float* bp = p.bias + static_cast<int64_t>(pix_ok ? pix : pix0) * p.Cout + co0;
+                        if (whole && (p.Cout & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < Cfg::CHUNK; j += 4) {
+                                const float4 b4 = __ldg(reinterpret_cast<const float4*>(bp + j));
+                                add[j] = b4.x; add[j + 1] = b4.y; add[j + 2] = b4.z; add[j + 3] = b4.w;
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < Cfg::CHUNK; j++) add[j] = co0 + j < p.Cout ? __ldg(bp + j) : 0.f;
+                        }
+                    } else if (p.bias_mode == NZB_BIAS_ROW) {
+#pragma unroll
+                        for (int j = 0; j < Cfg::CHUNK; j++) add[j] = __ldg(p.bias + min(co0 + j, p.Cout - 1));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < Cfg::CHUNK; j++) add[j] = 0.f;
+                    }
+                    if constexpr (ACC) {
+                        if (pix_ok) {
+                            if (whole) {
+#pragma unroll
+                                for (int j = 0; j < Cfg::CHUNK; j++) add[j] += yg[static_cast<int64_t>(j) * p.HoWo];
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < Cfg::CHUNK; j++)
+                                    if (co0 + j < p.Cout) add[j] += yg[static_cast<int64_t>(j) * p.HoWo];
+                            }
+                        }
+                    }
                     uint32_t v[Cfg::CHUNK];
                     if constexpr (Cfg::CHUNK == 32) tmem_ld_32x32(taddr, v);
                     else tmem_ld_32x16(taddr, v);
-                    if (p.bias_mode == NZB_BIAS_MATRIX) {
-                        // bias is [pixel][channel]: read with lanes along channels (coalesced), transpose
-                        // through shared memory so that each lane gets its own pixel's row
-                        constexpr int RPI = 32 / Cfg::CHUNK;
-                        const int32_t co = co0 + (lane % Cfg::CHUNK);
-                        float bv[32 / RPI];
-#pragma unroll
-                        for (int i = 0; i < 32 / RPI; i++) {
-                            const int r = i * RPI + lane / Cfg::CHUNK;
-                            bv[i] = (m0 + r < t.npx && co < p.Cout)
-                                        ? __ldg(p.bias + static_cast<int64_t>(pix0 + r) * p.Cout + co) : 0.f;
-                        }
-#pragma unroll
-                        for (int i = 0; i < 32 / RPI; i++)
-                            bt[(i * RPI + lane / Cfg::CHUNK) * 33 + (lane % Cfg::CHUNK)] = bv[i];
-                        __syncwarp();
-                    }
                     tmem_ld_wait();
-                    // Straight-line inner loops: every mode decision is taken once per group of 16
-                    // channels, not per element (a branch per element costs more than the store).
-                    constexpr int G = Cfg::CHUNK < 16 ? Cfg::CHUNK : 16;
                     const float floor_v = p.relu ? 0.f : -INFINITY;
-#pragma unroll
-                    for (int g0 = 0; g0 < Cfg::CHUNK; g0 += G) {
-                        if (!pix_ok || co0 + g0 >= p.Cout) continue;
-                        const bool whole = co0 + g0 + G <= p.Cout;
-                        float* yg = yb + static_cast<int64_t>(co0 + g0) * p.HoWo;
-                        float add[G];
-                        if (p.bias_mode == NZB_BIAS_MATRIX) {
-#pragma unroll
-                            for (int j = 0; j < G; j++) add[j] = bt[lane * 33 + g0 + j];
-                        } else if (p.bias_mode == NZB_BIAS_ROW) {
-#pragma unroll
-                            for (int j = 0; j < G; j++) add[j] = __ldg(p.bias + min(co0 + g0 + j, p.Cout - 1));
-                        } else {
-#pragma unroll
-                            for (int j = 0; j < G; j++) add[j] = 0.f;
-                        }
-                        if constexpr (ACC) {
-                            if (whole) {
-#pragma unroll
-                                for (int j = 0; j < G; j++) add[j] += yg[static_cast<int64_t>(j) * p.HoWo];
-                            } else {
-#pragma unroll
-                                for (int j = 0; j < G; j++)
-                                    if (co0 + g0 + j < p.Cout) add[j] += yg[static_cast<int64_t>(j) * p.HoWo];
-                            }
-                        }
+                    if (pix_ok) {
                         if (whole) {
 #pragma unroll
-                            for (int j = 0; j < G; j++)
-                                yg[static_cast<int64_t>(j) * p.HoWo] = fmaxf(__uint_as_float(v[g0 + j]) + add[j], floor_v);
+                            for (int j = 0; j < Cfg::CHUNK; j++)
+                                yg[static_cast<int64_t>(j) * p.HoWo] = fmaxf(__uint_as_float(v[j]) + add[j], floor_v);
                         } else {
 #pragma unroll
-                            for (int j = 0; j < G; j++)
-                                if (co0 + g0 + j < p.Cout)
-                                    yg[static_cast<int64_t>(j) * p.HoWo] =
-                                        fmaxf(__uint_as_float(v[g0 + j]) + add[j], floor_v);
+                            for (int j = 0; j < Cfg::CHUNK; j++)
+                                if (co0 + j < p.Cout)
+                                    yg[static_cast<int64_t>(j) * p.HoWo] = fmaxf(__uint_as_float(v[j]) + add[j], floor_v);
                         }
                     }
                     __syncwarp();
@@ -1492,6 +1485,7 @@ static int run_conv_tma_cfg(const ConvTmaRun& r, const TmaPlan& pl, void* ws, co
         }
         p.img0 = (int32_t)img0;
         p.total_tiles = n * r.Ho * p.tiles_per_row * p.tiles_n;
+        if (p.total_tiles > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "more than 2^31 output tiles in one pass");
         const int64_t cap = (int64_t)ds.sm_count * Cfg::MIN_BLOCKS;
         const int64_t grid = p.total_tiles < cap ? p.total_tiles : cap;
         if (r.accumulate)
@@ -1509,10 +1503,10 @@ static int run_conv_tma(const ConvTmaRun& r, const TmaPlan& pl, void* ws, cudaSt
     if (rc != NZB_OK) return rc;
     if (r.Ho * r.Wo > INT32_MAX - 256 || r.N * r.Ho > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "per-image extent exceeds 2^31");
     if (r.R > 128) return run_conv_tma_cfg<ConvTmaCfg<256, 4, 1>>(r, pl, ws, *ds, stream);
-    if (r.R > 64) return run_conv_tma_cfg<ConvTmaCfg<128, 6, 1>>(r, pl, ws, *ds, stream);
-    if (r.R > 32) return run_conv_tma_cfg<ConvTmaCfg<64, 3, 2>>(r, pl, ws, *ds, stream);
-    if (r.R > 16) return run_conv_tma_cfg<ConvTmaCfg<32, 4, 2>>(r, pl, ws, *ds, stream);
-    return run_conv_tma_cfg<ConvTmaCfg<16, 5, 2>>(r, pl, ws, *ds, stream);
+    if (r.R > 64) return run_conv_tma_cfg<ConvTmaCfg<128, 7, 1>>(r, pl, ws, *ds, stream);
+    if (r.R > 32) return run_conv_tma_cfg<ConvTmaCfg<64, 4, 2>>(r, pl, ws, *ds, stream);
+    if (r.R > 16) return run_conv_tma_cfg<ConvTmaCfg<32, 5, 2>>(r, pl, ws, *ds, stream);
+    return run_conv_tma_cfg<ConvTmaCfg<16, 6, 2>>(r, pl, ws, *ds, stream);
 }
 
 static int check_conv_desc(const nzb_conv_desc* d, int64_t* Ho, int64_t* Wo) {
