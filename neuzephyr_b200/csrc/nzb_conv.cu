@@ -1052,6 +1052,244 @@ __global__ void __launch_bounds__(256) tma_weights_kernel(__half* __restrict__ o
 }
 
 // ---------------------------------------------------------------------------
+// Weight gradient in the TMA im2col mode: dW[k][co] += sum over pixels of col[pixel][k] * dY[pixel][co].
+// The contraction runs over pixels, so both operands are K-major with pixels contiguous:
+//   A (128 rows of k x 128 pixels): the same boxes of the shifted copies the forward kernel
+//     loads -- rows (ci, kh) of tap column kw, here up to 128/Kh channels per box -- read as a
+//     K-major operand;
+//   B (BN channels x 128 pixels): boxes of an fp16 copy of dY with the same row pitch, whose
+//     columns past Wo are zero, so that the extra columns of a copy never contribute.
+// A k block is 128 pixels of one output row (two 64-pixel boxes per operand). An output tile
+// (one tap column x one channel block x BN output channels) is shared among several CTAs
+// along the pixel space; partial sums are added to dW with fp32 atomics.
+// ---------------------------------------------------------------------------
+struct WgradParams {
+    float* dW;  // {wN, 1, C*Kh*Kw, Cout}
+    int32_t C, Cout, Kh, Kw, pad;
+    int32_t Ho, segs;        // segs = ceil(Wo / 128)
+    int32_t cbw;             // channels per A box (cbw * Kh <= 128)
+    int32_t cblks;           // ceil(C / cbw)
+    int32_t tiles_n;         // ceil(Cout / BN)
+    int32_t tiles;           // Kw * cblks * tiles_n
+    int32_t groups;          // separate outputs: images when weights are per sample, else 1
+    int32_t imgs_per_group;  // images contracted into one output
+    int32_t splits;          // CTAs sharing one (tile, group)
+    int32_t img0;            // first image of this chunk (selects the per-sample dW)
+    int32_t w_per_sample;
+    uint32_t stage_tx;
+    int64_t kb_per_group;  // imgs_per_group * Ho * segs
+    int64_t total_items;   // tiles * groups * splits
+    int* status;
+};
+
+template <int BN_, int STAGES_>
+struct WgradCfg {
+    static constexpr int BN = BN_, STAGES = STAGES_;
+    static constexpr int A_BYTES = 2 * 16384;       // two 64-pixel halves of 128 k rows
+    static constexpr int B_BYTES = 2 * BN * 128;    // two 64-pixel halves of BN channels
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+    static constexpr int TMEM_COLS = (BN < 32) ? 32 : BN;
+    static constexpr int THREADS = 6 * 32;
+    static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, 1)
+conv2d_wgrad_tma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
+                        const WgradParams p) {
+    using namespace ptx;
+    constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* tfull = bars + 2 * STAGES;   // [1]
+    uint64_t* tempty = bars + 2 * STAGES + 1;  // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmX);
+        prefetch_tensormap(&tmDY);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(tfull, 1);
+        mbar_init(tempty, 4);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // item -> (tile, group, split); tile -> (kw, cb, nt)
+    auto item_range = [&](uint32_t item, int32_t& kw, int32_t& cb, int32_t& nt, int32_t& group, uint32_t& kk0,
+                          uint32_t& kk1) {
+        const uint32_t split = item % (uint32_t)p.splits;
+        uint32_t r = item / (uint32_t)p.splits;
+        group = (int32_t)(r % (uint32_t)p.groups);
+        r /= (uint32_t)p.groups;
+        nt = (int32_t)(r % (uint32_t)p.tiles_n);
+        r /= (uint32_t)p.tiles_n;
+        cb = (int32_t)(r % (uint32_t)p.cblks);
+        kw = (int32_t)(r / (uint32_t)p.cblks);
+        kk0 = (uint32_t)(p.kb_per_group * split / p.splits);
+        kk1 = (uint32_t)(p.kb_per_group * (split + 1) / p.splits);
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA ----------------
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x) {
+            int32_t kw, cb, nt, group;
+            uint32_t kk0, kk1;
+            item_range((uint32_t)item, kw, cb, nt, group, kk0, kk1);
+            // k block -> (image, output row, segment), advanced incrementally
+            const uint32_t per_img = (uint32_t)(p.Ho * p.segs);
+            int32_t img = (int32_t)(kk0 / per_img);
+            uint32_t rem = kk0 - (uint32_t)img * per_img;
+            int32_t ho = (int32_t)(rem / (uint32_t)p.segs), seg = (int32_t)(rem % (uint32_t)p.segs);
+            img += p.w_per_sample ? group : 0;
+            for (uint32_t kk = kk0; kk < kk1; kk++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
+                    uint8_t* sb = sa + Cfg::A_BYTES;
+                    const int32_t w0 = seg * 128;
+                    mbar_arrive_expect_tx(&full[s], p.stage_tx);
+                    tma_load_5d(sa, &tmX, w0, ho - p.pad, cb * p.cbw, img, kw, &full[s]);
+                    tma_load_5d(sa + 16384, &tmX, w0 + 64, ho - p.pad, cb * p.cbw, img, kw, &full[s]);
+                    tma_load_4d(sb, &tmDY, w0, ho, nt * BN, img, &full[s]);
+                    tma_load_4d(sb + BN * 128, &tmDY, w0 + 64, ho, nt * BN, img, &full[s]);
+                }
+                __syncwarp();
+                if (++seg == p.segs) {
+                    seg = 0;
+                    if (++ho == p.Ho) {
+                        ho = 0;
+                        img++;
+                    }
+                }
+            }
+        }
+        if (!ok && lane == 0) {
+            const long long t0 = clock64();
+            const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
+            for (uint32_t j = first; j < it; j++)
+                while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1))
+                    if (clock64() - t0 > kWaitCycleLimit) break;
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA: 8 steps of 16 pixels per k block ----------------
+        constexpr uint32_t idesc = make_idesc_f16_f32(128, BN);
+        uint32_t it = 0, icount = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x, icount++) {
+            int32_t kw, cb, nt, group;
+            uint32_t kk0, kk1;
+            item_range((uint32_t)item, kw, cb, nt, group, kk0, kk1);
+            if (!mbar_wait_warp(tempty, (icount & 1) ^ 1, abort_flag)) break;
+            tc_fence_after();
+            for (uint32_t kk = kk0; kk < kk1; kk++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                const uint64_t da0 = make_sw128_kmajor_desc(sa), da1 = make_sw128_kmajor_desc(sa + 16384);
+                const uint64_t db0 = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                const uint64_t db1 = make_sw128_kmajor_desc(sa + Cfg::A_BYTES + BN * 128);
+                if (elect_one()) {
+                    mma_f16_ss(tmem_base, da0, db0, idesc, kk > kk0 ? 1u : 0u);
+                    mma_f16_ss(tmem_base, da0 + 2, db0 + 2, idesc, 1u);
+                    mma_f16_ss(tmem_base, da0 + 4, db0 + 4, idesc, 1u);
+                    mma_f16_ss(tmem_base, da0 + 6, db0 + 6, idesc, 1u);
+                    mma_f16_ss(tmem_base, da1, db1, idesc, 1u);
+                    mma_f16_ss(tmem_base, da1 + 2, db1 + 2, idesc, 1u);
+                    mma_f16_ss(tmem_base, da1 + 4, db1 + 4, idesc, 1u);
+                    mma_f16_ss(tmem_base, da1 + 6, db1 + 6, idesc, 1u);
+                    mma_commit(&empty[s]);
+                }
+                __syncwarp();
+            }
+            if (ok && elect_one()) mma_commit(tfull);
+            __syncwarp();
+        }
+    } else {
+        // ---------------- epilogue: lane = k row, atomic adds into dW[k][co .. co+BN) ----------------
+        const int q = warp & 3;
+        uint32_t icount = 0;
+        for (int64_t item = blockIdx.x; item < p.total_items; item += gridDim.x, icount++) {
+            int32_t kw, cb, nt, group;
+            uint32_t kk0, kk1;
+            item_range((uint32_t)item, kw, cb, nt, group, kk0, kk1);
+            if (!mbar_wait_relaxed(tfull, icount & 1, abort_flag)) break;
+            tc_fence_after();
+            const int32_t m = q * 32 + lane;  // row of the tile: (channel in box, kh)
+            const int32_t ci = m / p.Kh, kh = m - ci * p.Kh;
+            const int32_t c = cb * p.cbw + ci;
+            const bool row_ok = kk1 > kk0 && ci < p.cbw && c < p.C;
+            const int64_t K = (int64_t)p.C * p.Kh * p.Kw;
+            float* dst = p.dW + (p.w_per_sample ? (int64_t)(p.img0 + group) * K * p.Cout : 0) +
+                         ((int64_t)(c * p.Kh + kh) * p.Kw + kw) * p.Cout + nt * BN;
+            constexpr int CH = BN < 16 ? BN : 16;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += CH) {
+                if (nt * BN + c0 >= p.Cout) break;
+                uint32_t v[16];
+                tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, v);
+                tmem_ld_wait();
+                if (row_ok) {
+                    if (nt * BN + c0 + 16 <= p.Cout) {
+#pragma unroll
+                        for (int j = 0; j < 16; j++) atomicAdd(dst + c0 + j, __uint_as_float(v[j]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (nt * BN + c0 + j < p.Cout) atomicAdd(dst + c0 + j, __uint_as_float(v[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty);
+        }
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = NZB_ERR_DEVICE_TIMEOUT;
+        __threadfence_system();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Weight staging for backward-data: W2[c][co*Kh*Kw + kh'*Kw + kw'] =
 //   half(W[wb][(c*Kh + (Kh-1-kh'))*Kw + (Kw-1-kw')][co])  -- the flipped-tap kernel whose
 // forward convolution over dY is the gradient with respect to the input.
@@ -1509,6 +1747,123 @@ static int run_conv_tma(const ConvTmaRun& r, const TmaPlan& pl, void* ws, cudaSt
     return run_conv_tma_cfg<ConvTmaCfg<16, 6, 2>>(r, pl, ws, *ds, stream);
 }
 
+// ---- weight gradient in the TMA im2col mode: planning and launch --------------------------------
+struct WgradPlan {
+    bool ok;
+    int64_t Wp, per_image, nchunk;
+    int32_t cbw;
+};
+static WgradPlan wgrad_plan(const nzb_conv_desc* d, int64_t Ho, int64_t Wo) {
+    WgradPlan t{};
+    t.ok = d->stride == 1 && d->Kh <= 4 && d->Kw <= 4 && Wo >= 32 && d->N > 0 && d->C <= INT32_MAX &&
+           d->Cout <= INT32_MAX;
+    t.Wp = round_up(Wo, 64);
+    t.cbw = (int32_t)((128 / d->Kh) / 16 * 16);
+    t.per_image = round_up(d->Kw * d->C * d->H * t.Wp * 2, 256) + round_up(d->Cout * Ho * t.Wp * 2, 256);
+    const int64_t budget = int64_t(3) << 29;  // 1.5 GiB of staged operands per pass
+    int64_t n = budget / (t.per_image > 0 ? t.per_image : 1);
+    if (n < 1) n = 1;
+    if (n > d->N) n = d->N > 0 ? d->N : 1;
+    t.nchunk = n;
+    return t;
+}
+
+template <class Cfg>
+static int run_wgrad_tma_cfg(const nzb_conv_desc* d, const WgradPlan& pl, const float* x, const float* dy, float* dw,
+                             void* ws, int64_t Ho, int64_t Wo, const DeviceState& ds, cudaStream_t stream) {
+    EncodeTiledFn enc;
+    int rc = get_encode_tiled(&enc);
+    if (rc != NZB_OK) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_wgrad_tma_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          Cfg::SMEM_BYTES));
+        attr_set = true;
+    }
+    WgradParams p{};
+    p.dW = dw;
+    p.C = (int32_t)d->C; p.Cout = (int32_t)d->Cout; p.Kh = (int32_t)d->Kh; p.Kw = (int32_t)d->Kw; p.pad = (int32_t)d->pad;
+    p.Ho = (int32_t)Ho; p.segs = (int32_t)((Wo + 127) / 128);
+    p.cbw = pl.cbw;
+    p.cblks = (int32_t)((d->C + pl.cbw - 1) / pl.cbw);
+    p.tiles_n = (int32_t)((d->Cout + Cfg::BN - 1) / Cfg::BN);
+    p.tiles = p.Kw * p.cblks * p.tiles_n;
+    p.w_per_sample = d->weights_per_sample ? 1 : 0;
+    p.stage_tx = (uint32_t)(2 * 64 * d->Kh * pl.cbw * 2 + 2 * 64 * Cfg::BN * 2);
+    p.status = ds.status_dev;
+    for (int64_t img0 = 0; img0 < d->N; img0 += pl.nchunk) {
+        const int64_t n = d->N - img0 < pl.nchunk ? d->N - img0 : pl.nchunk;
+        __half* XS = reinterpret_cast<__half*>(ws);
+        __half* DY = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(ws) + round_up(d->Kw * n * d->C * d->H * pl.Wp * 2, 256));
+        {
+            const int64_t rows = n * d->C * d->H;
+            int64_t blocks = (rows * (pl.Wp / 8) + 255) / 256;
+            if (blocks > (int64_t)ds.sm_count * 32) blocks = (int64_t)ds.sm_count * 32;
+            const float* src = x + img0 * d->C * d->H * d->W;
+            switch (d->Kw) {
+                case 1: shift_copies_kernel<1><<<(unsigned)blocks, 256, 0, stream>>>(XS, src, rows, (int)d->W, (int)pl.Wp, (int)d->pad); break;
+                case 2: shift_copies_kernel<2><<<(unsigned)blocks, 256, 0, stream>>>(XS, src, rows, (int)d->W, (int)pl.Wp, (int)d->pad); break;
+                case 3: shift_copies_kernel<3><<<(unsigned)blocks, 256, 0, stream>>>(XS, src, rows, (int)d->W, (int)pl.Wp, (int)d->pad); break;
+                default: shift_copies_kernel<4><<<(unsigned)blocks, 256, 0, stream>>>(XS, src, rows, (int)d->W, (int)pl.Wp, (int)d->pad); break;
+            }
+            NZB_CUDA_TRY(cudaGetLastError());
+            // dY as one unshifted copy: columns [Wo, Wp) become zeros
+            const int64_t rows2 = n * d->Cout * Ho;
+            int64_t blocks2 = (rows2 * (pl.Wp / 8) + 255) / 256;
+            if (blocks2 > (int64_t)ds.sm_count * 32) blocks2 = (int64_t)ds.sm_count * 32;
+            shift_copies_kernel<1><<<(unsigned)blocks2, 256, 0, stream>>>(DY, dy + img0 * d->Cout * Ho * Wo, rows2, (int)Wo,
+                                                                          (int)pl.Wp, 0);
+            NZB_CUDA_TRY(cudaGetLastError());
+        }
+        CUtensorMap tmX, tmDY;
+        {
+            const cuuint64_t row_b = (cuuint64_t)pl.Wp * 2;
+            cuuint64_t dims[5] = {(cuuint64_t)pl.Wp, (cuuint64_t)d->H, (cuuint64_t)d->C, (cuuint64_t)n, (cuuint64_t)d->Kw};
+            cuuint64_t strides[4] = {row_b, row_b * d->H, row_b * d->H * d->C, row_b * d->H * d->C * n};
+            cuuint32_t box[5] = {64, (cuuint32_t)d->Kh, (cuuint32_t)pl.cbw, 1, 1};
+            cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+            CUresult cr = enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, XS, dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (shifted copies) failed with CUresult %d", (int)cr);
+            cuuint64_t dims2[4] = {(cuuint64_t)pl.Wp, (cuuint64_t)Ho, (cuuint64_t)d->Cout, (cuuint64_t)n};
+            cuuint64_t strides2[3] = {row_b, row_b * Ho, row_b * Ho * d->Cout};
+            cuuint32_t box2[4] = {64, 1, (cuuint32_t)Cfg::BN, 1};
+            cuuint32_t estr2[4] = {1, 1, 1, 1};
+            cr = enc(&tmDY, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, DY, dims2, strides2, box2, estr2,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+            if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (dY copy) failed with CUresult %d", (int)cr);
+        }
+        p.img0 = (int32_t)img0;
+        p.groups = p.w_per_sample ? (int32_t)n : 1;
+        p.imgs_per_group = p.w_per_sample ? 1 : (int32_t)n;
+        p.kb_per_group = (int64_t)p.imgs_per_group * Ho * p.segs;
+        if (p.kb_per_group > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "contraction length exceeds 2^31 blocks");
+        int64_t splits = ds.sm_count / ((int64_t)p.tiles * p.groups);
+        if (splits < 1) splits = 1;
+        if (splits > p.kb_per_group) splits = p.kb_per_group;
+        p.splits = (int32_t)splits;
+        p.total_items = (int64_t)p.tiles * p.groups * p.splits;
+        if (p.total_items > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "more than 2^31 work items");
+        const int64_t grid = p.total_items < ds.sm_count ? p.total_items : ds.sm_count;
+        conv2d_wgrad_tma_kernel<Cfg><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmX, tmDY, p);
+        NZB_CUDA_TRY(cudaGetLastError());
+    }
+    return NZB_OK;
+}
+
+static int run_wgrad_tma(const nzb_conv_desc* d, const WgradPlan& pl, const float* x, const float* dy, float* dw, void* ws,
+                         int64_t Ho, int64_t Wo, cudaStream_t stream) {
+    DeviceState* ds;
+    int rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    if (d->Cout > 64) return run_wgrad_tma_cfg<WgradCfg<128, 3>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream);
+    if (d->Cout > 32) return run_wgrad_tma_cfg<WgradCfg<64, 4>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream);
+    if (d->Cout > 16) return run_wgrad_tma_cfg<WgradCfg<32, 5>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream);
+    return run_wgrad_tma_cfg<WgradCfg<16, 6>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream);
+}
+
 static int check_conv_desc(const nzb_conv_desc* d, int64_t* Ho, int64_t* Wo) {
     if (!d) return fail(NZB_ERR_BAD_ARG, "descriptor is null");
     if (d->N < 0 || d->C < 1 || d->H < 1 || d->W < 1 || d->Cout < 1 || d->Kh < 1 || d->Kw < 1 || d->stride < 1 ||
@@ -1562,6 +1917,8 @@ int nzb_conv2d_workspace_bytes(const nzb_conv_desc* d, size_t* bytes_out) {
     if (tf.ok && tf.w_bytes + tf.nchunk * tf.per_image > m) m = tf.w_bytes + tf.nchunk * tf.per_image;
     const TmaPlan tb = tma_plan(d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W, wN);
     if (tb.ok && tb.w_bytes + tb.nchunk * tb.per_image > m) m = tb.w_bytes + tb.nchunk * tb.per_image;
+    const WgradPlan tg = wgrad_plan(d, Ho, Wo);
+    if (tg.ok && tg.nchunk * tg.per_image > m) m = tg.nchunk * tg.per_image;
     *bytes_out = (size_t)round_up(m, 256);
     return NZB_OK;
 }
@@ -1656,6 +2013,10 @@ int nzb_conv2d_backward_weight(const nzb_conv_desc* d, const float* x, const flo
     rc = get_device_state(&ds);
     if (rc != NZB_OK) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    {
+        const WgradPlan tg = wgrad_plan(d, Ho, Wo);
+        if (tg.ok) return run_wgrad_tma(d, tg, x, dy, dw, workspace, Ho, Wo, s);
+    }
     const int64_t HoWo = Ho * Wo, K = d->C * d->Kh * d->Kw;
     int64_t nb;
     weight_grad_stage_bytes(d, HoWo, &nb);
