@@ -241,39 +241,47 @@ __device__ __forceinline__ void drain_accumulator_transposed(const GemmParams& p
     constexpr int G = 16;
     const int32_t gr = row0 + lane;  // caller's column
     const bool row_ok = gr < p.M;
+    const bool with_bias = p.bias_mode != NZB_BIAS_NONE && (p.splits == 1 || first_split);
+    const float floor_v = (p.relu && p.splits == 1) ? 0.f : -INFINITY;
+    const float bias_row = (with_bias && p.bias_mode == NZB_BIAS_ROW && row_ok) ? p.bias[gr] : 0.f;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += G) {
-        if (col_tile + c0 >= p.N) break;  // warp-uniform
+        const int32_t gc0 = col_tile + c0;  // caller's first row of this group
+        if (gc0 >= p.N) break;              // warp-uniform
+        const bool whole = gc0 + G <= p.N;
+        float* cg = Cb + static_cast<int64_t>(gc0) * p.ldc + gr;
+        // addends first (their loads overlap the tensor-memory read); every mode decision is per
+        // group of 16, the inner loops are straight-line code
+        float add[G];
+#pragma unroll
+        for (int j = 0; j < G; j++) add[j] = bias_row;
+        if (with_bias && p.bias_mode == NZB_BIAS_COL) {
+#pragma unroll
+            for (int j = 0; j < G; j++) add[j] = p.bias[min(gc0 + j, p.N - 1)];
+        } else if (with_bias && p.bias_mode == NZB_BIAS_MATRIX && row_ok) {
+#pragma unroll
+            for (int j = 0; j < G; j++)
+                add[j] = p.bias[static_cast<int64_t>(min(gc0 + j, p.N - 1)) * p.bias_ld + gr];
+        }
+        if (p.accumulate && p.splits == 1 && row_ok) {
+#pragma unroll
+            for (int j = 0; j < G; j++) add[j] += cg[static_cast<int64_t>(whole ? j : min(j, p.N - 1 - gc0)) * p.ldc];
+        }
         uint32_t v[G];
         tmem_ld_32x16(tmem_acc + c0, v);
         tmem_ld_wait();
-        float old[G];
-        if (p.accumulate && p.splits == 1) {
+        if (!row_ok) continue;
+        if (p.splits > 1) {
 #pragma unroll
-            for (int j = 0; j < G; j++) {
-                const int32_t gc = col_tile + c0 + j;  // caller's row
-                old[j] = (row_ok && gc < p.N) ? Cb[static_cast<int64_t>(gc) * p.ldc + gr] : 0.f;
-            }
-        }
+            for (int j = 0; j < G; j++)
+                if (whole || gc0 + j < p.N) atomicAdd(cg + static_cast<int64_t>(j) * p.ldc, __uint_as_float(v[j]) + add[j]);
+        } else if (whole) {
 #pragma unroll
-        for (int j = 0; j < G; j++) {
-            const int32_t gc = col_tile + c0 + j;
-            if (!row_ok || gc >= p.N) continue;
-            float x = __uint_as_float(v[j]);
-            float* cp = Cb + static_cast<int64_t>(gc) * p.ldc + gr;
-            const bool with_bias = p.splits == 1 || first_split;
-            if (with_bias) {
-                if (p.bias_mode == NZB_BIAS_ROW) x += p.bias[gr];
-                else if (p.bias_mode == NZB_BIAS_COL) x += p.bias[gc];
-                else if (p.bias_mode == NZB_BIAS_MATRIX) x += p.bias[static_cast<int64_t>(gc) * p.bias_ld + gr];
-            }
-            if (p.splits > 1) {
-                atomicAdd(cp, x);
-                continue;
-            }
-            if (p.accumulate) x += old[j];
-            if (p.relu) x = fmaxf(x, 0.f);
-            *cp = x;
+            for (int j = 0; j < G; j++) cg[static_cast<int64_t>(j) * p.ldc] = fmaxf(__uint_as_float(v[j]) + add[j], floor_v);
+        } else {
+#pragma unroll
+            for (int j = 0; j < G; j++)
+                if (gc0 + j < p.N) cg[static_cast<int64_t>(j) * p.ldc] = fmaxf(__uint_as_float(v[j]) + add[j], floor_v);
         }
     }
 }

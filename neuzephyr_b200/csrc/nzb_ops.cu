@@ -225,6 +225,50 @@ __global__ void __launch_bounds__(256) avgpool_plane_kernel(float* __restrict__ 
     }
 }
 
+// Unpadded pooling, four consecutive input columns per thread (W % 4 == 0): the windows that cover
+// them overlap, so each gradient value is loaded once for the four, and the update of the input
+// gradient is one 16-byte read-modify-write. The terms are summed before the single division by
+// pool^2 (the reference adds gout / pool^2 term by term with atomics, in no fixed order; both are
+// within an ulp or two of the exact sum).
+template <int STRIDE>
+__global__ void __launch_bounds__(256) avgpool_backward_quad_kernel(float* __restrict__ gin,
+                                                                    const float* __restrict__ gout, int pool,
+                                                                    int stride_rt, int H, int W, int Ho, int Wo,
+                                                                    int planes) {
+    const int stride = STRIDE > 0 ? STRIDE : stride_rt;
+    const int W4 = W >> 2, per = H * W4;
+    const float full = (float)(pool * pool);
+    for (int bc = blockIdx.y; bc < planes; bc += gridDim.y) {
+        const float* g = gout + (int64_t)bc * Ho * Wo;
+        float* dst = gin + (int64_t)bc * H * W;
+        for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < per; idx += gridDim.x * blockDim.x) {
+            const int hi = idx / W4, wi0 = (idx - hi * W4) * 4;
+            const int hn = hi - pool + stride;
+            const int h_lo = hn <= 0 ? 0 : hn / stride, h_hi = min(hi / stride, Ho - 1);
+            int w_lo[4], w_hi[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int wn = wi0 + j - pool + stride;
+                w_lo[j] = wn <= 0 ? 0 : wn / stride;
+                w_hi[j] = min((wi0 + j) / stride, Wo - 1);
+            }
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int h = h_lo; h <= h_hi; h++) {
+                const float* grow = g + (int64_t)h * Wo;
+                for (int w = w_lo[0]; w <= w_hi[3]; w++) {
+                    const float v = __ldg(grow + w);
+#pragma unroll
+                    for (int j = 0; j < 4; j++) s[j] += (w >= w_lo[j] && w <= w_hi[j]) ? v : 0.f;
+                }
+            }
+            float4* d4 = reinterpret_cast<float4*>(dst + (int64_t)hi * W + wi0);
+            float4 o = *d4;
+            o.x += s[0] / full; o.y += s[1] / full; o.z += s[2] / full; o.w += s[3] / full;
+            *d4 = o;
+        }
+    }
+}
+
 // STRIDE > 0 fixes the stride at compile time (shifts instead of divisions); 0 = any stride.
 template <int STRIDE>
 __global__ void __launch_bounds__(256) avgpool_backward_plane_kernel(float* __restrict__ gin,
@@ -531,6 +575,21 @@ int nzb_avgpool_backward(float* gin, const float* gout, int64_t pool, int64_t st
         if (gx > capx) gx = capx;
         const int64_t gy = planes < 65535 ? planes : 65535;
         const dim3 grid((unsigned)gx, (unsigned)gy);
+        if (pad == 0 && W_in % 4 == 0 && (reinterpret_cast<uintptr_t>(gin) & 15) == 0) {
+            int64_t gq = (per / 4 + 255) / 256;
+            if (gq > capx) gq = capx;
+            const dim3 gridq((unsigned)gq, (unsigned)gy);
+            if (stride == 1)
+                avgpool_backward_quad_kernel<1><<<gridq, 256, 0, s>>>(gin, gout, (int)pool, 1, (int)H_in, (int)W_in,
+                                                                      (int)H_out, (int)W_out, (int)planes);
+            else if (stride == 2)
+                avgpool_backward_quad_kernel<2><<<gridq, 256, 0, s>>>(gin, gout, (int)pool, 2, (int)H_in, (int)W_in,
+                                                                      (int)H_out, (int)W_out, (int)planes);
+            else
+                avgpool_backward_quad_kernel<0><<<gridq, 256, 0, s>>>(gin, gout, (int)pool, (int)stride, (int)H_in,
+                                                                      (int)W_in, (int)H_out, (int)W_out, (int)planes);
+            NZB_OPS_EPILOGUE();
+        }
         if (stride == 1)
             avgpool_backward_plane_kernel<1><<<grid, 256, 0, s>>>(gin, gout, (int)pool, 1, (int)pad, (int)H_in, (int)W_in,
                                                                   (int)H_out, (int)W_out, (int)planes);
