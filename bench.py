@@ -29,8 +29,8 @@ CPU_SAMPLE_ROWS = 4096  # rows of C computed by the CPU baseline per step
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one GEMM launch at this size, from the ncu
-# capture summarised in profiles/gemm_f16_tcgen05_8192x8192x8192.md (algorithmic: 512 MB).
-NCU_DRAM_BYTES_PER_LAUNCH = 1.37e9
+# capture summarised in profiles/gemm_f16_tcgen05_pair_8192x8192x8192.md (algorithmic: 512 MB).
+NCU_DRAM_BYTES_PER_LAUNCH = 1.36e9
 
 
 def measured_hbm_gbs():

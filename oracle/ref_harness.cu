@@ -5,6 +5,11 @@
 //   ref_harness gemm_file  A.bin B.bin C.bin aN aC M K bN bC N      forward, GEMMTensorCore
 //   ref_harness gemm_bwd   A.bin B.bin C.bin aN aC M K bN bC N cN cC  iGEMMBackward into C (C.bin read, then overwritten)
 //   ref_harness gemm_bench M N K steps warmup e2e                   prints one JSON line
+//   ref_harness linear_bench B In Out steps warmup                  Model::Linear -> ReLU -> MSELoss, forward + backward
+//   ref_harness conv_bench N C H W Cout k pad steps warmup          Model::Conv2d -> ReLU -> MSELoss, forward + backward
+//   ref_harness model_bench B S steps warmup                        the README-style segmentation model, one Adam step
+#include <NeuZephyr/Model.cuh>
+#include <NeuZephyr/Optimizer.cuh>
 #include <NeuZephyr/Tensor.cuh>
 #include <NeuZephyr/TensorOperations.cuh>
 
@@ -39,9 +44,79 @@ static double now_ms() {
     return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
 
+// Reference models built with the reference's own Model builders (src/Model.cu).
+class RefLinear : public nz::Model {
+public:
+    nz::nodes::io::InputNode input, target;
+    RefLinear(size_t B, size_t In, size_t Out) : input({B, 1, In, 1}), target({B, 1, Out, 1}) {
+        auto x = Linear(&input, Out);
+        x = ReLU(x);
+        MSELoss(x, &target);
+    }
+};
+class RefConv : public nz::Model {
+public:
+    nz::nodes::io::InputNode input, target;
+    RefConv(size_t N, size_t C, size_t H, size_t W, size_t Co, size_t k, size_t pad)
+        : input({N, C, H, W}), target({N, Co, H + 2 * pad - k + 1, W + 2 * pad - k + 1}) {
+        auto x = Conv2d(&input, Co, k, k, 1, pad);
+        x = ReLU(x);
+        MSELoss(x, &target);
+    }
+};
+class RefSeg : public nz::Model {
+public:
+    nz::nodes::io::InputNode input, target;
+    RefSeg(size_t B, size_t S) : input({B, 3, S, S}), target({B, 1, 16, 1}) {
+        auto x = Conv2d(&input, 16, 3, 3, 1, 1);
+        x = ReLU(x);
+        x = Conv2d(x, 16, 3, 3, 1, 1);
+        x = AvgPool2d(x, 5, 2);
+        x = Linear(x, 16);
+        x = Softmax(x);
+        BCELoss(x, &target);
+    }
+};
+
+template <class M>
+static void time_model(M& model, const char* name, int steps, int warmup, bool update, double images) {
+    model.input.output->randomize(7);
+    model.target.output->fill(0.5f);
+    nz::opt::Adam adam(0.01f, 0.9f, 0.999f);
+    auto step = [&]() {
+        model.forward();
+        model.backward();
+        if (update) model.update(&adam);
+    };
+    for (int i = 0; i < warmup; i++) step();
+    cudaDeviceSynchronize();
+    const double t0 = now_ms();
+    for (int i = 0; i < steps; i++) step();
+    cudaDeviceSynchronize();
+    const double ms = (now_ms() - t0) / steps;
+    printf("{\"mode\": \"%s\", \"ms_per_step\": %.4f, \"img_per_s\": %.3f, \"steps\": %d}\n", name, ms,
+           images / ms * 1e3, steps);
+}
+
 int main(int argc, char** argv) {
     if (argc < 2) return 1;
     const std::string mode = argv[1];
+    if (mode == "linear_bench" && argc == 7) {
+        RefLinear m(atoll(argv[2]), atoll(argv[3]), atoll(argv[4]));
+        time_model(m, "linear_bench", atoi(argv[5]), atoi(argv[6]), false, (double)atoll(argv[2]));
+        return 0;
+    }
+    if (mode == "conv_bench" && argc == 11) {
+        RefConv m(atoll(argv[2]), atoll(argv[3]), atoll(argv[4]), atoll(argv[5]), atoll(argv[6]), atoll(argv[7]),
+                  atoll(argv[8]));
+        time_model(m, "conv_bench", atoi(argv[9]), atoi(argv[10]), false, (double)atoll(argv[2]));
+        return 0;
+    }
+    if (mode == "model_bench" && argc == 6) {
+        RefSeg m(atoll(argv[2]), atoll(argv[3]));
+        time_model(m, "model_bench", atoi(argv[4]), atoi(argv[5]), true, (double)atoll(argv[2]));
+        return 0;
+    }
     if (mode == "gemm_file" && argc == 12) {
         const size_t aN = atoll(argv[5]), aC = atoll(argv[6]), M = atoll(argv[7]), K = atoll(argv[8]);
         const size_t bN = atoll(argv[9]), bC = atoll(argv[10]), N = atoll(argv[11]);
