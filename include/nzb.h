@@ -147,6 +147,25 @@ NZB_API int nzb_gemm_static(const nzb_gemm_desc* desc, const float* A, const flo
                             void* stream);
 
 /*
+ * nzb_gemm for operands and result in HOST memory, as one pipelined call. Replaces the sequence a
+ * NeuZephyr user writes around the GEMM: Tensor::dataInject for A and B (src/Tensor.cu, one
+ * blocking cudaMemcpy each), GEMMTensorCore (include/NeuZephyr/TensorOperations.cuh:1024-1028),
+ * Tensor::hostData for C (another blocking copy). A is cut into row blocks; host-to-device
+ * copies, staging + GEMM per block, and device-to-host copies of finished blocks run on three
+ * streams, so the two PCIe directions overlap each other and the compute.
+ *   - desc: one matrix product (batch extents 1), transA = 0, accumulate = 0, bias NONE / ROW / COL;
+ *     bias, if any, is a host pointer too.
+ *   - host buffers should be pinned (cudaHostAlloc / cudaHostRegister); pageable memory gives the
+ *     same results without the overlap.
+ *   - workspace: device memory, nzb_gemm_host_workspace_bytes (fp32 images of A, B, C + staging).
+ *   - stream: work queued on it before the call precedes the first copy; when the stream reaches
+ *     the end of the call all of C is in host memory.
+ */
+NZB_API int nzb_gemm_host_workspace_bytes(const nzb_gemm_desc* desc, size_t* bytes_out);
+NZB_API int nzb_gemm_host(const nzb_gemm_desc* desc, const float* hostA, const float* hostB, float* hostC,
+                          const float* host_bias, void* workspace, size_t workspace_bytes, void* stream);
+
+/*
  * The GEMM alone on operands that are already staged as fp16: A16 holds op(A) as
  * [nA][M][ldk] and B16 holds op(B)^T as [nB][N][ldk] (both K-major, ldk >= K, ldk % 8 == 0,
  * 16-byte aligned), e.g. written by nzb_cast_f32_f16 or kept as fp16 shadow copies of

@@ -64,6 +64,36 @@ def gemm(A, B, out=None, transA=False, transB=False, bias=None, bias_mode=C.BIAS
     return out
 
 
+def gemm_host(hA, hB, hC=None, transB=False, bias=None, bias_mode=C.BIAS_NONE, relu=False, device=None):
+    """C = A @ op(B) with A, B, C (and bias) in host memory (pinned for overlap) through nzb_gemm_host:
+    copies in, staging + GEMM per row block, and copies out are pipelined on three streams. The call
+    is asynchronous on torch's current stream; synchronise it before reading hC."""
+    for t in (hA, hB, hC, bias):
+        if t is not None and (t.is_cuda or t.dtype != torch.float32 or not t.is_contiguous()):
+            raise ValueError("expected contiguous float32 host tensors")
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    M, K = hA.shape
+    K2, N = (hB.shape[1], hB.shape[0]) if transB else hB.shape
+    if K != K2:
+        raise ValueError("inner dimensions differ")
+    if hC is None:
+        hC = torch.empty((M, N), dtype=torch.float32).pin_memory()
+    d = C.GemmDesc()
+    d.M, d.N, d.K = M, N, K
+    d.lda, d.ldb, d.ldc = hA.shape[1], hB.shape[1], N
+    d.transA, d.transB = 0, int(transB)
+    d.batch[0] = d.batch[1] = 1
+    d.relu = int(relu)
+    d.bias_mode = bias_mode if bias is not None else C.BIAS_NONE
+    d.bias_ld = N
+    n = ctypes.c_size_t(0)
+    C.check(C.lib().nzb_gemm_host_workspace_bytes(ctypes.byref(d), ctypes.byref(n)))
+    ws = _workspace(n.value, device)
+    C.check(C.lib().nzb_gemm_host(ctypes.byref(d), _ptr(hA), _ptr(hB), _ptr(hC), _ptr(bias), _ptr(ws), ws.numel(),
+                                  _stream()))
+    return hC
+
+
 def gemm_f16(A16, B16, M, N, K, out=None, bias=None, bias_mode=C.BIAS_NONE, relu=False, accumulate=False):
     """GEMM on pre-staged K-major fp16 operands A16 [M][ldk], B16 [N][ldk] (nzb_gemm_f16)."""
     if out is None:
