@@ -225,6 +225,96 @@ __global__ void __launch_bounds__(256) avgpool_plane_kernel(float* __restrict__ 
     }
 }
 
+// Compile-time window forms of both pooling kernels (no padding): all loops have fixed trip
+// counts and unroll, and a window that lies inside the image needs no bounds test. The generic
+// kernels below take any other (pool, stride, pad).
+template <int POOL, int STRIDE>
+__global__ void __launch_bounds__(256) avgpool_fixed_kernel(float* __restrict__ out, const float* __restrict__ in, int H,
+                                                            int W, int Ho, int Wo, int planes) {
+    const int per = Ho * Wo;
+    for (int bc = blockIdx.y; bc < planes; bc += gridDim.y) {
+        const float* src = in + (int64_t)bc * H * W;
+        float* dst = out + (int64_t)bc * per;
+        for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < per; idx += gridDim.x * blockDim.x) {
+            const int h = idx / Wo, w = idx - h * Wo;
+            const int h0 = h * STRIDE, w0 = w * STRIDE;
+            const float* base = src + (int64_t)h0 * W + w0;
+            float s = 0.f;
+            if (h0 + POOL <= H && w0 + POOL <= W) {
+#pragma unroll
+                for (int i = 0; i < POOL; i++)
+#pragma unroll
+                    for (int j = 0; j < POOL; j++) s += __ldg(base + i * W + j);
+                dst[idx] = s / (float)(POOL * POOL);
+            } else {
+                int cnt = 0;
+#pragma unroll
+                for (int i = 0; i < POOL; i++)
+#pragma unroll
+                    for (int j = 0; j < POOL; j++)
+                        if (h0 + i < H && w0 + j < W) {
+                            s += __ldg(base + i * W + j);
+                            cnt++;
+                        }
+                dst[idx] = cnt > 0 ? s / (float)cnt : 0.f;
+            }
+        }
+    }
+}
+
+// Four consecutive input columns per thread (W % 4 == 0): the windows that cover them overlap, so
+// each gradient value is loaded once for the four, and the update of the input gradient is one
+// 16-byte read-modify-write. The terms are summed before the single division by pool^2 (the
+// reference adds gout / pool^2 term by term with atomics, in no fixed order; both are within an
+// ulp or two of the exact sum).
+template <int POOL, int STRIDE>
+__global__ void __launch_bounds__(256) avgpool_backward_fixed_kernel(float* __restrict__ gin,
+                                                                     const float* __restrict__ gout, int H, int W,
+                                                                     int Ho, int Wo, int planes) {
+    constexpr int NH = (POOL + STRIDE - 1) / STRIDE;          // windows that can cover one row
+    constexpr int NW = (POOL + 3 + STRIDE - 1) / STRIDE + 1;  // windows that can cover four columns
+    const int W4 = W >> 2, per = H * W4;
+    for (int bc = blockIdx.y; bc < planes; bc += gridDim.y) {
+        const float* g = gout + (int64_t)bc * Ho * Wo;
+        float* dst = gin + (int64_t)bc * H * W;
+        for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < per; idx += gridDim.x * blockDim.x) {
+            const int hi = idx / W4, wi0 = (idx - hi * W4) * 4;
+            const int hn = hi - POOL + STRIDE;
+            const int h_lo = hn <= 0 ? 0 : hn / STRIDE, h_hi = min(hi / STRIDE, Ho - 1);
+            const int wn0 = wi0 - POOL + STRIDE;
+            const int wbase = wn0 <= 0 ? 0 : wn0 / STRIDE;  // first window of column wi0
+            // which of the NW candidate windows covers which of the four columns
+            uint32_t mask = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int wn = wi0 + j - POOL + STRIDE;
+                const int lo = wn <= 0 ? 0 : wn / STRIDE, hi_w = min((wi0 + j) / STRIDE, Wo - 1);
+#pragma unroll
+                for (int d = 0; d < NW; d++)
+                    if (wbase + d >= lo && wbase + d <= hi_w) mask |= 1u << (d * 4 + j);
+            }
+            float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int dh = 0; dh < NH; dh++) {
+                const int h = h_lo + dh;
+                if (h > h_hi) break;
+                const float* grow = g + (int64_t)h * Wo + wbase;
+#pragma unroll
+                for (int d = 0; d < NW; d++) {
+                    const float v = (wbase + d < Wo && ((mask >> (d * 4)) & 15u)) ? __ldg(grow + d) : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 4; j++) s[j] += ((mask >> (d * 4 + j)) & 1u) ? v : 0.f;
+                }
+            }
+            float4* d4 = reinterpret_cast<float4*>(dst + (int64_t)hi * W + wi0);
+            float4 o = *d4;
+            constexpr float full = (float)(POOL * POOL);
+            o.x += s[0] / full; o.y += s[1] / full; o.z += s[2] / full; o.w += s[3] / full;
+            *d4 = o;
+        }
+    }
+}
+
 // Unpadded pooling, four consecutive input columns per thread (W % 4 == 0): the windows that cover
 // them overlap, so each gradient value is loaded once for the four, and the update of the input
 // gradient is one 16-byte read-modify-write. The terms are summed before the single division by
@@ -551,6 +641,16 @@ int nzb_avgpool(float* out, const float* in, int64_t pool, int64_t stride, int64
         const int64_t capx = ((int64_t)ds->sm_count * 16 + planes - 1) / planes;
         if (gx > capx) gx = capx;
         const int64_t gy = planes < 65535 ? planes : 65535;
+        if (pad == 0 && ((pool == 5 && stride == 2) || (pool == 2 && stride == 2) || (pool == 3 && stride == 2))) {
+            const dim3 grid((unsigned)gx, (unsigned)gy);
+            if (pool == 5)
+                avgpool_fixed_kernel<5, 2><<<grid, 256, 0, s>>>(out, in, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+            else if (pool == 3)
+                avgpool_fixed_kernel<3, 2><<<grid, 256, 0, s>>>(out, in, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+            else
+                avgpool_fixed_kernel<2, 2><<<grid, 256, 0, s>>>(out, in, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+            NZB_OPS_EPILOGUE();
+        }
         avgpool_plane_kernel<<<dim3((unsigned)gx, (unsigned)gy), 256, 0, s>>>(out, in, (int)pool, (int)stride, (int)pad,
                                                                              (int)H_in, (int)W_in, (int)H_out,
                                                                              (int)W_out, (int)planes);
@@ -579,6 +679,15 @@ int nzb_avgpool_backward(float* gin, const float* gout, int64_t pool, int64_t st
             int64_t gq = (per / 4 + 255) / 256;
             if (gq > capx) gq = capx;
             const dim3 gridq((unsigned)gq, (unsigned)gy);
+            if (stride == 2 && (pool == 5 || pool == 3 || pool == 2)) {
+                if (pool == 5)
+                    avgpool_backward_fixed_kernel<5, 2><<<gridq, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+                else if (pool == 3)
+                    avgpool_backward_fixed_kernel<3, 2><<<gridq, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+                else
+                    avgpool_backward_fixed_kernel<2, 2><<<gridq, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+                NZB_OPS_EPILOGUE();
+            }
             if (stride == 1)
                 avgpool_backward_quad_kernel<1><<<gridq, 256, 0, s>>>(gin, gout, (int)pool, 1, (int)H_in, (int)W_in,
                                                                       (int)H_out, (int)W_out, (int)planes);

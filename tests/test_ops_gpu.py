@@ -102,7 +102,11 @@ def test_relu(L):
 
 
 @pytest.mark.parametrize("pool,s,p,h,w", [(2, 2, 0, 4, 5), (3, 2, 1, 8, 9), (5, 2, 0, 30, 31), (3, 1, 1, 7, 7),
-                                          (4, 3, 2, 13, 11)])
+                                          (4, 3, 2, 13, 11),
+                                          # widths that are multiples of 4 take the four-column backward kernels,
+                                          # (5|3|2, stride 2, no padding) the compile-time-window kernels
+                                          (5, 2, 0, 30, 32), (5, 2, 0, 21, 68), (3, 2, 0, 17, 40), (2, 2, 0, 10, 36),
+                                          (4, 3, 0, 20, 24), (3, 1, 0, 9, 16), (5, 2, 0, 5, 8)])
 def test_avgpool(L, pool, s, p, h, w):
     rng = np.random.default_rng(pool * 7 + h)
     n, c = 2, 3
