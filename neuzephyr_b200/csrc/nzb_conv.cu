@@ -25,6 +25,8 @@
 // Every wait is bounded as in the GEMM kernel.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "nzb_internal.h"
 #include "nzb_ptx.cuh"
 
@@ -1606,6 +1608,17 @@ static int run_conv(const ConvRun& r, const __half* W16, int64_t Kp, int64_t wN,
     return run_conv_cfg<ConvCfg<16, 8>>(r, W16, Kp, wN, *ds, stream);
 }
 
+// Bytes of staged operands one pass may hold (images are processed in chunks that fit). The
+// environment variable NZB_CONV_STAGE_BYTES overrides the default, which lets tests run the
+// chunked path on small tensors.
+static int64_t stage_budget(int64_t dflt) {
+    static const int64_t env = [] {
+        const char* e = getenv("NZB_CONV_STAGE_BYTES");
+        return e ? atoll(e) : (long long)0;
+    }();
+    return env > 0 ? env : dflt;
+}
+
 // ---- TMA im2col mode: planning and launch ----------------------------------------------------
 struct TmaPlan {
     bool ok;
@@ -1625,7 +1638,7 @@ static TmaPlan tma_plan(int64_t N, int64_t Cin, int64_t Hin, int64_t Win, int64_
     t.Wp = round_up(Wo, 64);  // rows start on 128-byte lines: one TMA request per box row
     t.w_bytes = round_up(wN * R * t.Kt * 2, 256);
     t.per_image = round_up(Kw * Cin * Hin * t.Wp * 2, 256);
-    const int64_t budget = int64_t(1) << 30;
+    const int64_t budget = stage_budget(int64_t(1) << 30);
     int64_t n = budget / (t.per_image > 0 ? t.per_image : 1);
     if (n < 1) n = 1;
     if (n > N) n = N > 0 ? N : 1;
@@ -1760,7 +1773,7 @@ static WgradPlan wgrad_plan(const nzb_conv_desc* d, int64_t Ho, int64_t Wo) {
     t.Wp = round_up(Wo, 64);
     t.cbw = (int32_t)((128 / d->Kh) / 16 * 16);
     t.per_image = round_up(d->Kw * d->C * d->H * t.Wp * 2, 256) + round_up(d->Cout * Ho * t.Wp * 2, 256);
-    const int64_t budget = int64_t(3) << 29;  // 1.5 GiB of staged operands per pass
+    const int64_t budget = stage_budget(int64_t(3) << 29);  // 1.5 GiB of staged operands per pass
     int64_t n = budget / (t.per_image > 0 ? t.per_image : 1);
     if (n < 1) n = 1;
     if (n > d->N) n = d->N > 0 ? d->N : 1;
@@ -1881,7 +1894,7 @@ static int check_conv_desc(const nzb_conv_desc* d, int64_t* Ho, int64_t* Wo) {
 static int64_t weight_grad_stage_bytes(const nzb_conv_desc* d, int64_t HoWo, int64_t* nb_out) {
     const int64_t K = d->C * d->Kh * d->Kw;
     const int64_t per_image = (K + d->Cout) * round_up(HoWo, 64) * 2;
-    const int64_t budget = int64_t(2) << 30;
+    const int64_t budget = stage_budget(int64_t(2) << 30);
     int64_t nb = 1;
     if (!d->weights_per_sample && d->N > 1) {
         int64_t nb_max = budget / (per_image > 0 ? per_image : 1);

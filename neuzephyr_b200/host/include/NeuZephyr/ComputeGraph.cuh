@@ -20,7 +20,8 @@ public:
     void topologicalSort();
     bool isSorted() const { return sorted_; }
     void forward();
-    void backward();
+    // `after_node`, when given, runs after each node's backward (in reverse topological order)
+    void backward(const std::function<void(nodes::Node*)>& after_node = nullptr);
     void zeroGrad() const;
     // Optimizer step, in insertion order, on the nodes whose output requires a gradient
     // (src/ComputeGraph.cu:541-547); gradients are left as they are (Model::update zeroes them,

@@ -28,6 +28,9 @@ public:
 
     void setFused(bool fused) { fused_ = fused; }
     void setCommunicator(dist::Communicator* comm) { comm_ = comm; }
+    // all-reduce each parameter gradient as soon as its last consumer's backward has been queued
+    // (default), or all of them in update() / syncGradients()
+    void setOverlapGradientSync(bool on) { overlap_sync_ = on; }
     // parameter nodes (weights / biases created by the builders), in creation order
     const std::vector<nodes::Node*>& parameters() const { return params_; }
     graph::ComputeGraph& graph() { return computeGraph; }
@@ -58,6 +61,8 @@ private:
     Node* own(Node* n, bool parameter = false);
     bool fused_ = true;
     bool grads_synced_ = false;
+    bool overlap_sync_ = true;
+    std::vector<bool> param_synced_;
     dist::Communicator* comm_ = nullptr;
     std::vector<Node*> params_;
 };

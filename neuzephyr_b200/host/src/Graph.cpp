@@ -58,9 +58,12 @@ void ComputeGraph::forward() {
     if (!sorted_) topologicalSort();
     for (Node* n : sorted_nodes_) n->forward();
 }
-void ComputeGraph::backward() {
+void ComputeGraph::backward(const std::function<void(Node*)>& after_node) {
     if (!sorted_) topologicalSort();
-    for (auto it = sorted_nodes_.rbegin(); it != sorted_nodes_.rend(); ++it) (*it)->backward();
+    for (auto it = sorted_nodes_.rbegin(); it != sorted_nodes_.rend(); ++it) {
+        (*it)->backward();
+        if (after_node) after_node(*it);
+    }
 }
 void ComputeGraph::zeroGrad() const {
     for (Node* n : nodes_) n->output->zeroGrad();
@@ -135,13 +138,38 @@ Tensor& Model::forward() {
     return *computeGraph.getOutputs().at(0)->output;
 }
 void Model::backward() {
-    computeGraph.backward();
     grads_synced_ = false;
+    param_synced_.assign(params_.size(), false);
+    if (!(comm_ && comm_->world() > 1 && overlap_sync_)) {
+        computeGraph.backward();
+        return;
+    }
+    // Data parallel: a parameter's gradient is complete once every node that reads the
+    // parameter has run its backward. Its all-reduce is queued on the communication stream at
+    // that point (ordered after the gradient's writers by the stream manager), so it runs
+    // under the rest of the backward pass. Every rank walks the same graph in the same order,
+    // so the collectives are issued in the same order everywhere.
+    std::vector<int> remaining(params_.size(), 0);
+    for (Node* n : computeGraph.getNodes())
+        for (Node* in : n->inputs)
+            for (size_t i = 0; i < params_.size(); i++)
+                if (params_[i] == in) remaining[i]++;
+    computeGraph.backward([&](Node* n) {
+        for (Node* in : n->inputs)
+            for (size_t i = 0; i < params_.size(); i++)
+                if (params_[i] == in && --remaining[i] == 0) {
+                    comm_->allReduceAverage(in->output->grad(), in->output->size());
+                    param_synced_[i] = true;
+                }
+    });
 }
 void Model::syncGradients() {
     if (comm_ && comm_->world() > 1 && !grads_synced_)
-        for (Node* p : params_) comm_->allReduceAverage(p->output->grad(), p->output->size());
+        for (size_t i = 0; i < params_.size(); i++)
+            if (i >= param_synced_.size() || !param_synced_[i])
+                comm_->allReduceAverage(params_[i]->output->grad(), params_[i]->output->size());
     grads_synced_ = true;
+    param_synced_.assign(params_.size(), true);
 }
 void Model::update(opt::Optimizer* optimizer) {
     computeGraph.update(optimizer, [this]() { syncGradients(); });

@@ -2,6 +2,8 @@
 against the host oracle's restatement of NeuZephyr's Img2Col -> MatMul -> Bias -> Col2Img
 composition. e_max = max|x - ref| / max|ref| <= 2e-5 against the fp64 result on fp16-rounded
 operands (fp32 accumulation order is the only difference), <= 1e-2 against unrounded operands."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -115,3 +117,43 @@ def test_conv_backward_weight(nz, n, c, h, w, co, k, s, p, per_sample):
     torch.cuda.synchronize()
     assert nz.device_status() == 0
     assert emax(dw.cpu().numpy() - dw0, dw_ref) <= 5e-5
+
+
+def test_conv_chunked_staging_subprocess():
+    """With a tiny staging budget the three directions process the batch in chunks of one or two images
+    (the path large batches take); results must not change. Runs in a child process because the budget
+    is read once per process."""
+    import subprocess
+    import sys
+    code = r"""
+import numpy as np, torch, sys
+sys.path.insert(0, %r)
+import neuzephyr_b200 as nz
+from oracle import nz_oracle as O
+def emax(x, ref):
+    ref = np.asarray(ref, np.float64); den = np.max(np.abs(ref)) or 1.0
+    return float(np.max(np.abs(np.asarray(x, np.float64) - ref)) / den)
+dev = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).cuda()
+for (n, c, h, w, co, k, p, per_sample) in [(5, 16, 9, 40, 16, 3, 1, False), (5, 3, 8, 64, 20, 3, 1, True)]:
+    rng = np.random.default_rng(n + c + co)
+    x = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)
+    wn = n if per_sample else 1
+    wt = (rng.normal(0, 1, (wn, 1, c * k * k, co)) * np.sqrt(2.0 / (c * k * k))).astype(np.float32)
+    ho, wo = O.conv_out_hw(h, w, k, k, 1, p)
+    bias = rng.normal(0, 1, (1, 1, ho * wo, co)).astype(np.float32)
+    y = nz.conv2d_forward(dev(x), dev(wt), dev(bias), k, k, 1, p).cpu().numpy()
+    assert emax(y, O.conv2d_forward(x, wt, bias, k, k, 1, p, True)) <= 3e-5
+    dy = rng.normal(0, 1, y.shape).astype(np.float32)
+    dx0 = rng.normal(0, 1, x.shape).astype(np.float32)
+    dw0 = rng.normal(0, 1, wt.shape).astype(np.float32)
+    rdx, rdw, _ = O.conv2d_backward(dy, x, wt, k, k, 1, p, want_db=False)
+    dx = dev(dx0); nz.conv2d_backward_data(dev(dy), dev(wt), x.shape, k, k, 1, p, dx)
+    assert emax(dx.cpu().numpy() - dx0, rdx) <= 5e-5
+    dw = dev(dw0); nz.conv2d_backward_weight(dev(x), dev(dy), wt.shape, k, k, 1, p, dw)
+    assert emax(dw.cpu().numpy() - dw0, rdw) <= 5e-5
+    torch.cuda.synchronize(); assert nz.device_status() == 0
+print("chunked ok")
+""" % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NZB_CONV_STAGE_BYTES="40000")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=env, timeout=300)
+    assert r.returncode == 0 and "chunked ok" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
