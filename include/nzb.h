@@ -268,6 +268,22 @@ NZB_API int nzb_conv2d_backward_weight(const nzb_conv_desc* desc, const float* x
  */
 NZB_API int nzb_conv2d_backward_bias(const nzb_conv_desc* desc, const float* dy, float* dbias, void* stream);
 
+/*
+ * The whole backward of one convolution layer on shared staging: dbias += sum over images of dY',
+ * dW += ..., dX += ..., with dY' = dY * (Y > 0) when desc->relu is set (y is the layer's forward
+ * output). Stands in for the same reference code as the three calls above plus ReLUNode::backward
+ * (src/Nodes.cu), but reads dY once: one pass masks it, writes the fp16 copies both tensor-core
+ * kernels consume and accumulates the bias gradient. Any of dx, dw, dbias may be null.
+ *   - handled shapes: stride 1, square kernel up to 4x4, pad <= K-1, input and output rows of at
+ *     least 32 pixels, bias gradient as the {Ho*Wo, Cout} matrix (desc->bias_mode NZB_BIAS_MATRIX);
+ *     nzb_conv2d_backward_workspace_bytes returns NZB_ERR_UNSUPPORTED otherwise and the caller
+ *     uses the separate entry points.
+ */
+NZB_API int nzb_conv2d_backward_workspace_bytes(const nzb_conv_desc* desc, size_t* bytes_out);
+NZB_API int nzb_conv2d_backward(const nzb_conv_desc* desc, const float* x, const float* w, const float* y,
+                                const float* dy, float* dx, float* dw, float* dbias, void* workspace,
+                                size_t workspace_bytes, void* stream);
+
 /* Node operations around the contraction ---------------------------------------------- */
 
 /*

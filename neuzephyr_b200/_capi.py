@@ -16,7 +16,7 @@ EXPORTS = [
     "nzb_gemm_backward", "nzb_cast_f32_f16",
     "nzb_linear_workspace_bytes", "nzb_linear_forward", "nzb_linear_backward",
     "nzb_conv2d_workspace_bytes", "nzb_conv2d_forward", "nzb_conv2d_backward_data", "nzb_conv2d_backward_weight",
-    "nzb_conv2d_backward_bias",
+    "nzb_conv2d_backward_bias", "nzb_conv2d_backward_workspace_bytes", "nzb_conv2d_backward",
     "nzb_img2col", "nzb_img2col_backward", "nzb_col2img", "nzb_col2img_backward", "nzb_add_broadcast",
     "nzb_add_backward", "nzb_relu", "nzb_relu_backward", "nzb_avgpool", "nzb_avgpool_backward", "nzb_softmax",
     "nzb_softmax_backward", "nzb_bce", "nzb_bce_backward", "nzb_adam", "nzb_fill", "nzb_expand", "nzb_scale",
@@ -91,6 +91,8 @@ def lib():
         L.nzb_conv2d_backward_data.argtypes = [cd, vp, vp, vp, vp, sz, vp]
         L.nzb_conv2d_backward_weight.argtypes = [cd, vp, vp, vp, vp, sz, vp]
         L.nzb_conv2d_backward_bias.argtypes = [cd, vp, vp, vp]
+        L.nzb_conv2d_backward_workspace_bytes.argtypes = [cd, ctypes.POINTER(sz)]
+        L.nzb_conv2d_backward.argtypes = [cd, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp]
         L.nzb_img2col.argtypes = [vp, vp] + [i64] * 10 + [vp]
         L.nzb_img2col_backward.argtypes = [vp, vp] + [i64] * 10 + [vp]
         L.nzb_col2img.argtypes = [vp, vp] + [i64] * 4 + [vp]

@@ -1025,6 +1025,76 @@ __global__ void __launch_bounds__(256) shift_copies_kernel(__half* __restrict__ 
     }
 }
 
+// One pass over dY for the whole backward of a convolution layer: applies ReLU's mask (Y > 0),
+// writes the KW shifted fp16 copies the data-gradient kernel reads (copy `pad` is the unshifted one,
+// which the weight-gradient kernel reads) and adds the batch sum into the {Ho*Wo, Cout} bias-gradient
+// matrix. A block owns 32 channels x 64 pixels of one output row and walks the images of the chunk,
+// so every bias element has one owner (no atomics) and is written once, through a shared-memory
+// transpose that makes the [pixel][channel] writes contiguous.
+template <int KW, int CT>
+__global__ void __launch_bounds__(256) dy_prepare_kernel(__half* __restrict__ xs, const float* __restrict__ dy,
+                                                         const float* __restrict__ ymask, float* __restrict__ dbias,
+                                                         int n, int Cout, int Ho, int Wo, int Wp, int pad, int only_kw) {
+    // a block owns CT channels x PX pixels of one output row (CT = 16 or 32, PX = 128 or 64)
+    constexpr int UNITS = 256 / CT, PX = UNITS * 8;
+    __shared__ float tile[PX][CT + 1];
+    const int segs = (Wp + PX - 1) / PX, cblks = (Cout + CT - 1) / CT;
+    const int co_l = threadIdx.x / UNITS, w8 = threadIdx.x % UNITS;
+    const int64_t copy_stride = (int64_t)n * Cout * Ho * Wp;
+    for (int64_t blk = blockIdx.x; blk < (int64_t)cblks * Ho * segs; blk += gridDim.x) {
+        const int seg = (int)(blk % segs);
+        const int ho = (int)((blk / segs) % Ho);
+        const int cb = (int)(blk / ((int64_t)segs * Ho));
+        const int co = cb * CT + co_l, w0 = seg * PX + w8 * 8;
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[j] = 0.f;
+        if (co < Cout && w0 < Wp) {
+            for (int img = 0; img < n; img++) {
+                const int64_t row = ((int64_t)img * Cout + co) * Ho + ho;
+                const float* src = dy + row * Wo;
+                const float* msk = ymask ? ymask + row * Wo : nullptr;
+                float v[8 + KW - 1];
+#pragma unroll
+                for (int j = 0; j < 8 + KW - 1; j++) {
+                    const int w = w0 + j - pad;
+                    float g = (unsigned)w < (unsigned)Wo ? __ldg(src + w) : 0.f;
+                    if (msk && (unsigned)w < (unsigned)Wo && !(__ldg(msk + w) > 0.f)) g = 0.f;
+                    v[j] = g;
+                }
+#pragma unroll
+                for (int kw = 0; kw < KW; kw++) {
+                    if (only_kw >= 0 && kw != only_kw) continue;
+                    uint4 o;
+                    __half2 t;
+                    t = __floats2half2_rn(v[kw], v[kw + 1]); o.x = *reinterpret_cast<uint32_t*>(&t);
+                    t = __floats2half2_rn(v[kw + 2], v[kw + 3]); o.y = *reinterpret_cast<uint32_t*>(&t);
+                    t = __floats2half2_rn(v[kw + 4], v[kw + 5]); o.z = *reinterpret_cast<uint32_t*>(&t);
+                    t = __floats2half2_rn(v[kw + 6], v[kw + 7]); o.w = *reinterpret_cast<uint32_t*>(&t);
+                    *reinterpret_cast<uint4*>(xs + kw * copy_stride + row * Wp + w0) = o;
+                }
+                if (dbias) {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) acc[j] += v[j + pad];  // pad <= KW - 1: the unshifted values
+                }
+            }
+        }
+        if (dbias) {
+#pragma unroll
+            for (int j = 0; j < 8; j++) tile[w8 * 8 + j][co_l] = acc[j];
+            __syncthreads();
+            const int c2 = threadIdx.x % CT;
+#pragma unroll
+            for (int i = 0; i < PX * CT / 256; i++) {
+                const int px = threadIdx.x / CT + i * (256 / CT);
+                const int w = seg * PX + px, c = cb * CT + c2;
+                if (w < Wo && c < Cout) dbias[((int64_t)ho * Wo + w) * Cout + c] += tile[px][c2];
+            }
+            __syncthreads();
+        }
+    }
+}
+
 // Weight staging for the TMA im2col mode, forward (flip = 0) and backward-data (flip = 1) forms.
 //   out[wb][r][k'],  k' = (kw*CB + cb)*64 + ci*Kh + kh,  cin = cb*16 + ci  (zero for cin >= Cin and
 //   for the columns 16*Kh..63 of every block: a block is one aligned 128-byte row segment, so a
@@ -1642,6 +1712,7 @@ static TmaPlan tma_plan(int64_t N, int64_t Cin, int64_t Hin, int64_t Win, int64_
     int64_t n = budget / (t.per_image > 0 ? t.per_image : 1);
     if (n < 1) n = 1;
     if (n > N) n = N > 0 ? N : 1;
+    if (N > 0) n = (N + (N + n - 1) / n - 1) / ((N + n - 1) / n);  // equal-sized passes
     t.nchunk = n;
     if (t.Kt > INT32_MAX - 256 || Cin > INT32_MAX || R > INT32_MAX) t.ok = false;
     return t;
@@ -1657,6 +1728,7 @@ struct ConvTmaRun {
     int64_t N, Cin, Hin, Win, R, Kh, Kw, pad, Ho, Wo;
     int64_t layerC, layerCout;  // the layer's own channel counts (weight tensor extents)
     int32_t w_per_sample, bias_mode, accumulate, relu, flip;
+    const __half* staged;  // shifted copies of exactly these N images, already written (skips the staging pass)
 };
 
 template <class Cfg>
@@ -1706,10 +1778,12 @@ static int run_conv_tma_cfg(const ConvTmaRun& r, const TmaPlan& pl, void* ws, co
     p.relu = r.relu;
     p.stage_tx = (uint32_t)(2 * 64 * r.Kh * 16 * 2 + Cfg::B_BYTES);
     p.status = ds.status_dev;
-    for (int64_t img0 = 0; img0 < r.N; img0 += pl.nchunk) {
-        const int64_t n = r.N - img0 < pl.nchunk ? r.N - img0 : pl.nchunk;
+    const int64_t chunk = r.staged ? r.N : pl.nchunk;
+    if (r.staged) XS = const_cast<__half*>(r.staged);
+    for (int64_t img0 = 0; img0 < r.N; img0 += chunk) {
+        const int64_t n = r.N - img0 < chunk ? r.N - img0 : chunk;
         const int64_t rows = n * r.Cin * r.Hin;
-        {
+        if (!r.staged) {
             const int64_t total = rows * (pl.Wp / 8);
             int64_t blocks = (total + 255) / 256;
             if (blocks > (int64_t)ds.sm_count * 32) blocks = (int64_t)ds.sm_count * 32;
@@ -1777,13 +1851,23 @@ static WgradPlan wgrad_plan(const nzb_conv_desc* d, int64_t Ho, int64_t Wo) {
     int64_t n = budget / (t.per_image > 0 ? t.per_image : 1);
     if (n < 1) n = 1;
     if (n > d->N) n = d->N > 0 ? d->N : 1;
+    if (d->N > 0) n = (d->N + (d->N + n - 1) / n - 1) / ((d->N + n - 1) / n);  // equal-sized passes
     t.nchunk = n;
     return t;
 }
 
+// Operands staged by the caller for all d->N images: the shifted copies of x (pitch pl.Wp) and one
+// unshifted fp16 copy of dY with its own pitch.
+struct WgradStaged {
+    const __half* xs;
+    const __half* dy16;
+    int64_t dy_wp;
+};
+
 template <class Cfg>
 static int run_wgrad_tma_cfg(const nzb_conv_desc* d, const WgradPlan& pl, const float* x, const float* dy, float* dw,
-                             void* ws, int64_t Ho, int64_t Wo, const DeviceState& ds, cudaStream_t stream) {
+                             void* ws, int64_t Ho, int64_t Wo, const DeviceState& ds, cudaStream_t stream,
+                             const WgradStaged* st = nullptr) {
     EncodeTiledFn enc;
     int rc = get_encode_tiled(&enc);
     if (rc != NZB_OK) return rc;
@@ -1804,11 +1888,14 @@ static int run_wgrad_tma_cfg(const nzb_conv_desc* d, const WgradPlan& pl, const 
     p.w_per_sample = d->weights_per_sample ? 1 : 0;
     p.stage_tx = (uint32_t)(2 * 64 * d->Kh * pl.cbw * 2 + 2 * 64 * Cfg::BN * 2);
     p.status = ds.status_dev;
-    for (int64_t img0 = 0; img0 < d->N; img0 += pl.nchunk) {
-        const int64_t n = d->N - img0 < pl.nchunk ? d->N - img0 : pl.nchunk;
-        __half* XS = reinterpret_cast<__half*>(ws);
-        __half* DY = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(ws) + round_up(d->Kw * n * d->C * d->H * pl.Wp * 2, 256));
-        {
+    const int64_t chunk = st ? d->N : pl.nchunk;
+    for (int64_t img0 = 0; img0 < d->N; img0 += chunk) {
+        const int64_t n = d->N - img0 < chunk ? d->N - img0 : chunk;
+        __half* XS = st ? const_cast<__half*>(st->xs) : reinterpret_cast<__half*>(ws);
+        __half* DY = st ? const_cast<__half*>(st->dy16)
+                        : reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(ws) + round_up(d->Kw * n * d->C * d->H * pl.Wp * 2, 256));
+        const int64_t dy_wp = st ? st->dy_wp : pl.Wp;
+        if (!st) {
             const int64_t rows = n * d->C * d->H;
             int64_t blocks = (rows * (pl.Wp / 8) + 255) / 256;
             if (blocks > (int64_t)ds.sm_count * 32) blocks = (int64_t)ds.sm_count * 32;
@@ -1839,8 +1926,9 @@ static int run_wgrad_tma_cfg(const nzb_conv_desc* d, const WgradPlan& pl, const 
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
             if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (shifted copies) failed with CUresult %d", (int)cr);
-            cuuint64_t dims2[4] = {(cuuint64_t)pl.Wp, (cuuint64_t)Ho, (cuuint64_t)d->Cout, (cuuint64_t)n};
-            cuuint64_t strides2[3] = {row_b, row_b * Ho, row_b * Ho * d->Cout};
+            const cuuint64_t row_b2 = (cuuint64_t)dy_wp * 2;
+            cuuint64_t dims2[4] = {(cuuint64_t)dy_wp, (cuuint64_t)Ho, (cuuint64_t)d->Cout, (cuuint64_t)n};
+            cuuint64_t strides2[3] = {row_b2, row_b2 * Ho, row_b2 * Ho * d->Cout};
             cuuint32_t box2[4] = {64, 1, (cuuint32_t)Cfg::BN, 1};
             cuuint32_t estr2[4] = {1, 1, 1, 1};
             cr = enc(&tmDY, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, DY, dims2, strides2, box2, estr2,
@@ -1867,14 +1955,45 @@ static int run_wgrad_tma_cfg(const nzb_conv_desc* d, const WgradPlan& pl, const 
 }
 
 static int run_wgrad_tma(const nzb_conv_desc* d, const WgradPlan& pl, const float* x, const float* dy, float* dw, void* ws,
-                         int64_t Ho, int64_t Wo, cudaStream_t stream) {
+                         int64_t Ho, int64_t Wo, cudaStream_t stream, const WgradStaged* st = nullptr) {
     DeviceState* ds;
     int rc = get_device_state(&ds);
     if (rc != NZB_OK) return rc;
-    if (d->Cout > 64) return run_wgrad_tma_cfg<WgradCfg<128, 3>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream);
-    if (d->Cout > 32) return run_wgrad_tma_cfg<WgradCfg<64, 4>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream);
-    if (d->Cout > 16) return run_wgrad_tma_cfg<WgradCfg<32, 5>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream);
-    return run_wgrad_tma_cfg<WgradCfg<16, 6>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream);
+    if (d->Cout > 64) return run_wgrad_tma_cfg<WgradCfg<128, 3>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream, st);
+    if (d->Cout > 32) return run_wgrad_tma_cfg<WgradCfg<64, 4>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream, st);
+    if (d->Cout > 16) return run_wgrad_tma_cfg<WgradCfg<32, 5>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream, st);
+    return run_wgrad_tma_cfg<WgradCfg<16, 6>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream, st);
+}
+
+// ---- whole backward of one layer on shared staging ------------------------------------------------
+struct BackwardPlan {
+    bool ok;
+    TmaPlan dx;      // data-gradient plan for one chunk (N = nchunk)
+    WgradPlan wg;
+    int64_t wp_dy;   // pitch of the dY copies (= the data-gradient kernel's input pitch)
+    int64_t x_bytes, dy_bytes;  // per image
+    int64_t nchunk;
+    int64_t total;
+};
+static BackwardPlan backward_plan(const nzb_conv_desc* d, int64_t Ho, int64_t Wo) {
+    BackwardPlan b{};
+    const int64_t wN1 = d->weights_per_sample ? 1 : 0;
+    b.wg = wgrad_plan(d, Ho, Wo);
+    b.ok = b.wg.ok && d->Kh == d->Kw && d->pad <= d->Kh - 1 && d->W >= 32 &&
+           (d->bias_mode == NZB_BIAS_MATRIX || d->bias_mode == NZB_BIAS_NONE);
+    b.wp_dy = round_up(d->W, 64);
+    b.x_bytes = round_up(d->Kw * d->C * d->H * b.wg.Wp * 2, 256);
+    b.dy_bytes = round_up(d->Kw * d->Cout * Ho * b.wp_dy * 2, 256);
+    const int64_t budget = stage_budget(int64_t(3) << 29);
+    int64_t n = budget / (b.x_bytes + b.dy_bytes);
+    if (n < 1) n = 1;
+    if (n > d->N) n = d->N > 0 ? d->N : 1;
+    if (d->N > 0) n = (d->N + (d->N + n - 1) / n - 1) / ((d->N + n - 1) / n);
+    b.nchunk = n;
+    b.dx = tma_plan(n, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W, wN1 ? n : 1);
+    b.ok = b.ok && b.dx.ok;
+    b.total = b.dx.w_bytes + n * (b.x_bytes + b.dy_bytes);
+    return b;
 }
 
 static int check_conv_desc(const nzb_conv_desc* d, int64_t* Ho, int64_t* Wo) {
@@ -1954,7 +2073,7 @@ int nzb_conv2d_forward(const nzb_conv_desc* d, const float* x, const float* w, c
         const TmaPlan tp = tma_plan(d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, Ho, Wo, wN);
         if (tp.ok) {
             ConvTmaRun r{x, y, bias, w, d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->pad, Ho, Wo, d->C, d->Cout,
-                         d->weights_per_sample ? 1 : 0, d->bias_mode, d->accumulate ? 1 : 0, d->relu ? 1 : 0, 0};
+                         d->weights_per_sample ? 1 : 0, d->bias_mode, d->accumulate ? 1 : 0, d->relu ? 1 : 0, 0, nullptr};
             return run_conv_tma(r, tp, workspace, s);
         }
     }
@@ -1992,7 +2111,7 @@ int nzb_conv2d_backward_data(const nzb_conv_desc* d, const float* dy, const floa
         const TmaPlan tp = tma_plan(d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W, wN);
         if (tp.ok) {
             ConvTmaRun r{dy, dx, nullptr, w, d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->Kh - 1 - d->pad, d->H, d->W,
-                         d->C, d->Cout, d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, 1, 0, 1};
+                         d->C, d->Cout, d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, 1, 0, 1, nullptr};
             return run_conv_tma(r, tp, workspace, s);
         }
     }
@@ -2065,6 +2184,99 @@ int nzb_conv2d_backward_weight(const nzb_conv_desc* d, const float* x, const flo
         g.accumulate = 1;
         rc = launch_gemm(g, s);
         if (rc != NZB_OK) return rc;
+    }
+    return NZB_OK;
+}
+
+int nzb_conv2d_backward_workspace_bytes(const nzb_conv_desc* d, size_t* bytes_out) {
+    if (!bytes_out) return fail(NZB_ERR_BAD_ARG, "bytes_out is null");
+    int64_t Ho, Wo;
+    int rc = check_conv_desc(d, &Ho, &Wo);
+    if (rc != NZB_OK) return rc;
+    const BackwardPlan b = backward_plan(d, Ho, Wo);
+    if (!b.ok) return fail(NZB_ERR_UNSUPPORTED, "the one-pass backward needs stride 1, a square kernel of at most 4x4, pad <= K-1, rows of 32+ pixels and a matrix (or no) bias gradient; use the separate backward calls");
+    *bytes_out = (size_t)round_up(b.total, 256);
+    return NZB_OK;
+}
+
+int nzb_conv2d_backward(const nzb_conv_desc* d, const float* x, const float* w, const float* y, const float* dy,
+                        float* dx, float* dw, float* dbias, void* workspace, size_t workspace_bytes, void* stream) {
+    int64_t Ho, Wo;
+    int rc = check_conv_desc(d, &Ho, &Wo);
+    if (rc != NZB_OK) return rc;
+    if (d->N == 0) return NZB_OK;
+    if (!dy) return fail(NZB_ERR_BAD_ARG, "dy must be non-null");
+    if ((dx && !w) || (dw && !x)) return fail(NZB_ERR_BAD_ARG, "dx needs w and dw needs x");
+    if (d->relu && !y) return fail(NZB_ERR_BAD_ARG, "the ReLU mask needs the forward output y");
+    if (dbias && d->bias_mode != NZB_BIAS_MATRIX) return fail(NZB_ERR_UNSUPPORTED, "the one-pass backward writes the {Ho*Wo, Cout} bias gradient; bias_mode must be NZB_BIAS_MATRIX");
+    const BackwardPlan b = backward_plan(d, Ho, Wo);
+    if (!b.ok) return fail(NZB_ERR_UNSUPPORTED, "shape not handled by the one-pass backward; use the separate backward calls");
+    if (!workspace || workspace_bytes < (size_t)b.total) return fail(NZB_ERR_WORKSPACE, "workspace of %lld bytes needed", (long long)b.total);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(NZB_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    DeviceState* ds;
+    rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    uint8_t* base = reinterpret_cast<uint8_t*>(workspace);
+    const int64_t K = d->C * d->Kh * d->Kw, padb = d->Kh - 1 - d->pad;
+    for (int64_t img0 = 0; img0 < d->N; img0 += b.nchunk) {
+        const int64_t n = d->N - img0 < b.nchunk ? d->N - img0 : b.nchunk;
+        __half* XSdy = reinterpret_cast<__half*>(base + b.dx.w_bytes);
+        __half* XSx = reinterpret_cast<__half*>(base + b.dx.w_bytes + n * b.dy_bytes);
+        const float* dy_c = dy + img0 * d->Cout * Ho * Wo;
+        const float* y_c = (d->relu && y) ? y + img0 * d->Cout * Ho * Wo : nullptr;
+        const float* x_c = x ? x + img0 * d->C * d->H * d->W : nullptr;
+        const float* w_c = (w && d->weights_per_sample) ? w + img0 * K * d->Cout : w;
+        {
+            // one pass over dY: mask, the Kw shifted copies, bias gradient
+            const int only_kw = dx ? -1 : (int)padb;  // without a data gradient only the unshifted copy is needed
+            const bool narrow = d->Cout <= 16;
+            const int64_t blocks_all = narrow ? ((d->Cout + 15) / 16) * Ho * ((b.wp_dy + 127) / 128)
+                                              : ((d->Cout + 31) / 32) * Ho * (b.wp_dy / 64);
+            const int64_t blocks = blocks_all < (int64_t)ds->sm_count * 16 ? blocks_all : (int64_t)ds->sm_count * 16;
+#define NZB_DY_PREPARE(KW)                                                                                          \
+    if (narrow)                                                                                                     \
+        dy_prepare_kernel<KW, 16><<<(unsigned)blocks, 256, 0, s>>>(XSdy, dy_c, y_c, dbias, (int)n, (int)d->Cout,      \
+                                                                   (int)Ho, (int)Wo, (int)b.wp_dy, (int)padb, only_kw); \
+    else                                                                                                            \
+        dy_prepare_kernel<KW, 32><<<(unsigned)blocks, 256, 0, s>>>(XSdy, dy_c, y_c, dbias, (int)n, (int)d->Cout,      \
+                                                                   (int)Ho, (int)Wo, (int)b.wp_dy, (int)padb, only_kw)
+            switch (d->Kw) {
+                case 1: NZB_DY_PREPARE(1); break;
+                case 2: NZB_DY_PREPARE(2); break;
+                case 3: NZB_DY_PREPARE(3); break;
+                default: NZB_DY_PREPARE(4); break;
+            }
+#undef NZB_DY_PREPARE
+            NZB_CUDA_TRY(cudaGetLastError());
+        }
+        nzb_conv_desc dc = *d;
+        dc.N = n;
+        if (dw) {
+            const int64_t rows = n * d->C * d->H;
+            int64_t blocks = (rows * (b.wg.Wp / 8) + 255) / 256;
+            if (blocks > (int64_t)ds->sm_count * 32) blocks = (int64_t)ds->sm_count * 32;
+            switch (d->Kw) {
+                case 1: shift_copies_kernel<1><<<(unsigned)blocks, 256, 0, s>>>(XSx, x_c, rows, (int)d->W, (int)b.wg.Wp, (int)d->pad); break;
+                case 2: shift_copies_kernel<2><<<(unsigned)blocks, 256, 0, s>>>(XSx, x_c, rows, (int)d->W, (int)b.wg.Wp, (int)d->pad); break;
+                case 3: shift_copies_kernel<3><<<(unsigned)blocks, 256, 0, s>>>(XSx, x_c, rows, (int)d->W, (int)b.wg.Wp, (int)d->pad); break;
+                default: shift_copies_kernel<4><<<(unsigned)blocks, 256, 0, s>>>(XSx, x_c, rows, (int)d->W, (int)b.wg.Wp, (int)d->pad); break;
+            }
+            NZB_CUDA_TRY(cudaGetLastError());
+            // copy number padb of the dY copies is the unshifted one
+            WgradStaged st{XSx, XSdy + padb * (n * d->Cout * Ho * b.wp_dy), b.wp_dy};
+            float* dw_c = dw + (d->weights_per_sample ? img0 * K * d->Cout : 0);
+            rc = run_wgrad_tma(&dc, b.wg, x_c, dy_c, dw_c, nullptr, Ho, Wo, s, &st);
+            if (rc != NZB_OK) return rc;
+        }
+        if (dx) {
+            TmaPlan pl = tma_plan(n, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W,
+                                  d->weights_per_sample ? n : 1);
+            ConvTmaRun r{dy_c, dx + img0 * d->C * d->H * d->W, nullptr, w_c, n, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, padb,
+                         d->H, d->W, d->C, d->Cout, d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, 1, 0, 1, XSdy};
+            rc = run_conv_tma(r, pl, base, s);
+            if (rc != NZB_OK) return rc;
+        }
     }
     return NZB_OK;
 }

@@ -293,6 +293,29 @@ void Conv2dNode::backward() {
     const Tensor& x = *inputs[0]->output;
     const Tensor& w = *inputs[1]->output;
     nzb_conv_desc d = conv_desc(x, w, kh_, kw_, stride_, pad_);
+    {
+        // one library call for the whole layer when the shape allows: dY is read once (ReLU mask,
+        // fp16 copies for both tensor-core kernels, bias gradient), nothing is materialised
+        nzb_conv_desc f = d;
+        const bool want_db = inputs.size() > 2 && inputs[2]->output->requiresGrad();
+        f.relu = relu_;
+        f.bias_mode = want_db ? NZB_BIAS_MATRIX : NZB_BIAS_NONE;
+        size_t fused_bytes = 0;
+        if (nzb_conv2d_backward_workspace_bytes(&f, &fused_bytes) == NZB_OK) {
+            float* db = want_db ? inputs[2]->output->grad() : nullptr;
+            float* dw = w.requiresGrad() ? w.grad() : nullptr;
+            float* dx = x.requiresGrad() ? x.grad() : nullptr;
+            const float* y = relu_ ? output->data() : nullptr;
+            const float* g = output->grad();
+            SM::Instance().run({db, dw, dx}, {x.data(), w.data(), y, g}, [&](cudaStream_t s) {
+                void* ws = SM::Instance().scratch(fused_bytes, s);
+                const int rc = nzb_conv2d_backward(&f, x.data(), w.data(), y, g, dx, dw, db, ws, fused_bytes, s);
+                SM::Instance().releaseScratch(ws, s);
+                NZB_CHECK(rc);
+            });
+            return;
+        }
+    }
     float* dy = output->grad();
     if (relu_) {
         // dY' = dY * (Y > 0), kept in a private buffer so that output->grad() is left as received

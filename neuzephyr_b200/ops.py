@@ -209,6 +209,21 @@ def conv2d_backward_bias(dy, x_shape, w_shape, Kh, Kw, stride, pad, dbias):
     return dbias
 
 
+def conv2d_backward(x, w, dy, Kh, Kw, stride, pad, dx=None, dw=None, dbias=None, y=None):
+    """The whole backward of one layer through nzb_conv2d_backward (dY read once): accumulates into the
+    given dx / dw / dbias ({1,1,Ho*Wo,Cout}); y, when given, is the forward output whose sign masks dY
+    (a layer with a fused ReLU). Raises for shapes the one-pass form does not take."""
+    _check_f32_cuda(x, w, dy, dx, dw, dbias, y)
+    d = _conv_desc(x.shape, w.shape, Kh, Kw, stride, pad)
+    d.bias_mode = C.BIAS_MATRIX if dbias is not None else C.BIAS_NONE
+    d.relu = int(y is not None)
+    n = ctypes.c_size_t(0)
+    C.check(C.lib().nzb_conv2d_backward_workspace_bytes(ctypes.byref(d), ctypes.byref(n)))
+    ws = _workspace(n.value, x.device)
+    C.check(C.lib().nzb_conv2d_backward(ctypes.byref(d), _ptr(x), _ptr(w), _ptr(y), _ptr(dy), _ptr(dx), _ptr(dw),
+                                        _ptr(dbias), _ptr(ws), ws.numel(), _stream()))
+
+
 def _linear_desc(batch, fin, fout, relu):
     d = C.LinearDesc()
     d.batch, d.in_features, d.out_features, d.relu = batch, fin, fout, int(relu)

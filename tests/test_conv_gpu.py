@@ -119,6 +119,38 @@ def test_conv_backward_weight(nz, n, c, h, w, co, k, s, p, per_sample):
     assert emax(dw.cpu().numpy() - dw0, dw_ref) <= 5e-5
 
 
+@pytest.mark.parametrize("n,c,h,w,co,k,p,per_sample,relu", [
+    (2, 16, 20, 48, 16, 3, 1, False, True), (3, 16, 7, 256, 16, 3, 1, True, False), (1, 64, 6, 224, 128, 3, 1, False, True),
+    (2, 40, 9, 35, 20, 3, 0, False, False), (1, 6, 8, 70, 33, 2, 1, False, True), (1, 20, 9, 60, 65, 4, 2, True, True),
+    (2, 3, 5, 300, 16, 3, 2, False, False)])
+def test_conv_backward_one_pass(nz, n, c, h, w, co, k, p, per_sample, relu):
+    """nzb_conv2d_backward (dY read once: mask, fp16 copies, bias gradient; then both tensor-core kernels on
+    the shared copies) against the oracle's backward of Conv2d (+ReLU)."""
+    rng = np.random.default_rng(n * 13 + c + co)
+    x = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)
+    wn = n if per_sample else 1
+    wt = (rng.normal(0, 1, (wn, 1, c * k * k, co)) * np.sqrt(2.0 / (c * k * k))).astype(np.float32)
+    ho, wo = O.conv_out_hw(h, w, k, k, 1, p)
+    dy = rng.normal(0, 1, (n, co, ho, wo)).astype(np.float32)
+    y = rng.normal(0, 1, dy.shape).astype(np.float32) if relu else None
+    dy_eff = dy * (y > 0) if relu else dy
+    dx_ref, dw_ref, db_ref = O.conv2d_backward(dy_eff, x, wt, k, k, 1, p)
+    dx0 = rng.normal(0, 1, x.shape).astype(np.float32)
+    dw0 = rng.normal(0, 1, wt.shape).astype(np.float32)
+    db0 = rng.normal(0, 1, (1, 1, ho * wo, co)).astype(np.float32)
+    dx, dw, db = dev(dx0), dev(dw0), dev(db0)
+    nz.conv2d_backward(dev(x), dev(wt), dev(dy), k, k, 1, p, dx=dx, dw=dw, dbias=db, y=dev(y) if relu else None)
+    torch.cuda.synchronize()
+    assert nz.device_status() == 0
+    assert emax(dx.cpu().numpy() - dx0, dx_ref) <= 5e-5
+    assert emax(dw.cpu().numpy() - dw0, dw_ref) <= 5e-5
+    assert emax(db.cpu().numpy() - db0, db_ref) <= 5e-6
+    # any subset of the outputs
+    dw2 = dev(dw0)
+    nz.conv2d_backward(dev(x), dev(wt), dev(dy), k, k, 1, p, dw=dw2, y=dev(y) if relu else None)
+    assert emax(dw2.cpu().numpy() - dw0, dw_ref) <= 5e-5
+
+
 def test_conv_chunked_staging_subprocess():
     """With a tiny staging budget the three directions process the batch in chunks of one or two images
     (the path large batches take); results must not change. Runs in a child process because the budget
@@ -151,6 +183,13 @@ for (n, c, h, w, co, k, p, per_sample) in [(5, 16, 9, 40, 16, 3, 1, False), (5, 
     assert emax(dx.cpu().numpy() - dx0, rdx) <= 5e-5
     dw = dev(dw0); nz.conv2d_backward_weight(dev(x), dev(dy), wt.shape, k, k, 1, p, dw)
     assert emax(dw.cpu().numpy() - dw0, rdw) <= 5e-5
+    db0 = rng.normal(0, 1, bias.shape).astype(np.float32)
+    _, _, rdb = O.conv2d_backward(dy, x, wt, k, k, 1, p)
+    dx, dw, db = dev(dx0), dev(dw0), dev(db0)
+    nz.conv2d_backward(dev(x), dev(wt), dev(dy), k, k, 1, p, dx=dx, dw=dw, dbias=db)
+    assert emax(dx.cpu().numpy() - dx0, rdx) <= 5e-5
+    assert emax(dw.cpu().numpy() - dw0, rdw) <= 5e-5
+    assert emax(db.cpu().numpy() - db0, rdb) <= 5e-6
     torch.cuda.synchronize(); assert nz.device_status() == 0
 print("chunked ok")
 """ % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
