@@ -262,6 +262,63 @@ __global__ void __launch_bounds__(256) avgpool_fixed_kernel(float* __restrict__ 
     }
 }
 
+// Stride 2, no padding, W % 4 == 0: a thread owns two input rows x four columns. The windows that
+// cover that tile form a small rectangle of the output gradient (3 x 4 values for pool 5), loaded
+// once; each of the eight input pixels sums its own sub-rectangle, chosen by compile-time-sized
+// loops with per-pixel bounds. One division per pixel (the reference adds gout / pool^2 term by term
+// with atomics in no fixed order; both are within an ulp or two of the exact sum).
+template <int POOL>
+__global__ void __launch_bounds__(256) avgpool_backward_s2_kernel(float* __restrict__ gin,
+                                                                  const float* __restrict__ gout, int H, int W, int Ho,
+                                                                  int Wo, int planes) {
+    constexpr int NH = (POOL - 1) / 2 + 1;      // windows covering rows 2a, 2a+1
+    constexpr int NW = (POOL - 1 + 3) / 2 + 1;  // windows covering columns 4b .. 4b+3
+    const int W4 = W >> 2, H2 = (H + 1) >> 1, per = H2 * W4;
+    constexpr float full = (float)(POOL * POOL);
+    for (int bc = blockIdx.y; bc < planes; bc += gridDim.y) {
+        const float* g = gout + (int64_t)bc * Ho * Wo;
+        float* dst = gin + (int64_t)bc * H * W;
+        for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < per; idx += gridDim.x * blockDim.x) {
+            const int a = idx / W4, wi0 = (idx - a * W4) * 4, hi0 = 2 * a;
+            // candidate windows: rows hb .. hb+NH-1, columns wb .. wb+NW-1 (may reach outside: masked)
+            const int hb = (hi0 - POOL + 2) >> 1;  // ceil((hi0 - POOL + 1) / 2), also right when negative
+            const int wb = (wi0 - POOL + 2) >> 1;
+            float v[NH][NW];
+#pragma unroll
+            for (int dh = 0; dh < NH; dh++)
+#pragma unroll
+                for (int dw = 0; dw < NW; dw++) {
+                    const int h = hb + dh, w = wb + dw;
+                    v[dh][dw] = ((unsigned)h < (unsigned)Ho && (unsigned)w < (unsigned)Wo) ? __ldg(g + (int64_t)h * Wo + w) : 0.f;
+                }
+#pragma unroll
+            for (int r = 0; r < 2; r++) {
+                const int hi = hi0 + r;
+                if (hi >= H) break;
+                // Windows of row hi0 + r and of column wi0 + j, as offsets from hb / wb: with hi0 even and
+                // wi0 a multiple of 4 they depend on r and j only, so after unrolling they are constants
+                // (windows outside the gradient were loaded as zeros above).
+                constexpr int base = (2 - POOL) >> 1;  // floor((2 - POOL) / 2)
+                const int h_lo = ((r - POOL + 2) >> 1) - base, h_hi = (r >> 1) - base;
+                float s[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int w_lo = ((j - POOL + 2) >> 1) - base, w_hi = (j >> 1) - base;
+#pragma unroll
+                    for (int dh = 0; dh < NH; dh++)
+#pragma unroll
+                        for (int dw = 0; dw < NW; dw++)
+                            if (dh >= h_lo && dh <= h_hi && dw >= w_lo && dw <= w_hi) s[j] += v[dh][dw];
+                }
+                float4* d4 = reinterpret_cast<float4*>(dst + (int64_t)hi * W + wi0);
+                float4 o = *d4;
+                o.x += s[0] / full; o.y += s[1] / full; o.z += s[2] / full; o.w += s[3] / full;
+                *d4 = o;
+            }
+        }
+    }
+}
+
 // Four consecutive input columns per thread (W % 4 == 0): the windows that cover them overlap, so
 // each gradient value is loaded once for the four, and the update of the input gradient is one
 // 16-byte read-modify-write. The terms are summed before the single division by pool^2 (the
@@ -680,12 +737,15 @@ int nzb_avgpool_backward(float* gin, const float* gout, int64_t pool, int64_t st
             if (gq > capx) gq = capx;
             const dim3 gridq((unsigned)gq, (unsigned)gy);
             if (stride == 2 && (pool == 5 || pool == 3 || pool == 2)) {
+                int64_t g2 = (((H_in + 1) / 2) * (W_in / 4) + 255) / 256;
+                if (g2 > capx) g2 = capx;
+                const dim3 grid2((unsigned)g2, (unsigned)gy);
                 if (pool == 5)
-                    avgpool_backward_fixed_kernel<5, 2><<<gridq, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+                    avgpool_backward_s2_kernel<5><<<grid2, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
                 else if (pool == 3)
-                    avgpool_backward_fixed_kernel<3, 2><<<gridq, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+                    avgpool_backward_s2_kernel<3><<<grid2, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
                 else
-                    avgpool_backward_fixed_kernel<2, 2><<<gridq, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+                    avgpool_backward_s2_kernel<2><<<grid2, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
                 NZB_OPS_EPILOGUE();
             }
             if (stride == 1)
