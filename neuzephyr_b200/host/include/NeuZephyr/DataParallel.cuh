@@ -21,6 +21,8 @@ public:
     int world() const { return world_; }
     // in-place average over all ranks of n floats at `grad` (device memory)
     void allReduceAverage(float* grad, size_t n);
+    // the same collective on a stream the caller orders itself (no StreamManager bookkeeping)
+    void allReduceAverageOn(float* grad, size_t n, void* cuda_stream);
     // in-place sum of a small host-visible value (used for reporting the loss)
     float allReduceSumHost(float v);
     void barrier();

@@ -83,6 +83,12 @@ void Communicator::allReduceAverage(float* grad, size_t n) {
     SM::Instance().recordData(grad, s);
 }
 
+void Communicator::allReduceAverageOn(float* grad, size_t n, void* cuda_stream) {
+    if (world_ <= 1 || n == 0) return;
+    NCCL_TRY(ncclAllReduce(grad, grad, n, ncclFloat32, ncclAvg, static_cast<ncclComm_t>(comm_),
+                           static_cast<cudaStream_t>(cuda_stream)));
+}
+
 float Communicator::allReduceSumHost(float v) {
     if (world_ <= 1) return v;
     cudaStream_t s = static_cast<cudaStream_t>(stream_);
@@ -97,3 +103,55 @@ float Communicator::allReduceSumHost(float v) {
 void Communicator::barrier() { (void)allReduceSumHost(0.f); }
 
 }  // namespace nz::dist
+
+// ---- C ABI over the communicator (include/nzb_dp.h) ----------------------------------------------
+#include <nzb_dp.h>
+
+namespace {
+thread_local std::string g_dp_error;
+int dp_fail(int code, const std::string& what) {
+    g_dp_error = what;
+    return code;
+}
+}  // namespace
+
+extern "C" {
+
+const char* nzb_dp_last_error_string(void) { return g_dp_error.c_str(); }
+
+int nzb_dp_init(int rank, int world, const char* id_file, int device, double timeout_s, void** comm_out) {
+    if (!comm_out || !id_file) return dp_fail(NZB_ERR_BAD_ARG, "comm_out and id_file must be non-null");
+    if (world < 1 || rank < 0 || rank >= world) return dp_fail(NZB_ERR_BAD_ARG, "rank outside [0, world)");
+    try {
+        *comm_out = new nz::dist::Communicator(rank, world, id_file, device, timeout_s > 0 ? timeout_s : 60.0);
+    } catch (const std::exception& e) {
+        *comm_out = nullptr;
+        return dp_fail(NZB_ERR_CUDA, e.what());
+    }
+    return NZB_OK;
+}
+
+int nzb_dp_allreduce_avg(void* comm, float* grad, size_t n, void* stream) {
+    if (!comm || (!grad && n)) return dp_fail(NZB_ERR_BAD_ARG, "null communicator or buffer");
+    try {
+        static_cast<nz::dist::Communicator*>(comm)->allReduceAverageOn(grad, n, stream);
+    } catch (const std::exception& e) {
+        return dp_fail(NZB_ERR_CUDA, e.what());
+    }
+    return NZB_OK;
+}
+
+int nzb_dp_world(void* comm, int* rank_out, int* world_out) {
+    if (!comm) return dp_fail(NZB_ERR_BAD_ARG, "null communicator");
+    auto* c = static_cast<nz::dist::Communicator*>(comm);
+    if (rank_out) *rank_out = c->rank();
+    if (world_out) *world_out = c->world();
+    return NZB_OK;
+}
+
+int nzb_dp_finalize(void* comm) {
+    delete static_cast<nz::dist::Communicator*>(comm);
+    return NZB_OK;
+}
+
+}  // extern "C"

@@ -74,3 +74,28 @@ def test_shape_entry_points_validate_without_a_device():
 
 def test_version():
     assert C.lib().nzb_version() >= 100
+
+
+def test_dp_library_exports_and_validates():
+    """include/nzb_dp.h: every declared symbol is exported by libneuzephyr_host.so, and argument
+    errors are reported before any device or NCCL call."""
+    import re
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    hdr = open(os.path.join(root, "include", "nzb_dp.h")).read()
+    names = re.findall(r"NZB_API\s+[\w\s\*]+?\b(nzb_dp_\w+)\s*\(", hdr)
+    assert sorted(names) == sorted(["nzb_dp_init", "nzb_dp_allreduce_avg", "nzb_dp_world", "nzb_dp_finalize",
+                                    "nzb_dp_last_error_string"])
+    lib_path = os.path.join(root, "neuzephyr_b200", "libneuzephyr_host.so")
+    assert os.path.exists(lib_path), "build the host layer first (python -c 'import __graft_entry__ as g; g.build()')"
+    H = ctypes.CDLL(lib_path)
+    for n in names:
+        assert hasattr(H, n), n
+    H.nzb_dp_init.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.c_double,
+                              ctypes.POINTER(ctypes.c_void_p)]
+    H.nzb_dp_last_error_string.restype = ctypes.c_char_p
+    out = ctypes.c_void_p()
+    assert H.nzb_dp_init(2, 2, b"/tmp/unused.id", 0, 1.0, ctypes.byref(out)) == C.ERR_BAD_ARG
+    assert b"rank" in H.nzb_dp_last_error_string()
+    assert H.nzb_dp_init(0, 2, None, 0, 1.0, ctypes.byref(out)) == C.ERR_BAD_ARG
+    H.nzb_dp_allreduce_avg.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+    assert H.nzb_dp_allreduce_avg(None, None, 4, None) == C.ERR_BAD_ARG

@@ -47,3 +47,44 @@ def test_two_rank_data_parallel_step_matches_full_batch():
     out = _last_json(r.stdout)
     assert r.returncode == 0 and out["ok"] and out["world"] == 2, r.stdout[-2000:] + r.stderr[-2000:]
     assert abs(out["loss_sharded"] - out["loss_full"]) < 1e-5
+
+
+_DP_CHILD = r"""
+import ctypes, os, sys, torch
+rank, world, idf, root = int(sys.argv[1]), int(sys.argv[2]), sys.argv[3], sys.argv[4]
+torch.cuda.set_device(rank)
+H = ctypes.CDLL(os.path.join(root, "neuzephyr_b200", "libneuzephyr_host.so"))
+H.nzb_dp_init.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.c_double,
+                          ctypes.POINTER(ctypes.c_void_p)]
+H.nzb_dp_allreduce_avg.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+H.nzb_dp_finalize.argtypes = [ctypes.c_void_p]
+H.nzb_dp_last_error_string.restype = ctypes.c_char_p
+comm = ctypes.c_void_p()
+rc = H.nzb_dp_init(rank, world, idf.encode(), rank, 60.0, ctypes.byref(comm))
+assert rc == 0, H.nzb_dp_last_error_string()
+g = torch.full((1000003,), float(rank + 1), device="cuda")
+s = torch.cuda.current_stream()
+for _ in range(2):  # the second call averages values that are already equal
+    assert H.nzb_dp_allreduce_avg(comm, ctypes.c_void_p(g.data_ptr()), g.numel(), ctypes.c_void_p(s.cuda_stream)) == 0
+torch.cuda.synchronize()
+want = sum(range(1, world + 1)) / world
+assert torch.all(g == want).item(), (g[:4], want)
+H.nzb_dp_finalize(comm)
+print("dp ok", rank)
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_dp_c_abi_two_ranks():
+    """include/nzb_dp.h through ctypes: two processes, one GPU each, average a gradient buffer in place."""
+    idf = "/tmp/nz_dp_abi_%d.id" % os.getpid()
+    if os.path.exists(idf):
+        os.remove(idf)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, "-c", _DP_CHILD, str(r), "2", idf, ROOT], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True, env=env) for r in range(2)]
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    if os.path.exists(idf):
+        os.remove(idf)
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and ("dp ok %d" % r) in o, o[-2000:]
