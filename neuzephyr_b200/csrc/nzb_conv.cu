@@ -1831,7 +1831,7 @@ static int run_conv_tma(const ConvTmaRun& r, const TmaPlan& pl, void* ws, cudaSt
     if (r.R > 64) return run_conv_tma_cfg<ConvTmaCfg<128, 7, 1>>(r, pl, ws, *ds, stream);
     if (r.R > 32) return run_conv_tma_cfg<ConvTmaCfg<64, 4, 2>>(r, pl, ws, *ds, stream);
     if (r.R > 16) return run_conv_tma_cfg<ConvTmaCfg<32, 5, 2>>(r, pl, ws, *ds, stream);
-    return run_conv_tma_cfg<ConvTmaCfg<16, 6, 2>>(r, pl, ws, *ds, stream);
+    return run_conv_tma_cfg<ConvTmaCfg<16, 4, 3>>(r, pl, ws, *ds, stream);
 }
 
 // ---- weight gradient in the TMA im2col mode: planning and launch --------------------------------
