@@ -1154,9 +1154,9 @@ struct WgradParams {
     int* status;
 };
 
-template <int BN_, int STAGES_>
+template <int BN_, int STAGES_, int MINB_ = 1>
 struct WgradCfg {
-    static constexpr int BN = BN_, STAGES = STAGES_;
+    static constexpr int BN = BN_, STAGES = STAGES_, MIN_BLOCKS = MINB_;
     static constexpr int A_BYTES = 2 * 16384;       // two 64-pixel halves of 128 k rows
     static constexpr int B_BYTES = 2 * BN * 128;    // two 64-pixel halves of BN channels
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -1165,11 +1165,11 @@ struct WgradCfg {
     static constexpr int TMEM_COLS = (BN < 32) ? 32 : BN;
     static constexpr int THREADS = 6 * 32;
     static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
-    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
+    static_assert((SMEM_BYTES + 1024) * MINB_ <= 233472, "exceeds the 228 KB shared memory of an sm_100 SM");
 };
 
 template <class Cfg>
-__global__ void __launch_bounds__(Cfg::THREADS, 1)
+__global__ void __launch_bounds__(Cfg::THREADS, Cfg::MIN_BLOCKS)
 conv2d_wgrad_tma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
                         const WgradParams p) {
     using namespace ptx;
@@ -1941,13 +1941,14 @@ static int run_wgrad_tma_cfg(const nzb_conv_desc* d, const WgradPlan& pl, const 
         p.imgs_per_group = p.w_per_sample ? 1 : (int32_t)n;
         p.kb_per_group = (int64_t)p.imgs_per_group * Ho * p.segs;
         if (p.kb_per_group > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "contraction length exceeds 2^31 blocks");
-        int64_t splits = ds.sm_count / ((int64_t)p.tiles * p.groups);
+        int64_t splits = (int64_t)ds.sm_count * Cfg::MIN_BLOCKS / ((int64_t)p.tiles * p.groups);
         if (splits < 1) splits = 1;
         if (splits > p.kb_per_group) splits = p.kb_per_group;
         p.splits = (int32_t)splits;
         p.total_items = (int64_t)p.tiles * p.groups * p.splits;
         if (p.total_items > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "more than 2^31 work items");
-        const int64_t grid = p.total_items < ds.sm_count ? p.total_items : ds.sm_count;
+        const int64_t cap = (int64_t)ds.sm_count * Cfg::MIN_BLOCKS;
+        const int64_t grid = p.total_items < cap ? p.total_items : cap;
         conv2d_wgrad_tma_kernel<Cfg><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmX, tmDY, p);
         NZB_CUDA_TRY(cudaGetLastError());
     }
@@ -1962,7 +1963,7 @@ static int run_wgrad_tma(const nzb_conv_desc* d, const WgradPlan& pl, const floa
     if (d->Cout > 64) return run_wgrad_tma_cfg<WgradCfg<128, 3>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream, st);
     if (d->Cout > 32) return run_wgrad_tma_cfg<WgradCfg<64, 4>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream, st);
     if (d->Cout > 16) return run_wgrad_tma_cfg<WgradCfg<32, 5>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream, st);
-    return run_wgrad_tma_cfg<WgradCfg<16, 6>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream, st);
+    return run_wgrad_tma_cfg<WgradCfg<16, 3, 2>>(d, pl, x, dy, dw, ws, Ho, Wo, *ds, stream, st);
 }
 
 // ---- whole backward of one layer on shared staging ------------------------------------------------
