@@ -45,9 +45,11 @@ struct GemmParams {
     int* status;
 };
 
-template <int BN_, int STAGES_>
+template <int BN_, int STAGES_, int MINB_ = 1>
 struct GemmCfg {
     static constexpr int BM = 128, BN = BN_, BK = 64, STAGES = STAGES_;
+    static constexpr int MIN_BLOCKS = MINB_;  // CTAs per SM: narrow tiles are bound by per-k-block and per-tile
+                                              // latencies, which a second resident CTA overlaps
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -58,7 +60,8 @@ struct GemmCfg {
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;
     static constexpr int CHUNK = (BN < 32) ? BN : 32;  // accumulator columns per tcgen05.ld
     static_assert(STAGE_BYTES % 1024 == 0, "operand tiles must stay 1024-byte aligned");
-    static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
+    static_assert((SMEM_BYTES + 1024) * MINB_ <= 233472, "exceeds the 228 KB shared memory of an sm_100 SM");
+    static_assert(TMEM_COLS * MINB_ <= 512, "exceeds the tensor memory of an SM");
 };
 
 
@@ -287,7 +290,7 @@ __device__ __forceinline__ void drain_accumulator_transposed(const GemmParams& p
 }
 
 template <class Cfg>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, Cfg::MIN_BLOCKS)
 gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                         const GemmParams p) {
     using namespace ptx;
@@ -702,8 +705,9 @@ static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds,
     // the full sum).
     p.splits = 1;
     const int64_t k_iters = (int64_t)p.red_e0 * p.red_e1 * p.k_blocks;
-    if (p.total_tiles * 2 <= ds.sm_count && k_iters >= 16 && !p.relu) {
-        int64_t sp = ds.sm_count / p.total_tiles;
+    const int64_t slots = (int64_t)ds.sm_count * Cfg::MIN_BLOCKS;
+    if (p.total_tiles * 2 <= slots && k_iters >= 16 && !p.relu) {
+        int64_t sp = slots / p.total_tiles;
         if (sp > k_iters / 8) sp = k_iters / 8;
         if (sp > 1) {
             p.splits = (int32_t)sp;
@@ -719,7 +723,7 @@ static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds,
         }
     }
     const int64_t items = p.total_tiles * p.splits;
-    const int64_t grid = items < ds.sm_count ? items : ds.sm_count;
+    const int64_t grid = items < slots ? items : slots;
     gemm_f16_tcgen05_kernel<Cfg><<<(unsigned)grid, 192, Cfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
     NZB_CUDA_TRY(cudaGetLastError());
     return NZB_OK;
@@ -825,8 +829,8 @@ int launch_gemm_on(const GemmLaunch& g_in, const DeviceState& dstate, cudaStream
     if (g.N > 64) return launch_cfg<GemmCfg<128, 6>>(g, p, *ds, stream);
     // an MN-major B tile is loaded in boxes of 64 columns: narrower outputs use the 64-wide tile
     if (g.N > 32 || g.b_mn) return launch_cfg<GemmCfg<64, 8>>(g, p, *ds, stream);
-    if (g.N > 16) return launch_cfg<GemmCfg<32, 8>>(g, p, *ds, stream);
-    return launch_cfg<GemmCfg<16, 8>>(g, p, *ds, stream);
+    if (g.N > 16) return launch_cfg<GemmCfg<32, 4, 2>>(g, p, *ds, stream);
+    return launch_cfg<GemmCfg<16, 5, 2>>(g, p, *ds, stream);
 }
 
 }  // namespace nzb
