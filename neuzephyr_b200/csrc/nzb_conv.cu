@@ -1828,7 +1828,7 @@ static int run_conv_tma(const ConvTmaRun& r, const TmaPlan& pl, void* ws, cudaSt
     if (rc != NZB_OK) return rc;
     if (r.Ho * r.Wo > INT32_MAX - 256 || r.N * r.Ho > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "per-image extent exceeds 2^31");
     if (r.R > 128) return run_conv_tma_cfg<ConvTmaCfg<256, 4, 1>>(r, pl, ws, *ds, stream);
-    if (r.R > 64) return run_conv_tma_cfg<ConvTmaCfg<128, 7, 1>>(r, pl, ws, *ds, stream);
+    if (r.R > 64) return run_conv_tma_cfg<ConvTmaCfg<128, 3, 2>>(r, pl, ws, *ds, stream);
     if (r.R > 32) return run_conv_tma_cfg<ConvTmaCfg<64, 4, 2>>(r, pl, ws, *ds, stream);
     if (r.R > 16) return run_conv_tma_cfg<ConvTmaCfg<32, 5, 2>>(r, pl, ws, *ds, stream);
     return run_conv_tma_cfg<ConvTmaCfg<16, 4, 3>>(r, pl, ws, *ds, stream);
