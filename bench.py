@@ -331,12 +331,16 @@ def other_workloads(dev, rank=0, world=1, local=0):
         f = _time_ms(lambda: nz.conv2d_forward(x, w, bias, k, k, 1, 1, out=y), 5)
         bd = _time_ms(lambda: nz.conv2d_backward_data(dy, w, x.shape, k, k, 1, 1, dx), 5)
         bwt = _time_ms(lambda: nz.conv2d_backward_weight(x, dy, w.shape, k, k, 1, 1, dw), 5)
-        f, bd, bwt = max_over_ranks([f, bd, bwt], device=dev)
+        db = torch.zeros_like(bias)
+        one = _time_ms(lambda: nz.conv2d_backward(x, w, dy, k, k, 1, 1, dx=dx, dw=dw, dbias=db, y=y), 5)
+        f, bd, bwt, one = max_over_ranks([f, bd, bwt, one], device=dev)
         flop = 2.0 * N_ * H_ * H_ * Co * C_ * k * k
         out["conv2d_n32_c64_224_co128"] = {"images_per_rank": N_, "n_gpus": world, "scaling": "weak",
                                            "forward_ms": f, "backward_data_ms": bd, "backward_weight_ms": bwt,
+                                           "backward_one_call_ms": one,  # dX, dW, bias gradient and the ReLU mask
                                            "forward_img_per_s": world * N_ / f * 1e3,
                                            "fwd_bwd_img_per_s": world * N_ / (f + bd + bwt) * 1e3,
+                                           "fwd_full_bwd_img_per_s": world * N_ / (f + one) * 1e3,
                                            "forward_tflops_per_gpu": flop / f / 1e9,
                                            "forward_hbm_gbs_algorithmic_per_gpu":
                                                4.0 * (x.numel() + y.numel() + bias.numel()) / f / 1e6,
