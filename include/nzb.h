@@ -145,6 +145,16 @@ NZB_API int nzb_gemm_backward(const float* A, const float* B, float* C, const in
 #define NZB_STATIC_SCRATCH_BYTES ((size_t)32 << 20)
 NZB_API int nzb_gemm_static(const nzb_gemm_desc* desc, const float* A, const float* B, float* C, const float* bias,
                             void* stream);
+/*
+ * The status word of the nzb_gemm_static path (no counterpart in NeuZephyr either). That path cannot
+ * use the mapped host word nzb_device_status reads, because creating it allocates; a bounded
+ * device-side wait that gives up during nzb_gemm_static writes NZB_ERR_DEVICE_TIMEOUT into a word
+ * inside the library image instead. nzb_gemm_static_status copies that word to *status_out after
+ * the work already queued on `stream` (it waits for that stream, and allocates nothing);
+ * nzb_gemm_static_status_reset queues its clearing on `stream`.
+ */
+NZB_API int nzb_gemm_static_status(int* status_out, void* stream);
+NZB_API int nzb_gemm_static_status_reset(void* stream);
 
 /*
  * nzb_gemm for operands and result in HOST memory, as one pipelined call. Replaces the sequence a

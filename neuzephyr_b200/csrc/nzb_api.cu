@@ -50,6 +50,17 @@ int get_device_state(DeviceState** out) {
     return NZB_OK;
 }
 
+int ensure_dynamic_smem(std::atomic<uint64_t>& done, const void* kernel, int bytes) {
+    int dev = -1;
+    NZB_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(NZB_ERR_NO_DEVICE, "device ordinal %d is outside 0..63", dev);
+    const uint64_t bit = 1ull << dev;
+    if (done.load(std::memory_order_acquire) & bit) return NZB_OK;
+    NZB_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+    done.fetch_or(bit, std::memory_order_release);
+    return NZB_OK;
+}
+
 int get_encode_tiled(EncodeTiledFn* out) {
     static EncodeTiledFn fn = nullptr;
     if (!fn) {

@@ -1570,13 +1570,12 @@ static int run_conv_cfg(const ConvRun& r, const __half* W16, int64_t Kp, int64_t
     CUtensorMap tmW;
     int rc = make_weight_map(&tmW, W16, p.K, Kp, p.Cout, wN, Cfg::BN);
     if (rc != NZB_OK) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_igemm_tcgen05_kernel<Cfg, false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_igemm_tcgen05_kernel<Cfg, true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set = true;
+    static std::atomic<uint64_t> smem_set[2];  // per kernel instantiation, one bit per device
+    {
+        int rc_attr = ensure_dynamic_smem(smem_set[0], reinterpret_cast<const void*>(conv2d_igemm_tcgen05_kernel<Cfg, false>), Cfg::SMEM_BYTES);
+        if (rc_attr == NZB_OK)
+            rc_attr = ensure_dynamic_smem(smem_set[1], reinterpret_cast<const void*>(conv2d_igemm_tcgen05_kernel<Cfg, true>), Cfg::SMEM_BYTES);
+        if (rc_attr != NZB_OK) return rc_attr;
     }
     p.total_tiles = (int64_t)r.N * p.tiles_per_image * p.tiles_n;
     const int64_t grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
@@ -1622,13 +1621,12 @@ static int run_conv_rows_cfg(const ConvRun& r, const __half* W16, int64_t Kp, in
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (image window) failed with CUresult %d", (int)cr);
     }
-    static bool attr_set = false;
-    if (!attr_set) {
-        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_rows_tcgen05_kernel<Cfg, false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_rows_tcgen05_kernel<Cfg, true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set = true;
+    static std::atomic<uint64_t> smem_set[2];  // per kernel instantiation, one bit per device
+    {
+        int rc_attr = ensure_dynamic_smem(smem_set[0], reinterpret_cast<const void*>(conv2d_rows_tcgen05_kernel<Cfg, false>), Cfg::SMEM_BYTES);
+        if (rc_attr == NZB_OK)
+            rc_attr = ensure_dynamic_smem(smem_set[1], reinterpret_cast<const void*>(conv2d_rows_tcgen05_kernel<Cfg, true>), Cfg::SMEM_BYTES);
+        if (rc_attr != NZB_OK) return rc_attr;
     }
     p.total_tiles = (int64_t)r.N * r.Ho * tiles_per_row * p.tiles_n;
     const int64_t grid = p.total_tiles < ds.sm_count ? p.total_tiles : ds.sm_count;
@@ -1757,13 +1755,12 @@ static int run_conv_tma_cfg(const ConvTmaRun& r, const TmaPlan& pl, void* ws, co
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (weights) failed with CUresult %d", (int)cr);
     }
-    static bool attr_set = false;
-    if (!attr_set) {
-        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_tma_tcgen05_kernel<Cfg, false>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_tma_tcgen05_kernel<Cfg, true>,
-                                          cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES));
-        attr_set = true;
+    static std::atomic<uint64_t> smem_set[2];  // per kernel instantiation, one bit per device
+    {
+        int rc_attr = ensure_dynamic_smem(smem_set[0], reinterpret_cast<const void*>(conv2d_tma_tcgen05_kernel<Cfg, false>), Cfg::SMEM_BYTES);
+        if (rc_attr == NZB_OK)
+            rc_attr = ensure_dynamic_smem(smem_set[1], reinterpret_cast<const void*>(conv2d_tma_tcgen05_kernel<Cfg, true>), Cfg::SMEM_BYTES);
+        if (rc_attr != NZB_OK) return rc_attr;
     }
     ConvTmaParams p{};
     p.Y = r.Y; p.bias = r.bias;
@@ -1871,11 +1868,10 @@ static int run_wgrad_tma_cfg(const nzb_conv_desc* d, const WgradPlan& pl, const 
     EncodeTiledFn enc;
     int rc = get_encode_tiled(&enc);
     if (rc != NZB_OK) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        NZB_CUDA_TRY(cudaFuncSetAttribute(conv2d_wgrad_tma_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          Cfg::SMEM_BYTES));
-        attr_set = true;
+    static std::atomic<uint64_t> smem_set{0};  // per kernel instantiation, one bit per device
+    {
+        const int rc_attr = ensure_dynamic_smem(smem_set, reinterpret_cast<const void*>(conv2d_wgrad_tma_kernel<Cfg>), Cfg::SMEM_BYTES);
+        if (rc_attr != NZB_OK) return rc_attr;
     }
     WgradParams p{};
     p.dW = dw;

@@ -694,11 +694,10 @@ static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds,
     if (rc != NZB_OK) return rc;
     p.tiles_n = (int32_t)((g.N + Cfg::BN - 1) / Cfg::BN);
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * p.out_e0 * p.out_e1;
-    static bool attr_set = false;  // per instantiation
-    if (!attr_set) {
-        NZB_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_kernel<Cfg>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          Cfg::SMEM_BYTES));
-        attr_set = true;
+    static std::atomic<uint64_t> smem_set{0};  // per kernel instantiation, one bit per device
+    {
+        const int rc_attr = ensure_dynamic_smem(smem_set, reinterpret_cast<const void*>(gemm_f16_tcgen05_kernel<Cfg>), Cfg::SMEM_BYTES);
+        if (rc_attr != NZB_OK) return rc_attr;
     }
     // Few output tiles but a long contraction: share each tile among several CTAs along k and
     // add the partial sums atomically (the first slice adds the bias; not with ReLU, which needs
@@ -739,11 +738,10 @@ static int launch_pair(const GemmLaunch& g, GemmParams& p, const DeviceState& ds
     p.group_m = 8;
     p.splits = 1;
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * p.out_e0 * p.out_e1;
-    static bool attr_set = false;
-    if (!attr_set) {
-        NZB_CUDA_TRY(cudaFuncSetAttribute(gemm_f16_tcgen05_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          PairCfg::SMEM_BYTES));
-        attr_set = true;
+    static std::atomic<uint64_t> smem_set{0};  // per kernel instantiation, one bit per device
+    {
+        const int rc_attr = ensure_dynamic_smem(smem_set, reinterpret_cast<const void*>(gemm_f16_tcgen05_pair_kernel), PairCfg::SMEM_BYTES);
+        if (rc_attr != NZB_OK) return rc_attr;
     }
     int64_t pairs = ds.sm_count / 2;
     if (p.total_tiles < pairs) pairs = p.total_tiles;

@@ -6,6 +6,8 @@
 #include <stddef.h>
 #include <cuda_fp16.h>
 
+#include <atomic>
+
 #include "../../include/nzb.h"
 
 namespace nzb {
@@ -38,6 +40,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 int get_encode_tiled(EncodeTiledFn* out);
 
 inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device property of a kernel: `done` holds one
+// bit per device ordinal (< 64) on which this kernel has been given `bytes` already. Callers racing on
+// the first use both set the attribute, which is harmless.
+int ensure_dynamic_smem(std::atomic<uint64_t>& done, const void* kernel, int bytes);
 
 // fp16 operand copy layout: rows x Kp halves, Kp = K rounded up to one 128-byte line.
 constexpr int64_t kOperandKAlign = 64;

@@ -16,7 +16,9 @@
 // (including the zero fill of the K padding), so nothing has to be cleared, but two calls
 // that overlap on the GPU (different streams, no ordering between them) race on it.
 // A bounded device-side wait that expires on this path is recorded in a device-resident
-// word of the library image (not in the mapped word nzb_device_status reads).
+// word of the library image (not in the mapped word nzb_device_status reads);
+// nzb_gemm_static_status / nzb_gemm_static_status_reset read and clear it with plain
+// stream-ordered copies, so the no-allocation property holds for them too.
 #include <cuda_fp16.h>
 
 #include <mutex>
@@ -103,6 +105,26 @@ int nzb_gemm_static(const nzb_gemm_desc* desc, const float* A, const float* B, f
     pl.g.C = C;
     pl.g.bias = bias;
     return launch_gemm_on(pl.g, ds, s);
+}
+
+int nzb_gemm_static_status(int* status_out, void* stream) {
+    if (!status_out) return fail(NZB_ERR_BAD_ARG, "status_out is null");
+    StaticState* st;
+    int rc = static_setup(&st);
+    if (rc != NZB_OK) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // ordered after the work already queued on `stream`; the host waits for the copy only
+    NZB_CUDA_TRY(cudaMemcpyAsync(status_out, st->status, sizeof(int), cudaMemcpyDeviceToHost, s));
+    NZB_CUDA_TRY(cudaStreamSynchronize(s));
+    return NZB_OK;
+}
+
+int nzb_gemm_static_status_reset(void* stream) {
+    StaticState* st;
+    int rc = static_setup(&st);
+    if (rc != NZB_OK) return rc;
+    NZB_CUDA_TRY(cudaMemsetAsync(st->status, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
+    return NZB_OK;
 }
 
 }  // extern "C"

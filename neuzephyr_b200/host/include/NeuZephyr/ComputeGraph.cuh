@@ -31,8 +31,16 @@ public:
     // forward() overwrites: that is several full passes over the largest tensors of the model
     // for no effect on training, so it is off by default. stepIntermediateNodes(true) restores
     // it for code that reads a hidden node's output between update() and the next forward().
+    // Either way every gradient-requiring node the reference would step advances the optimizer's
+    // per-call counter (Optimizer::skip), so Adam's bias-correction exponent t of each parameter
+    // is the reference's: nodes that are skipped here count one tick each, and a fused node
+    // declares the reference nodes it stands for with addPhantomSteps().
     void update(opt::Optimizer* optimizer, const std::function<void()>& before_step = nullptr) const;
     void stepIntermediateNodes(bool on) { step_intermediates_ = on; }
+    // `n` optimizer ticks that belong to gradient-requiring reference nodes which have no node of
+    // their own in this graph (a fused node collapses several); they are placed before the next
+    // node that is added, or at the end of the list.
+    void addPhantomSteps(int n) { pending_ticks_ += n; }
     float getLoss() const;
     const std::vector<nodes::Node*>& getNodes() const { return nodes_; }
     const std::vector<nodes::io::OutputNode*>& getOutputs() const { return outputs_; }
@@ -41,6 +49,8 @@ private:
     std::vector<nodes::Node*> nodes_, sorted_nodes_;
     std::vector<nodes::io::InputNode*> inputs_;
     std::vector<nodes::io::OutputNode*> outputs_;
+    std::vector<int> ticks_before_;  // per entry of nodes_: phantom optimizer ticks that precede it
+    int pending_ticks_ = 0;
     bool sorted_ = false;
     bool step_intermediates_ = false;
 };

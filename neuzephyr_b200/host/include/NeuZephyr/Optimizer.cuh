@@ -13,6 +13,9 @@ class Optimizer {
 public:
     virtual ~Optimizer() = default;
     virtual void step(nodes::Node* input) = 0;
+    // `n` step() calls the reference would have made on nodes this graph does not step
+    // (activations, nodes folded into a fused node): only per-call state advances.
+    virtual void skip(int n) { (void)n; }
 
 protected:
     float learning_rate = 0.f;
@@ -28,6 +31,7 @@ class Adam : public Optimizer {
 public:
     Adam(float learning_rate, float beta1, float beta2);
     void step(nodes::Node* input) override;
+    void skip(int n) override { it_ += n; }
     // false restores "one time step per optimisation step" semantics: call nextIteration() once
     // per Model::update and every parameter uses the same t
     bool perCallTimeStep = true;

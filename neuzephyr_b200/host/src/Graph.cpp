@@ -19,6 +19,8 @@ bool ComputeGraph::inGraph(Node* node) const { return std::find(nodes_.begin(), 
 void ComputeGraph::addNode(Node* node) {
     if (inGraph(node)) return;
     nodes_.push_back(node);
+    ticks_before_.push_back(pending_ticks_);
+    pending_ticks_ = 0;
     sorted_ = false;
 }
 void ComputeGraph::addInput(nodes::io::InputNode* node) {
@@ -70,8 +72,14 @@ void ComputeGraph::zeroGrad() const {
 }
 void ComputeGraph::update(opt::Optimizer* optimizer, const std::function<void()>& before_step) const {
     if (before_step) before_step();
-    for (Node* n : nodes_)
-        if (n->output->requiresGrad() && (step_intermediates_ || n->inputs.empty())) optimizer->step(n);
+    for (size_t i = 0; i < nodes_.size(); i++) {
+        Node* n = nodes_[i];
+        if (ticks_before_[i]) optimizer->skip(ticks_before_[i]);
+        if (!n->output->requiresGrad()) continue;
+        if (step_intermediates_ || n->inputs.empty()) optimizer->step(n);
+        else optimizer->skip(1);  // the reference steps this activation (src/ComputeGraph.cu:541-547)
+    }
+    if (pending_ticks_) optimizer->skip(pending_ticks_);
 }
 float ComputeGraph::getLoss() const {
     if (outputs_.empty()) throw std::runtime_error("No output node");
@@ -203,16 +211,22 @@ Model::Node* Model::Linear(Node* input, size_t outSize) {
     computeGraph.addNode(input);
     const auto s = input->output->shape();
     const size_t inSize = s[1] * s[2] * s[3];
-    auto* w = new io::InputNode(Dimension(1, 1, outSize, inSize), true);
-    w->output->randomize();
-    own(w, true);
+    // node order of the reference (src/Model.cu:87-103): [Reshape], weight, MatMul, bias, Add
     if (fused_) {
+        if (s[2] != inSize && input->output->requiresGrad()) computeGraph.addPhantomSteps(1);  // Reshape
+        auto* w = new io::InputNode(Dimension(1, 1, outSize, inSize), true);
+        w->output->randomize();
+        own(w, true);
+        computeGraph.addPhantomSteps(1);  // MatMul
         auto* b = new io::InputNode(Dimension(1, 1, outSize, 1), true);
         b->output->randomize();
         own(b, true);
-        return own(new calc::LinearNode(input, w, b, false));
+        return own(new calc::LinearNode(input, w, b, false));  // stands for Add
     }
     Node* shaped = s[2] != inSize ? Reshape(input, Dimension(s[0], 1, inSize, 1)) : input;
+    auto* w = new io::InputNode(Dimension(1, 1, outSize, inSize), true);
+    w->output->randomize();
+    own(w, true);
     return Bias(Mul(w, shaped));
 }
 Model::Node* Model::ReLU(Node* input) {
@@ -251,11 +265,20 @@ Model::Node* Model::Conv2d(Node* input, size_t outChannels, size_t kh, size_t kw
     w->output->randomize();
     own(w, true);
     if (fused_) {
+        // The fused node stands for Img2Col, MatMul, [Add], Col2Img, [ReLU] (src/Model.cu:244-263):
+        // every one of them that requires a gradient is one optimizer tick in the reference, placed
+        // where that node sits relative to the parameters. The fused node itself is the last of them.
+        int before_bias = (input->output->requiresGrad() ? 1 : 0) + 1;  // Img2Col (if x needs a gradient), MatMul
+        int after_bias = (bias ? 1 : 0) + 1 + (fuseRelu ? 1 : 0);       // Add, Col2Img, ReLU
         Node* b = nullptr;
         if (bias) {
+            computeGraph.addPhantomSteps(before_bias);
             auto* bn = new io::InputNode(Dimension(1, 1, ho * wo, outChannels), true);
             bn->output->randomize();
             b = own(bn, true);
+            computeGraph.addPhantomSteps(after_bias - 1);
+        } else {
+            computeGraph.addPhantomSteps(before_bias + after_bias - 1);
         }
         return own(new calc::Conv2dNode(input, w, b, kh, kw, stride, pad, fuseRelu));
     }

@@ -351,8 +351,9 @@ void Conv2dNode::backward() {
             // general stride: the reference's composition on library kernels
             const auto so = output->shape();
             const size_t K = x.shape().C() * kh_ * kw_, P = so.H() * so.W();
-            Tensor dmm(Dimension(so.N(), 1, P, so.W()));
-            data::iCol2imgBackward(dmm.data(), dy, so.H(), so.W(), so.W(), so.N());
+            // dY {N, Cout, Ho, Wo} -> {N, 1, Ho*Wo, Cout}: the channel extent is C(), not the row width
+            Tensor dmm(Dimension(so.N(), 1, P, so.C()));
+            data::iCol2imgBackward(dmm.data(), dy, so.H(), so.W(), so.C(), so.N());
             Tensor dcol(Dimension(so.N(), 1, P, K));
             dcol.clear();
             Tensor wT = data::transpose(w);

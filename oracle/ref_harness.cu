@@ -8,11 +8,21 @@
 //   ref_harness linear_bench B In Out steps warmup                  Model::Linear -> ReLU -> MSELoss, forward + backward
 //   ref_harness conv_bench N C H W Cout k pad steps warmup          Model::Conv2d -> ReLU -> MSELoss, forward + backward
 //   ref_harness model_bench B S steps warmup                        the README-style segmentation model, one Adam step
+//   ref_harness conv_file  dir N C H W Cout k stride pad shared relu  Img2Col -> MatMul -> Add -> Col2Img [-> ReLU] with injected
+//                                                                     weights: reads x,w,b,dy .bin from dir, writes y,dx,dw,db .bin
+//   ref_harness linear_file dir B In Out relu                       Reshape-free Model::Linear chain, same files
+//   ref_harness model_file dir B S steps shared                     the segmentation model as Model's builders compose it, built
+//                                                                   node by node so that parameters can be injected: reads x,t,p0..p5,
+//                                                                   writes loss.txt, g0..g5 (first backward), q<step>_<i> (after each update)
 #include <NeuZephyr/Model.cuh>
 #include <NeuZephyr/Optimizer.cuh>
 #include <NeuZephyr/Tensor.cuh>
 #include <NeuZephyr/TensorOperations.cuh>
 
+#include <NeuZephyr/ComputeGraph.cuh>
+#include <NeuZephyr/Nodes.cuh>
+
+#include <algorithm>
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -43,6 +53,86 @@ static void write_bin(const char* path, const std::vector<float>& v) {
 static double now_ms() {
     return std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now().time_since_epoch()).count();
 }
+
+static std::string in_dir(const std::string& dir, const std::string& name) { return dir + "/" + name; }
+
+using nz::nodes::Node;
+using nz::nodes::io::InputNode;
+namespace calc = nz::nodes::calc;
+
+// A chain of reference nodes driven by hand, the way test/Test.cpp drives single nodes: forward in
+// creation order, the upstream gradient injected into the last node, backward in reverse order.
+struct Chain {
+    std::vector<Node*> nodes;
+    template <class T>
+    T* add(T* n) {
+        nodes.push_back(n);
+        return n;
+    }
+    void forward() {
+        for (Node* n : nodes) n->forward();
+    }
+    void backward(float* dy) {
+        for (Node* n : nodes)
+            if (n->output->requiresGrad()) n->output->zeroGrad();
+        nodes.back()->output->dataInject(dy, true);
+        for (auto it = nodes.rbegin(); it != nodes.rend(); ++it) (*it)->backward();
+        cudaDeviceSynchronize();
+    }
+    ~Chain() {
+        for (Node* n : nodes) delete n;
+    }
+};
+
+// The segmentation model in the node order Model::Conv2d / ReLU / AvgPool2d / Linear / Softmax /
+// BCELoss create (src/Model.cu:87-103, 185-202, 244-263, 317-325), on a ComputeGraph of its own.
+struct SegGraph {
+    nz::graph::ComputeGraph g;
+    std::vector<Node*> owned, params;
+    InputNode *input, *target;
+    template <class T>
+    T* add(T* n, bool param = false) {
+        owned.push_back(n);
+        g.addNode(n);
+        if (param) params.push_back(n);
+        return n;
+    }
+    Node* conv(Node* in, size_t cout, size_t k, size_t pad, bool shared) {
+        const auto s = in->output->shape();
+        auto* w = add(new InputNode({shared ? 1 : s.N(), 1, s.C() * k * k, cout}, true), true);
+        auto* col = add(new calc::Img2ColNode(in, k, k, 1, pad));
+        auto* mm = add(new calc::MatMulNode(col, w));
+        auto* b = add(new InputNode({1, mm->output->shape()[1], mm->output->shape()[2], mm->output->shape()[3]}, true), true);
+        auto* sum = add(new calc::AddNode(mm, b));
+        return add(new calc::Col2ImgNode(sum, s.H() + 2 * pad - k + 1, s.W() + 2 * pad - k + 1));
+    }
+    SegGraph(size_t B, size_t S, bool shared) {
+        input = new InputNode({B, 3, S, S});
+        target = new InputNode({B, 1, 16, 1});
+        owned.push_back(input);
+        owned.push_back(target);
+        g.addNode(input);
+        Node* x = conv(input, 16, 3, 1, shared);
+        x = add(new calc::ReLUNode(x));
+        x = conv(x, 16, 3, 1, shared);
+        x = add(new calc::AveragePoolingNode(x, 5, 2, 0));
+        const auto s = x->output->shape();
+        const size_t in = s[1] * s[2] * s[3];
+        x = add(new calc::ReshapeNode(x, {s[0], 1, in, 1}));
+        auto* w = add(new InputNode({1, 1, 16, in}, true), true);
+        x = add(new calc::MatMulNode(w, x));
+        auto* b = add(new InputNode({1, 1, 16, 1}, true), true);
+        x = add(new calc::AddNode(x, b));
+        x = add(new calc::SoftmaxNode(x));
+        g.addNode(target);
+        auto* bce = new nz::nodes::loss::BinaryCrossEntropyNode(x, target);
+        owned.push_back(bce);
+        g.addOutput(bce);
+    }
+    ~SegGraph() {
+        for (Node* n : owned) delete n;
+    }
+};
 
 // Reference models built with the reference's own Model builders (src/Model.cu).
 class RefLinear : public nz::Model {
@@ -117,6 +207,102 @@ int main(int argc, char** argv) {
         time_model(m, "model_bench", atoi(argv[4]), atoi(argv[5]), true, (double)atoll(argv[2]));
         return 0;
     }
+    if (mode == "conv_file" && argc == 14) {
+        const std::string dir = argv[2];
+        const size_t N = atoll(argv[3]), C = atoll(argv[4]), H = atoll(argv[5]), W = atoll(argv[6]), Co = atoll(argv[7]);
+        const size_t k = atoll(argv[8]), stride = atoll(argv[9]), pad = atoll(argv[10]);
+        const bool shared = atoi(argv[11]) != 0, relu = atoi(argv[12]) != 0, with_bias = atoi(argv[13]) != 0;
+        const size_t Ho = (H + 2 * pad - k) / stride + 1, Wo = (W + 2 * pad - k) / stride + 1, K = C * k * k;
+        Chain c;
+        auto* x = c.add(new InputNode({N, C, H, W}, true));
+        auto* w = c.add(new InputNode({shared ? 1 : N, 1, K, Co}, true));
+        auto* col = c.add(new calc::Img2ColNode(x, k, k, stride, pad));
+        Node* y = c.add(new calc::MatMulNode(col, w));
+        InputNode* b = nullptr;
+        if (with_bias) {
+            b = c.add(new InputNode({1, 1, Ho * Wo, Co}, true));
+            y = c.add(new calc::AddNode(y, b));
+        }
+        y = c.add(new calc::Col2ImgNode(y, Ho, Wo));
+        if (relu) y = c.add(new calc::ReLUNode(y));
+        auto hx = read_bin(in_dir(dir, "x.bin").c_str(), N * C * H * W);
+        auto hw = read_bin(in_dir(dir, "w.bin").c_str(), (shared ? 1 : N) * K * Co);
+        auto hdy = read_bin(in_dir(dir, "dy.bin").c_str(), N * Co * Ho * Wo);
+        x->output->dataInject(hx.data());
+        w->output->dataInject(hw.data());
+        if (b) {
+            auto hb = read_bin(in_dir(dir, "b.bin").c_str(), Ho * Wo * Co);
+            b->output->dataInject(hb.data());
+        }
+        c.forward();
+        write_bin(in_dir(dir, "ref_y.bin").c_str(), y->output->hostData());
+        c.backward(hdy.data());
+        write_bin(in_dir(dir, "ref_dx.bin").c_str(), x->output->hostGrad());
+        write_bin(in_dir(dir, "ref_dw.bin").c_str(), w->output->hostGrad());
+        if (b) write_bin(in_dir(dir, "ref_db.bin").c_str(), b->output->hostGrad());
+        return 0;
+    }
+    if (mode == "linear_file" && argc == 7) {
+        const std::string dir = argv[2];
+        const size_t B = atoll(argv[3]), In = atoll(argv[4]), Out = atoll(argv[5]);
+        const bool relu = atoi(argv[6]) != 0;
+        Chain c;
+        auto* x = c.add(new InputNode({B, 1, In, 1}, true));
+        auto* w = c.add(new InputNode({1, 1, Out, In}, true));
+        Node* y = c.add(new calc::MatMulNode(w, x));
+        auto* b = c.add(new InputNode({1, 1, Out, 1}, true));
+        y = c.add(new calc::AddNode(y, b));
+        if (relu) y = c.add(new calc::ReLUNode(y));
+        auto hx = read_bin(in_dir(dir, "x.bin").c_str(), B * In);
+        auto hw = read_bin(in_dir(dir, "w.bin").c_str(), Out * In);
+        auto hb = read_bin(in_dir(dir, "b.bin").c_str(), Out);
+        auto hdy = read_bin(in_dir(dir, "dy.bin").c_str(), B * Out);
+        x->output->dataInject(hx.data());
+        w->output->dataInject(hw.data());
+        b->output->dataInject(hb.data());
+        c.forward();
+        write_bin(in_dir(dir, "ref_y.bin").c_str(), y->output->hostData());
+        c.backward(hdy.data());
+        write_bin(in_dir(dir, "ref_dx.bin").c_str(), x->output->hostGrad());
+        write_bin(in_dir(dir, "ref_dw.bin").c_str(), w->output->hostGrad());
+        write_bin(in_dir(dir, "ref_db.bin").c_str(), b->output->hostGrad());
+        return 0;
+    }
+    if (mode == "model_file" && argc == 7) {
+        const std::string dir = argv[2];
+        const size_t B = atoll(argv[3]), S = atoll(argv[4]);
+        const int steps = atoi(argv[5]);
+        const bool shared = atoi(argv[6]) != 0;
+        SegGraph m(B, S, shared);
+        auto hx = read_bin(in_dir(dir, "x.bin").c_str(), B * 3 * S * S);
+        auto ht = read_bin(in_dir(dir, "t.bin").c_str(), B * 16);
+        m.input->output->dataInject(hx.data());
+        m.target->output->dataInject(ht.data());
+        for (size_t i = 0; i < m.params.size(); i++) {
+            auto hp = read_bin(in_dir(dir, "p" + std::to_string(i) + ".bin").c_str(), m.params[i]->output->size());
+            m.params[i]->output->dataInject(hp.data());
+        }
+        m.g.zeroGrad();
+        nz::opt::Adam adam(0.01f, 0.9f, 0.999f);
+        FILE* lf = fopen(in_dir(dir, "ref_loss.txt").c_str(), "w");
+        for (int s = 0; s < steps; s++) {
+            m.g.forward();
+            fprintf(lf, "%.9g\n", m.g.getLoss());  // accumulates over steps, as the reference's loss node does
+            m.g.backward();
+            cudaDeviceSynchronize();
+            if (s == 0)
+                for (size_t i = 0; i < m.params.size(); i++)
+                    write_bin(in_dir(dir, "ref_g" + std::to_string(i) + ".bin").c_str(), m.params[i]->output->hostGrad());
+            m.g.update(&adam);  // Model::update (src/Model.cu:20-23)
+            m.g.zeroGrad();
+            cudaDeviceSynchronize();
+            for (size_t i = 0; i < m.params.size(); i++)
+                write_bin(in_dir(dir, "ref_q" + std::to_string(s) + "_" + std::to_string(i) + ".bin").c_str(),
+                          m.params[i]->output->hostData());
+        }
+        fclose(lf);
+        return 0;
+    }
     if (mode == "gemm_file" && argc == 12) {
         const size_t aN = atoll(argv[5]), aC = atoll(argv[6]), M = atoll(argv[7]), K = atoll(argv[8]);
         const size_t bN = atoll(argv[9]), bC = atoll(argv[10]), N = atoll(argv[11]);
@@ -170,12 +356,26 @@ int main(int argc, char** argv) {
         };
         for (int i = 0; i < warmup; i++) step();
         cudaDeviceSynchronize();
-        const double t0 = now_ms();
-        for (int i = 0; i < steps; i++) step();
-        cudaDeviceSynchronize();
-        const double ms = (now_ms() - t0) / steps;
-        printf("{\"ms_per_step\": %.6f, \"tflops\": %.6f, \"M\": %zu, \"N\": %zu, \"K\": %zu, \"e2e\": %d, \"checksum\": %.6g}\n",
-               ms, 2.0 * M * N * K / ms / 1e9, M, N, K, e2e, checksum);
+        // every step timed on its own (the library allocates and frees about 1 GB per call from the
+        // stream-ordered pool, and an occasional pool re-map costs hundreds of milliseconds): the
+        // median is the steady-state figure, the list shows the outliers
+        std::vector<double> each(steps);
+        for (int i = 0; i < steps; i++) {
+            const double t0 = now_ms();
+            step();
+            cudaDeviceSynchronize();
+            each[i] = now_ms() - t0;
+        }
+        std::vector<double> sorted = each;
+        std::sort(sorted.begin(), sorted.end());
+        const double ms = sorted[sorted.size() / 2];
+        double mean = 0;
+        for (double v : each) mean += v / steps;
+        printf("{\"ms_per_step\": %.6f, \"mean_ms_per_step\": %.6f, \"tflops\": %.6f, \"M\": %zu, \"N\": %zu, \"K\": %zu, "
+               "\"e2e\": %d, \"checksum\": %.6g, \"steps\": %d, \"warmup\": %d, \"each_ms\": [",
+               ms, mean, 2.0 * M * N * K / ms / 1e9, M, N, K, e2e, checksum, steps, warmup);
+        for (int i = 0; i < steps; i++) printf("%s%.3f", i ? ", " : "", each[i]);
+        printf("]}\n");
         return 0;
     }
     fprintf(stderr, "bad arguments\n");

@@ -76,3 +76,110 @@ def test_backward_against_reference(tmp_path):
     O.gemm_backward(A, B, truth, round_operands=False)
     e_ref, e_ours = emax(c_ref, truth), emax(out.cpu().numpy(), truth)
     assert e_ours <= 1e-2 and e_ours <= 2 * e_ref + 1e-7, (e_ours, e_ref)
+
+
+def _subset_sum_ok(ref, parts, tol):
+    """Every element of `ref` equals the sum of SOME subset of the per-sample terms `parts` [n, ...]: the
+    reference adds the per-sample bias gradients with unsynchronised `+=` launches on different streams
+    (AddNode::backward -> gradCopy, src/Nodes.cu:106-121, src/OperationKernels.cu:1230-1254), so terms
+    can be lost. Returns (all elements explained, fraction that kept every term)."""
+    n = parts.shape[0]
+    best = np.full(ref.shape, np.inf)
+    for mask in range(1, 1 << n):
+        s = sum(parts[i].astype(np.float64) for i in range(n) if mask >> i & 1)
+        best = np.minimum(best, np.abs(ref - s))
+    full = np.abs(ref - parts.astype(np.float64).sum(axis=0)) <= tol
+    return bool(np.all(best <= tol)), float(np.mean(full))
+
+
+@needs_ref
+@pytest.mark.parametrize("N,C,H,W,Co,k,stride,pad,shared,relu", [
+    (2, 3, 12, 40, 16, 3, 1, 1, True, True),     # TMA im2col kernels, shared weights, fused ReLU
+    (2, 16, 10, 48, 16, 3, 1, 1, False, False),  # one weight matrix per sample, as Model::Conv2d allocates
+    (1, 8, 11, 9, 24, 3, 1, 1, True, True),      # narrow rows: gather kernels
+    (1, 5, 13, 36, 20, 3, 2, 0, True, False),    # stride 2 (forward, dW, db)
+])
+def test_conv2d_composition_against_reference(tmp_path, N, C, H, W, Co, k, stride, pad, shared, relu):
+    """Model::Conv2d's node chain (Img2Col -> MatMul -> Add -> Col2Img [-> ReLU], src/Model.cu:244-263) run by
+    NeuZephyr with injected weights, against nzb_conv2d_forward / nzb_conv2d_backward* on the same data."""
+    import neuzephyr_b200 as nz
+    rng = np.random.default_rng(N * 1000 + C * 10 + Co + stride)
+    Ho, Wo = O.conv_out_hw(H, W, k, k, stride, pad)
+    K = C * k * k
+    x = rng.normal(0, 1, (N, C, H, W)).astype(np.float32)
+    w = (rng.normal(0, 1, (1 if shared else N, 1, K, Co)) * np.sqrt(2.0 / K)).astype(np.float32)
+    b = rng.normal(0, 0.5, (1, 1, Ho * Wo, Co)).astype(np.float32)
+    dy = rng.normal(0, 1, (N, Co, Ho, Wo)).astype(np.float32)
+    for name, a in (("x", x), ("w", w), ("b", b), ("dy", dy)):
+        a.tofile(str(tmp_path / (name + ".bin")))
+    r = subprocess.run([HARNESS, "conv_file", str(tmp_path)] + [str(v) for v in (N, C, H, W, Co, k, stride, pad,
+                       int(shared), int(relu), 1)], capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-1000:]
+    load = lambda n, s: np.fromfile(str(tmp_path / ("ref_%s.bin" % n)), dtype=np.float32).reshape(s)
+    y_ref, dx_ref, dw_ref, db_ref = load("y", dy.shape), load("dx", x.shape), load("dw", w.shape), load("db", b.shape)
+    xd, wd, bd, dyd = dev(x), dev(w), dev(b), dev(dy)
+    y = nz.conv2d_forward(xd, wd, bd, k, k, stride, pad, relu=relu)
+    dx, dw, db = torch.zeros_like(xd), torch.zeros_like(wd), torch.zeros_like(bd)
+    if stride == 1:
+        nz.conv2d_backward(xd, wd, dyd, k, k, stride, pad, dx=dx, dw=dw, dbias=db, y=y if relu else None)
+    else:
+        nz.conv2d_backward_weight(xd, dyd, w.shape, k, k, stride, pad, dw)
+        nz.conv2d_backward_bias(dyd, x.shape, w.shape, k, k, stride, pad, db)
+    torch.cuda.synchronize()
+    assert nz.device_status() == 0
+    y, dx, dw, db = y.cpu().numpy(), dx.cpu().numpy(), dw.cpu().numpy(), db.cpu().numpy()
+    # ground truth on unrounded operands (host oracle)
+    y_t = O.conv2d_forward(x, w, b, k, k, stride, pad, False, relu=relu)
+    dy_eff = dy * (y_ref > 0) if relu else dy
+    dx_t, dw_t, db_t = O.conv2d_backward(dy_eff, x, w, k, k, stride, pad, round_operands=False)
+    for name, ours, ref, truth in (("y", y, y_ref, y_t), ("dw", dw, dw_ref, dw_t)) + \
+            ((("dx", dx, dx_ref, dx_t),) if stride == 1 else ()):
+        e_o, e_r = emax(ours, truth), emax(ref, truth)
+        assert e_o <= 1e-2 and e_o <= 2 * e_r + 1e-6, (name, e_o, e_r)
+        assert emax(ours, ref) <= 1e-4, (name, emax(ours, ref))
+    assert emax(db, db_t) <= 1e-5
+    parts = dy_eff.reshape(N, Co, Ho * Wo).transpose(0, 2, 1).reshape(N, 1, Ho * Wo, Co)
+    explained, full = _subset_sum_ok(db_ref.astype(np.float64)[0], parts, 1e-5 * max(np.max(np.abs(db_t)), 1.0))
+    assert explained, "reference bias gradient holds a value that is no sum of per-sample terms"
+    print("reference db kept every sample's term in %.1f%% of its elements" % (100 * full))
+
+
+@needs_ref
+@pytest.mark.parametrize("B,In,Out,relu", [(1, 300, 40, True), (5, 130, 24, True), (3, 64, 16, False)])
+def test_linear_composition_against_reference(tmp_path, B, In, Out, relu):
+    """Model::Linear's chain (MatMul(W, x) -> Add(bias) [-> ReLU], src/Model.cu:87-103) run by NeuZephyr,
+    against nzb_linear_forward / nzb_linear_backward."""
+    import neuzephyr_b200 as nz
+    rng = np.random.default_rng(B * 100 + In + Out)
+    x = rng.normal(0, 1, (B, In)).astype(np.float32)
+    w = rng.uniform(-1, 1, (Out, In)).astype(np.float32) * np.float32((6.0 / In) ** 0.5)
+    b = rng.normal(0, 0.5, Out).astype(np.float32)
+    dy = rng.normal(0, 1, (B, Out)).astype(np.float32)
+    for name, a in (("x", x), ("w", w), ("b", b), ("dy", dy)):
+        a.tofile(str(tmp_path / (name + ".bin")))
+    r = subprocess.run([HARNESS, "linear_file", str(tmp_path), str(B), str(In), str(Out), str(int(relu))],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-1000:] + r.stderr[-1000:]
+    load = lambda n, s: np.fromfile(str(tmp_path / ("ref_%s.bin" % n)), dtype=np.float32).reshape(s)
+    y_ref, dx_ref, dw_ref, db_ref = load("y", dy.shape), load("dx", x.shape), load("dw", w.shape), load("db", b.shape)
+    xd, wd, bd, dyd = dev(x), dev(w), dev(b), dev(dy)
+    y = nz.linear_forward(xd, wd, bd, relu=relu)
+    dx, dw, db = torch.zeros_like(xd), torch.zeros_like(wd), torch.zeros_like(bd)
+    nz.linear_backward(xd, wd, y, dyd, dx, dw, db, relu=relu)
+    torch.cuda.synchronize()
+    assert nz.device_status() == 0
+    y, dx, dw, db = y.cpu().numpy(), dx.cpu().numpy(), dw.cpu().numpy(), db.cpu().numpy()
+    x64, w64 = x.astype(np.float64), w.astype(np.float64)
+    y_t = x64 @ w64.T + b
+    if relu:
+        y_t = np.maximum(y_t, 0)
+    dym = (dy * (y_ref > 0) if relu else dy).astype(np.float64)
+    truths = {"y": y_t, "dx": dym @ w64, "dw": dym.T @ x64}
+    for name, ours, ref in (("y", y, y_ref), ("dx", dx, dx_ref), ("dw", dw, dw_ref)):
+        e_o, e_r = emax(ours, truths[name]), emax(ref, truths[name])
+        assert e_o <= 1e-2 and e_o <= 2 * e_r + 1e-6, (name, e_o, e_r)
+        assert emax(ours, ref) <= 1e-4, (name, emax(ours, ref))
+    assert emax(db, dym.sum(axis=0)) <= 1e-5
+    explained, full = _subset_sum_ok(db_ref.astype(np.float64), dym.reshape(B, Out), 1e-5)
+    assert explained
+    print("reference db kept every sample's term in %.1f%% of its elements" % (100 * full))

@@ -6,8 +6,9 @@ are banned -- so they cannot provide the scratch nzb_gemm wants. nzb_gemm_static
 that scratch in a fixed 32 MiB array inside the library. This test drives it through the
 C ABI and requires its output to match nzb_gemm's (same kernels, so bit-identical; the
 assertion uses the suite's usual e_max <= 2e-5) on two consecutive calls with different
-shapes, the second smaller than the first so stale scratch contents would show, and
-checks that an oversized problem is refused with a clear message.
+shapes, the second smaller than the first so stale scratch contents would show, checks that the
+driver's free-memory figure does not move across the calls (nothing was allocated), reads the path's
+own status word, and checks that an oversized problem is refused with a clear message.
 
 Collected last on purpose (file name): a failure here cannot hide other tests from a run
 that stops at the first failure. It passes alone in a fresh process and after the rest.
@@ -36,7 +37,8 @@ def test_static_scratch_gemm_matches_workspace_gemm_twice():
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
     g = torch.Generator(device="cuda")
     g.manual_seed(2024)
-    for (M, N, K) in [(700, 520, 900), (130, 77, 45)]:
+    free_seen = []
+    for (M, N, K) in [(700, 520, 900), (130, 77, 45), (700, 520, 900)]:
         A = torch.rand((M, K), device="cuda", generator=g) * 2 - 1
         B = torch.rand((K, N), device="cuda", generator=g) * 2 - 1
         bias = torch.rand((N,), device="cuda", generator=g)
@@ -44,14 +46,26 @@ def test_static_scratch_gemm_matches_workspace_gemm_twice():
         got = torch.full((M, N), float("nan"), device="cuda")
         d = _desc(C, M, N, K)
         d.bias_mode, d.relu = C.BIAS_ROW, 1
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
         rc = L.nzb_gemm_static(ctypes.byref(d), ctypes.c_void_p(A.data_ptr()), ctypes.c_void_p(B.data_ptr()),
                                ctypes.c_void_p(got.data_ptr()), ctypes.c_void_p(bias.data_ptr()), stream)
         assert rc == C.OK, L.nzb_last_error_string()
         torch.cuda.synchronize()
+        free_seen.append((free_before, torch.cuda.mem_get_info()[0]))
         w, x = want.double().cpu().numpy(), got.double().cpu().numpy()
         assert np.isfinite(x).all()
         assert np.max(np.abs(x - w)) / np.max(np.abs(w)) <= 2e-5
     assert nz.device_status() == 0
+    # the first call on a device may make the driver load this library's code and look up the array;
+    # from the second call on the free-memory figure must not move at all
+    for before, after in free_seen[1:]:
+        assert after == before, free_seen
+    # the path's own status word (a bounded device-side wait that gave up would be recorded there)
+    st = ctypes.c_int(-1)
+    assert L.nzb_gemm_static_status(ctypes.byref(st), stream) == C.OK and st.value == 0
+    assert L.nzb_gemm_static_status_reset(stream) == C.OK
+    assert torch.cuda.mem_get_info()[0] == free_seen[-1][1]
 
 
 def test_static_scratch_rejects_oversized_problem():
