@@ -85,6 +85,19 @@ NZB_API const char* nzb_last_error_string(void);
 NZB_API int nzb_device_status(int* status_out);
 NZB_API int nzb_device_status_reset(void);
 
+/*
+ * Lets one bounded device-side wait run out, on purpose and harmlessly: launches a two-warp kernel
+ * whose warps wait on an mbarrier nothing arrives at, one of them with a budget of limit_cycles SM
+ * cycles (1 .. 2^28). That warp gives up, raises the CTA's abort flag, the other warp sees the flag
+ * and leaves too, and the kernel writes NZB_ERR_DEVICE_TIMEOUT to the status word -- the same helpers
+ * and the same sequence as in the GEMM and convolution kernels, without any copy in flight or tensor
+ * memory held. *roles_left_dev (device int) receives the number of warps that left through the abort
+ * path (2). Afterwards nzb_device_status() reads NZB_ERR_DEVICE_TIMEOUT until it is reset, and the
+ * context is as usable as before. No counterpart in NeuZephyr, whose error policy is cudaDeviceReset
+ * (include/NeuZephyr/NeuZephyrCudaErrorHandling.cuh:101-118).
+ */
+NZB_API int nzb_selftest_wait_timeout(long long limit_cycles, int* roles_left_dev, void* stream);
+
 /* GEMM -------------------------------------------------------------------- */
 
 /* Scratch bytes nzb_gemm needs for this descriptor (fp16 operand copies). */

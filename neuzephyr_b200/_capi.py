@@ -11,7 +11,7 @@ BIAS_NONE, BIAS_ROW, BIAS_COL, BIAS_MATRIX = range(4)
 STATIC_SCRATCH_BYTES = 32 << 20
 
 EXPORTS = [
-    "nzb_version", "nzb_last_error_string", "nzb_device_status", "nzb_device_status_reset",
+    "nzb_version", "nzb_last_error_string", "nzb_device_status", "nzb_device_status_reset", "nzb_selftest_wait_timeout",
     "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_gemm_f16", "nzb_gemm_static", "nzb_gemm_static_status", "nzb_gemm_static_status_reset", "nzb_gemm_host_workspace_bytes", "nzb_gemm_host", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
     "nzb_gemm_backward", "nzb_cast_f32_f16",
     "nzb_linear_workspace_bytes", "nzb_linear_forward", "nzb_linear_backward",
@@ -82,6 +82,7 @@ def lib():
         L.nzb_cast_f32_f16.argtypes = [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                        ctypes.c_int, vp]
         L.nzb_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]
+        L.nzb_selftest_wait_timeout.argtypes = [ctypes.c_longlong, vp, vp]
         i64, f32, ci = ctypes.c_int64, ctypes.c_float, ctypes.c_int
         ld = ctypes.POINTER(LinearDesc)
         L.nzb_linear_workspace_bytes.argtypes = [ld, ctypes.POINTER(sz)]

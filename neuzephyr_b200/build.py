@@ -12,11 +12,32 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnzb.so")
-SOURCES = ["nzb_api.cu", "nzb_cast.cu", "nzb_gemm.cu", "nzb_static.cu", "nzb_host_gemm.cu", "nzb_ops.cu", "nzb_conv.cu", "nzb_linear.cu"]
+SOURCES = ["nzb_api.cu", "nzb_cast.cu", "nzb_gemm.cu", "nzb_static.cu", "nzb_selftest.cu", "nzb_host_gemm.cu", "nzb_ops.cu", "nzb_conv.cu", "nzb_linear.cu"]
 HEADERS = ["nzb_internal.h", "nzb_ptx.cuh", os.path.join("..", "..", "include", "nzb.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
+
+
+OBJ_DIR = os.path.join(HERE, "build")  # per-source objects, so that editing one file recompiles one file
+
+
+def _obj(src):
+    return os.path.join(OBJ_DIR, src[:-3] + ".o")
+
+
+def _headers_mtime():
+    return max(os.path.getmtime(os.path.join(CSRC, h)) for h in HEADERS)
+
+
+def _stale_sources():
+    hm = _headers_mtime()
+    out = []
+    for f in SOURCES:
+        o = _obj(f)
+        if not os.path.exists(o) or os.path.getmtime(o) < max(os.path.getmtime(os.path.join(CSRC, f)), hm):
+            out.append(f)
+    return out
 
 
 def _stale():
@@ -92,8 +113,18 @@ def build_tools():
 
 def build(force=False, verbose=False):
     if force or _stale():
-        cmd = [NVCC] + FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-o", LIB] + SOURCES
-        subprocess.check_call(cmd, cwd=CSRC)
+        os.makedirs(OBJ_DIR, exist_ok=True)
+        todo = SOURCES if force else _stale_sources()
+        compile_flags = [f for f in FLAGS if f != "-shared"] + (["-Xptxas", "-v"] if verbose else [])
+        procs = [(f, subprocess.Popen([NVCC] + compile_flags + ["-c", f, "-o", _obj(f)], cwd=CSRC)) for f in todo]
+        failed = [f for f, p in procs if p.wait() != 0]
+        if failed:
+            raise subprocess.CalledProcessError(1, "nvcc -c " + " ".join(failed))
+        # link to a temporary name and rename: the library in place is always a complete file
+        tmp = LIB + ".tmp"
+        subprocess.check_call([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-o", tmp] +
+                              [_obj(f) for f in SOURCES], cwd=CSRC)
+        os.replace(tmp, LIB)
     build_host(force)
     return LIB
 

@@ -4,6 +4,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "nzb_internal.h"
@@ -122,6 +123,14 @@ int make_plan(const nzb_gemm_desc* d, Plan* pl) {
     g.bias_ld = d->bias_ld;
     g.accumulate = d->accumulate ? 1 : 0;
     g.relu = d->relu ? 1 : 0;
+    // One matrix product with float4-aligned rows: the CTA-pair kernel's converter warps can stage the
+    // operands themselves (pointer alignment and the kernel choice are checked at launch).
+    pl->fusable = e0 == 1 && e1 == 1 && d->M % 4 == 0 && d->N % 4 == 0 && d->K % 4 == 0 && d->lda % 4 == 0 &&
+                  d->ldb % 4 == 0 && (g.b_mn || d->transB) &&
+                  (pl->M + 255) / 256 + (pl->N + 255) / 256 <= kFuseMaxPanels &&
+                  // enough tiles for two rounds of the persistent grid: below that the wait for the first
+                  // panels is a visible share of the run and three small kernels are as fast
+                  ((pl->M + 255) / 256) * ((pl->N + 255) / 256) >= 148;
     return NZB_OK;
 }
 
@@ -148,6 +157,15 @@ int stage_operands(Plan* pl, const nzb_gemm_desc* d, const float* A, const float
     return NZB_OK;
 }
 
+// NZB_FUSED_STAGING=0 in the environment keeps the separate staging kernels (read once per process).
+static bool fused_staging_enabled() {
+    static const bool on = [] {
+        const char* e = getenv("NZB_FUSED_STAGING");
+        return !(e && e[0] == '0');
+    }();
+    return on;
+}
+
 static int run_gemm(const nzb_gemm_desc* d, const float* A, const float* B, float* C, const float* bias, void* ws,
                     size_t ws_bytes, cudaStream_t stream) {
     Plan pl;
@@ -157,17 +175,33 @@ static int run_gemm(const nzb_gemm_desc* d, const float* A, const float* B, floa
     if (!A || !B || !C) return fail(NZB_ERR_BAD_ARG, "A, B and C must be non-null");
     if (d->bias_mode != NZB_BIAS_NONE && !bias) return fail(NZB_ERR_BAD_ARG, "bias_mode set but bias is null");
     if (d->K == 0) return fail(NZB_ERR_UNSUPPORTED, "K = 0 is not supported");
-    if (!ws || ws_bytes < pl.a_bytes + pl.b_bytes) return fail(NZB_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", pl.a_bytes + pl.b_bytes, ws ? ws_bytes : (size_t)0);
+    const size_t need = pl.a_bytes + pl.b_bytes + kFuseSyncBytes;
+    if (!ws || ws_bytes < need) return fail(NZB_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", need, ws ? ws_bytes : (size_t)0);
     if (reinterpret_cast<uintptr_t>(ws) & 255) return fail(NZB_ERR_WORKSPACE, "workspace must be 256-byte aligned");
     __half* A16 = reinterpret_cast<__half*>(ws);
     __half* B16 = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(ws) + pl.a_bytes);
     DeviceState* ds;
     rc = get_device_state(&ds);
     if (rc != NZB_OK) return rc;
-    rc = stage_operands(&pl, d, A, B, A16, B16, ds->sm_count, stream);
-    if (rc != NZB_OK) return rc;
     pl.g.C = C;
     pl.g.bias = bias;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0;
+    if (pl.fusable && aligned && fused_staging_enabled() && gemm_uses_pair_kernel(pl.g, ds->sm_count)) {
+        // one kernel: its converter warps write the fp16 copies while its tensor-core warps consume them
+        unsigned* sync = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(ws) + pl.a_bytes + pl.b_bytes);
+        const size_t used = 4 * (size_t)(8 + (pl.M + 255) / 256 + (pl.N + 255) / 256);
+        NZB_CUDA_TRY(cudaMemsetAsync(sync, 0, used, stream));
+        pl.g.A16 = A16;
+        pl.g.B16 = B16;
+        pl.g.A32 = A;
+        pl.g.B32 = B;
+        pl.g.lda32 = d->lda;
+        pl.g.ldb32 = d->ldb;
+        pl.g.fuse_sync = sync;
+        return launch_gemm(pl.g, stream);
+    }
+    rc = stage_operands(&pl, d, A, B, A16, B16, ds->sm_count, stream);
+    if (rc != NZB_OK) return rc;
     return launch_gemm(pl.g, stream);
 }
 
@@ -233,7 +267,7 @@ int nzb_gemm_workspace_bytes(const nzb_gemm_desc* desc, size_t* bytes_out) {
     Plan pl;
     int rc = make_plan(desc, &pl);
     if (rc != NZB_OK) return rc;
-    *bytes_out = pl.a_bytes + pl.b_bytes;
+    *bytes_out = pl.a_bytes + pl.b_bytes + kFuseSyncBytes;
     return NZB_OK;
 }
 

@@ -468,6 +468,110 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 // accumulating its 128 rows x 256 columns in its own tensor memory. Loads are plain
 // per-CTA TMA copies; only barrier arrivals cross between the CTAs.
 // ---------------------------------------------------------------------------
+// ---- in-kernel staging for the CTA-pair kernel ------------------------------------------------
+// One fp32 operand as stored (rows x cols, row-major) and its fp16 copy of the same layout. The
+// tensor core consumes the copy in panels of 256 output rows / columns: for a K-major copy a panel
+// is 256 storage rows, for an MN-major copy it is 256 storage columns over all rows.
+struct FuseOperand {
+    const float* src;
+    __half* dst;
+    int64_t ld_src, ld_dst;
+    int32_t rows, cols;
+    int32_t by_cols;            // panels are column ranges (MN-major copy)
+    uint32_t segs;              // by rows: 2048-float segments per storage row
+    uint32_t chunks_per_panel;  // by rows: 256 * segs; by cols: ceil(rows / 8)
+    uint32_t panels;
+};
+struct FuseParams {
+    FuseOperand a, b;
+    unsigned* sync;         // [0] next chunk; [8 + i] finished chunks of A panel i; [8 + a.panels + j] of B panel j
+    uint32_t lead_a;        // A panels of the first rasterisation group: converted right after B panel 0
+    uint32_t total_chunks;
+};
+
+// A chunk is 2048 floats: one segment of a storage row (row panels) or 8 rows x 256 columns (column
+// panels); every lane moves 16 float4, in two rounds of 8 loads followed by 8 stores.
+__device__ __forceinline__ void store_half4(__half* d, const float4& v) {
+    const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<const uint32_t*>(&lo);
+    u.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(d) = u;
+}
+__device__ __forceinline__ void convert_chunk(const FuseOperand& o, uint32_t panel, uint32_t within, int lane) {
+    if (!o.by_cols) {
+        const int64_t row = static_cast<int64_t>(panel) * 256 + within / o.segs;
+        if (row >= o.rows) return;
+        const int32_t c0 = static_cast<int32_t>(within % o.segs) * 2048;
+        const int32_t n = min(2048, o.cols - c0);
+        const float* s = o.src + row * o.ld_src + c0 + lane * 4;
+        __half* d = o.dst + row * o.ld_dst + c0 + lane * 4;
+#pragma unroll 1
+        for (int h = 0; h < 2; h++) {
+            float4 v[8];
+            const int base = h * 1024 + lane * 4;
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (base + j * 128 < n) v[j] = __ldcs(reinterpret_cast<const float4*>(s + h * 1024 + j * 128));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                if (base + j * 128 < n) store_half4(d + h * 1024 + j * 128, v[j]);
+            }
+        }
+    } else {
+        const int32_t k0 = static_cast<int32_t>(within) * 8;
+        const int32_t col = static_cast<int32_t>(panel) * 256 + lane * 4;
+        const float* s = o.src + static_cast<int64_t>(k0) * o.ld_src + col;
+        __half* d = o.dst + static_cast<int64_t>(k0) * o.ld_dst + col;
+#pragma unroll 1
+        for (int h = 0; h < 2; h++) {
+            float4 v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int r = h * 4 + (j >> 1), c = (j & 1) * 128;
+                if (k0 + r < o.rows && col + c < o.cols)
+                    v[j] = __ldcs(reinterpret_cast<const float4*>(s + static_cast<int64_t>(r) * o.ld_src + c));
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int r = h * 4 + (j >> 1), c = (j & 1) * 128;
+                if (k0 + r < o.rows && col + c < o.cols) store_half4(d + static_cast<int64_t>(r) * o.ld_dst + c, v[j]);
+            }
+        }
+    }
+}
+
+// Whole-warp bounded wait until a global counter written by other CTAs reaches `target`, followed by
+// the fence that orders the TMA (async proxy) reads after the generic-proxy writes the counter covers.
+__device__ __forceinline__ bool wait_counter_warp(const unsigned* counter, unsigned target, volatile int* abort_flag) {
+    bool ok = true;
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+    if (v < target) {
+        const long long t0 = clock64();
+        uint32_t spins = 0;
+        do {
+            __nanosleep(64);
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+            if ((++spins & 0x3f) == 0) {
+                if (*abort_flag) {
+                    ok = false;
+                    break;
+                }
+                if (clock64() - t0 > ptx::kWaitCycleLimit) {
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+            }
+        } while (v < target);
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    asm volatile("fence.proxy.async.global;" ::: "memory");
+    return ok;
+}
+
 struct PairCfg {
     static constexpr int BN = 256, STAGES = 6;
     static constexpr int A_BYTES = 128 * 64 * 2;
@@ -482,9 +586,15 @@ struct PairCfg {
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 };
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+// FUSED adds eight converter warps per CTA (448 threads) that stage the fp32 operands as fp16 while the
+// GEMM runs: they take 2048-float chunks from one global counter, in the order the tile schedule needs
+// the panels, and count finished chunks per panel; a producer warp starts a tile's loads only once the
+// tile's A panel and B panel are complete. Converters never wait for anything, so the kernel cannot
+// deadlock on itself; the producers' waits are bounded like every other wait.
+template <bool FUSED>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSED ? 448 : 192, 1)
 gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                             const GemmParams p) {
+                             const GemmParams p, const FuseParams f) {
     using namespace ptx;
     using Cfg = PairCfg;
     constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES;
@@ -537,6 +647,13 @@ gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
             const TileCoord t = decode_tile(p, tile);
             const int32_t row_a = t.mt * 256 + (int32_t)rank * 128;
             const int32_t row_b = t.nt * 256 + (int32_t)rank * 128;
+            if constexpr (FUSED) {
+                if (!wait_counter_warp(f.sync + 8 + t.mt, f.a.chunks_per_panel, abort_flag) ||
+                    !wait_counter_warp(f.sync + 8 + f.a.panels + t.nt, f.b.chunks_per_panel, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+            }
             for (int32_t r0 = 0; r0 < p.red_e0 && ok; r0++) {
                 for (int32_t r1 = 0; r1 < p.red_e1 && ok; r1++) {
                     const int32_t i0 = t.b0 + r0, i1 = t.b1 + r1;
@@ -608,6 +725,46 @@ gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __gr
                 if (ok && elect_one()) mma_commit_pair(&tfull[acc]);
                 __syncwarp();
             }
+        }
+    } else if (FUSED && warp >= 6) {
+        // ---------------- converter warps (both CTAs): fp32 -> fp16 staging ----------------
+        const uint32_t c0 = f.b.chunks_per_panel;                          // B panel 0
+        const uint32_t c1 = c0 + f.lead_a * f.a.chunks_per_panel;          // A panels of the first group
+        const uint32_t c2 = c1 + (f.b.panels - 1) * f.b.chunks_per_panel;  // remaining B panels
+        for (;;) {
+            unsigned c = 0;
+            if (lane == 0) c = atomicAdd(f.sync, 1u);
+            c = __shfl_sync(0xffffffffu, c, 0);
+            if (c >= f.total_chunks) break;
+            uint32_t panel, within, slot;
+            bool is_b;
+            if (c < c0) {
+                is_b = true; panel = 0; within = c;
+            } else if (c < c1) {
+                is_b = false; panel = (c - c0) / f.a.chunks_per_panel; within = (c - c0) % f.a.chunks_per_panel;
+            } else if (c < c2) {
+                is_b = true; panel = 1 + (c - c1) / f.b.chunks_per_panel; within = (c - c1) % f.b.chunks_per_panel;
+            } else {
+                is_b = false; panel = f.lead_a + (c - c2) / f.a.chunks_per_panel; within = (c - c2) % f.a.chunks_per_panel;
+            }
+            {
+                FuseOperand o;  // one copy of the conversion code serves both operands (register budget)
+                o.src = is_b ? f.b.src : f.a.src;
+                o.dst = is_b ? f.b.dst : f.a.dst;
+                o.ld_src = is_b ? f.b.ld_src : f.a.ld_src;
+                o.ld_dst = is_b ? f.b.ld_dst : f.a.ld_dst;
+                o.rows = is_b ? f.b.rows : f.a.rows;
+                o.cols = is_b ? f.b.cols : f.a.cols;
+                o.by_cols = is_b ? f.b.by_cols : f.a.by_cols;
+                o.segs = is_b ? f.b.segs : f.a.segs;
+                convert_chunk(o, panel, within, lane);
+                slot = is_b ? 8 + f.a.panels + panel : 8 + panel;
+            }
+            // every lane's stores become visible (to the TMA engine too) before the chunk is counted
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) atomicAdd(f.sync + slot, 1u);
         }
     } else {
         // ---------------- epilogue warps (both CTAs) ----------------
@@ -729,6 +886,28 @@ static int launch_cfg(const GemmLaunch& g, GemmParams& p, const DeviceState& ds,
 }
 
 
+// Describes one operand for the converter warps: K-major copies are staged by row panels, MN-major by
+// column panels. `out_extent` is the operand's extent along the output dimension (M for A, N for B).
+static FuseOperand fuse_operand(const float* src, int64_t ld_src, const __half* dst, int32_t mn, int64_t out_extent,
+                                int64_t K, int64_t Kp, int64_t ld_mn) {
+    FuseOperand o{};
+    o.src = src;
+    o.dst = const_cast<__half*>(dst);
+    o.ld_src = ld_src;
+    o.by_cols = mn ? 1 : 0;
+    o.panels = (uint32_t)((out_extent + 255) / 256);
+    if (mn) {  // stored K x extent
+        o.rows = (int32_t)K; o.cols = (int32_t)out_extent; o.ld_dst = ld_mn;
+        o.segs = 1;
+        o.chunks_per_panel = (uint32_t)((K + 7) / 8);
+    } else {  // stored extent x K
+        o.rows = (int32_t)out_extent; o.cols = (int32_t)K; o.ld_dst = Kp;
+        o.segs = (uint32_t)((K + 2047) / 2048);
+        o.chunks_per_panel = 256 * o.segs;
+    }
+    return o;
+}
+
 static int launch_pair(const GemmLaunch& g, GemmParams& p, const DeviceState& ds, cudaStream_t stream) {
     CUtensorMap tmA, tmB;
     int rc = make_maps(g, &tmA, &tmB, 128);
@@ -738,18 +917,43 @@ static int launch_pair(const GemmLaunch& g, GemmParams& p, const DeviceState& ds
     p.group_m = 8;
     p.splits = 1;
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * p.out_e0 * p.out_e1;
-    static std::atomic<uint64_t> smem_set{0};  // per kernel instantiation, one bit per device
-    {
-        const int rc_attr = ensure_dynamic_smem(smem_set, reinterpret_cast<const void*>(gemm_f16_tcgen05_pair_kernel), PairCfg::SMEM_BYTES);
-        if (rc_attr != NZB_OK) return rc_attr;
-    }
+    static std::atomic<uint64_t> smem_set[2];  // per kernel instantiation, one bit per device
     int64_t pairs = ds.sm_count / 2;
     if (p.total_tiles < pairs) pairs = p.total_tiles;
-    gemm_f16_tcgen05_pair_kernel<<<(unsigned)(2 * pairs), 192, PairCfg::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    FuseParams f{};
+    if (g.fuse_sync) {
+        rc = ensure_dynamic_smem(smem_set[1], reinterpret_cast<const void*>(gemm_f16_tcgen05_pair_kernel<true>),
+                                 PairCfg::SMEM_BYTES);
+        if (rc != NZB_OK) return rc;
+        f.a = fuse_operand(g.A32, g.lda32, g.A16, g.a_mn, g.M, g.K, g.Kp, g.lda16);
+        f.b = fuse_operand(g.B32, g.ldb32, g.B16, g.b_mn, g.N, g.K, g.Kp, g.ldb16);
+        f.sync = g.fuse_sync;
+        f.lead_a = (uint32_t)(p.tiles_m < p.group_m ? p.tiles_m : p.group_m);
+        const uint64_t total = (uint64_t)f.a.panels * f.a.chunks_per_panel + (uint64_t)f.b.panels * f.b.chunks_per_panel;
+        if (total >= 0xffffffffull || f.a.panels + f.b.panels > (uint64_t)kFuseMaxPanels)
+            return fail(NZB_ERR_UNSUPPORTED, "operands too large for in-kernel staging");
+        f.total_chunks = (uint32_t)total;
+        gemm_f16_tcgen05_pair_kernel<true><<<(unsigned)(2 * pairs), 448, PairCfg::SMEM_BYTES, stream>>>(tmA, tmB, p, f);
+    } else {
+        rc = ensure_dynamic_smem(smem_set[0], reinterpret_cast<const void*>(gemm_f16_tcgen05_pair_kernel<false>),
+                                 PairCfg::SMEM_BYTES);
+        if (rc != NZB_OK) return rc;
+        gemm_f16_tcgen05_pair_kernel<false><<<(unsigned)(2 * pairs), 192, PairCfg::SMEM_BYTES, stream>>>(tmA, tmB, p, f);
+    }
     NZB_CUDA_TRY(cudaGetLastError());
     return NZB_OK;
 }
 
+// True when launch_gemm_on() would take the CTA-pair kernel for this launch (the only kernel that can
+// stage its own operands).
+bool gemm_uses_pair_kernel(const GemmLaunch& g, int sm_count) {
+    if (g.M <= 128 || g.N <= 128 || g.force_single_cta) return false;
+    if (g.M <= 32 && g.N >= 4 * g.M && g.N > 64) return false;
+    const int64_t tiles1 = ((g.M + 127) / 128) * ((g.N + 255) / 256) * g.out_e[0] * g.out_e[1];
+    const int64_t k_iters = (int64_t)g.red_e[0] * g.red_e[1] * ((g.K + 63) / 64);
+    const bool want_split = tiles1 * 2 <= sm_count && k_iters >= 64 && !g.relu;
+    return !want_split;
+}
 
 int launch_gemm(const GemmLaunch& g, cudaStream_t stream) {
     DeviceState* ds;
@@ -820,8 +1024,10 @@ int launch_gemm_on(const GemmLaunch& g_in, const DeviceState& dstate, cudaStream
         const int64_t tiles1 = (int64_t)p.tiles_m * ((g.N + 255) / 256) * p.out_e0 * p.out_e1;
         const int64_t k_iters = (int64_t)p.red_e0 * p.red_e1 * p.k_blocks;
         const bool want_split = tiles1 * 2 <= ds->sm_count && k_iters >= 64 && !p.relu;
-        if (g.N > 128 && g.M > 128 && !g.force_single_cta && !want_split && !swap) return launch_pair(g, p, *ds, stream);
+        (void)want_split;
+        if (!swap && gemm_uses_pair_kernel(g, ds->sm_count)) return launch_pair(g, p, *ds, stream);
     }
+    if (g.fuse_sync) return fail(NZB_ERR_UNSUPPORTED, "in-kernel staging was requested for a shape the CTA-pair kernel does not take");
 
     if (g.N > 128) return launch_cfg<GemmCfg<256, 4>>(g, p, *ds, stream);
     if (g.N > 64) return launch_cfg<GemmCfg<128, 6>>(g, p, *ds, stream);

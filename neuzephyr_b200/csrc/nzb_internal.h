@@ -77,8 +77,21 @@ struct GemmLaunch {
     // instead of the K-major layout above; the leading dimension is a multiple of 8 halves.
     int32_t a_mn, b_mn;
     int64_t lda16, ldb16;
+    // In-kernel staging (CTA-pair kernel only): when fuse_sync is non-null the copies A16 / B16 have
+    // NOT been written yet; the kernel's converter warps round the fp32 sources into them, panel by
+    // panel in the order the tiles need them, while the tensor cores work on finished panels.
+    // fuse_sync points to kFuseSyncBytes of device memory zeroed on the launch stream.
+    const float* A32;
+    const float* B32;
+    int64_t lda32, ldb32;
+    unsigned* fuse_sync;
 };
+// Counters of the in-kernel staging: next chunk, then one finished-chunk count per 256-wide panel.
+constexpr size_t kFuseSyncBytes = 16384;
+constexpr int64_t kFuseMaxPanels = (int64_t)(kFuseSyncBytes / 4) - 8;
 int launch_gemm(const GemmLaunch& g, cudaStream_t stream);
+// True when launch_gemm_on() takes the CTA-pair kernel for this launch.
+bool gemm_uses_pair_kernel(const GemmLaunch& g, int sm_count);
 // Same launches with the device facts supplied by the caller instead of looked up
 // (ds needs sm_count and status_dev only).
 int launch_gemm_on(const GemmLaunch& g, const DeviceState& ds, cudaStream_t stream);
@@ -98,6 +111,7 @@ struct Plan {
     int64_t Mp, Np;  // leading dimensions of MN-major copies
     int64_t nA0, nA1, nB0, nB1;  // matrices in the fp16 copies along each batch dimension
     size_t a_bytes, b_bytes;
+    bool fusable;  // one matrix product whose staging the CTA-pair kernel can do itself
     GemmLaunch g;
 };
 int make_plan(const nzb_gemm_desc* d, Plan* pl);

@@ -45,21 +45,25 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
 // exceeds it raises the CTA-wide abort flag; every role then leaves its loop.
 constexpr long long kWaitCycleLimit = 1ll << 32;
 
-// Returns false if the wait was abandoned (this CTA aborted).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+// Returns false if the wait was abandoned (this CTA aborted). `limit` is the cycle budget.
+__device__ __forceinline__ bool mbar_wait_bounded_limit(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                                        long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0xff) == 0) {
             if (*abort_flag) return false;
-            if (clock64() - t0 > kWaitCycleLimit) {
+            if (clock64() - t0 > limit) {
                 *abort_flag = 1;
                 return false;
             }
         }
     }
     return true;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    return mbar_wait_bounded_limit(bar, parity, abort_flag, kWaitCycleLimit);
 }
 
 // Variant for roles that are not on the critical path: backs off with nanosleep so that idle

@@ -5,9 +5,40 @@
 // gradient's pending writers and publishes a writer event on it.
 #pragma once
 #include <cstddef>
+#include <cstdint>
+#include <functional>
 #include <string>
 
 namespace nz::dist {
+
+// File rendezvous used to hand the NCCL unique id from rank 0 to the other ranks. A record carries
+// a magic word, the launcher's nonce and its creation time, so that a file left behind by an earlier
+// or crashed run is never taken for this run's: readers ignore records whose nonce differs or that
+// were written more than `max_age_s` before the reader started waiting. The writer removes any old
+// file first and publishes with a rename, so a reader never sees a partial record. Host-only code.
+void rendezvousPublish(const std::string& file, const void* payload, size_t bytes, uint64_t nonce);
+// Blocks until a valid record appears; throws std::runtime_error("timed out ...") after timeout_s.
+void rendezvousWait(const std::string& file, void* payload, size_t bytes, uint64_t nonce, double timeout_s,
+                    double max_age_s);
+// Nonce of this launch: NZ_DP_NONCE if set, else a hash of MASTER_ADDR, MASTER_PORT and
+// TORCHELASTIC_RUN_ID (equal on all ranks of one launch).
+uint64_t launchNonce();
+
+// Watches a collective that has been queued: polls its state until it is done, reports an error, or
+// a host deadline passes; on error or deadline it calls `abort` once so that no rank stays blocked in
+// a collective a peer never joined. poll() returns 0 = finished, 1 = in progress, anything else = the
+// failing code (NCCL: ncclCommGetAsyncError + stream query; tests: a scripted sequence).
+struct CollectiveWatchdog {
+    enum Outcome { Done = 0, Failed = 1, TimedOut = 2 };
+    std::function<int()> poll;
+    std::function<void()> abort;
+    double deadline_s = 30.0;
+    double poll_interval_s = 0.001;
+    int last_code = 0;
+    int polls = 0;
+    bool aborted = false;
+    Outcome wait();
+};
 
 class Communicator {
 public:
@@ -26,12 +57,19 @@ public:
     // in-place sum of a small host-visible value (used for reporting the loss)
     float allReduceSumHost(float v);
     void barrier();
+    // Host-side health check of the communicator: waits (at most deadline_s) for everything queued on
+    // the communication stream while polling ncclCommGetAsyncError; on an asynchronous error or when
+    // the deadline passes it aborts the communicator (ncclCommAbort) and throws, instead of leaving
+    // this rank blocked in a collective that a failed peer never joins.
+    void waitHealthy(double deadline_s = 30.0);
+    bool aborted() const { return aborted_; }
 
 private:
     int rank_, world_;
     void* comm_ = nullptr;    // ncclComm_t
     void* stream_ = nullptr;  // dedicated communication stream
     float* scalar_ = nullptr;
+    bool aborted_ = false;
 };
 
 }  // namespace nz::dist

@@ -22,34 +22,102 @@ using SM = cuStrm::StreamManager<float>;
             throw std::runtime_error(std::string("NCCL: ") + ncclGetErrorString(r_) + " in " #call); \
     } while (0)
 
+namespace {
+struct RendezvousHeader {
+    uint64_t magic, nonce;
+    int64_t created_ns;  // wall clock (system_clock) of the writer
+    uint64_t bytes;
+};
+constexpr uint64_t kRendezvousMagic = 0x4e5a44503152657aull;  // "NZDP1Rez"
+int64_t wall_ns() {
+    return std::chrono::duration_cast<std::chrono::nanoseconds>(std::chrono::system_clock::now().time_since_epoch())
+        .count();
+}
+uint64_t fnv1a(uint64_t h, const char* s) {
+    for (; s && *s; s++) h = (h ^ (unsigned char)*s) * 1099511628211ull;
+    return h;
+}
+}  // namespace
+
+void rendezvousPublish(const std::string& file, const void* payload, size_t bytes, uint64_t nonce) {
+    std::remove(file.c_str());  // whatever an earlier run left behind
+    const std::string tmp = file + ".tmp";
+    FILE* f = fopen(tmp.c_str(), "wb");
+    const RendezvousHeader h{kRendezvousMagic, nonce, wall_ns(), (uint64_t)bytes};
+    if (!f || fwrite(&h, sizeof(h), 1, f) != 1 || fwrite(payload, bytes, 1, f) != 1) {
+        if (f) fclose(f);
+        throw std::runtime_error("cannot write " + tmp);
+    }
+    fclose(f);
+    if (rename(tmp.c_str(), file.c_str()) != 0) throw std::runtime_error("cannot publish " + file);
+}
+
+void rendezvousWait(const std::string& file, void* payload, size_t bytes, uint64_t nonce, double timeout_s,
+                    double max_age_s) {
+    const auto t0 = std::chrono::steady_clock::now();
+    const int64_t started = wall_ns();
+    std::string why = "no file";
+    for (;;) {
+        FILE* f = fopen(file.c_str(), "rb");
+        if (f) {
+            RendezvousHeader h{};
+            const bool got = fread(&h, sizeof(h), 1, f) == 1 && h.magic == kRendezvousMagic && h.bytes == bytes &&
+                             fread(payload, bytes, 1, f) == 1;
+            fclose(f);
+            if (!got) why = "unreadable or foreign record";
+            else if (h.nonce != nonce) why = "record of another launch (nonce differs)";
+            else if ((double)(started - h.created_ns) * 1e-9 > max_age_s) why = "stale record (older than this launch)";
+            else return;
+        }
+        if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > timeout_s)
+            throw std::runtime_error("timed out waiting for the rendezvous file " + file + " (" + why + ")");
+        std::this_thread::sleep_for(std::chrono::milliseconds(10));
+    }
+}
+
+uint64_t launchNonce() {
+    if (const char* n = getenv("NZ_DP_NONCE")) return strtoull(n, nullptr, 0);
+    uint64_t h = 1469598103934665603ull;
+    h = fnv1a(h, getenv("MASTER_ADDR"));
+    h = fnv1a(h, getenv("MASTER_PORT"));
+    h = fnv1a(h, getenv("TORCHELASTIC_RUN_ID"));
+    return h;
+}
+
+CollectiveWatchdog::Outcome CollectiveWatchdog::wait() {
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        last_code = poll();
+        polls++;
+        if (last_code == 0) return Done;
+        const bool failed = last_code != 1;
+        const bool late = std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > deadline_s;
+        if (failed || late) {
+            if (abort && !aborted) abort();
+            aborted = true;
+            return failed ? Failed : TimedOut;
+        }
+        std::this_thread::sleep_for(std::chrono::duration<double>(poll_interval_s));
+    }
+}
+
 Communicator::Communicator(int rank, int world, const std::string& id_file, int device, double timeout_s)
     : rank_(rank), world_(world) {
     CHECK(cudaSetDevice(device));
     ncclUniqueId id;
+    const uint64_t nonce = launchNonce();
     if (rank == 0) {
         NCCL_TRY(ncclGetUniqueId(&id));
-        const std::string tmp = id_file + ".tmp";
-        FILE* f = fopen(tmp.c_str(), "wb");
-        if (!f || fwrite(&id, sizeof(id), 1, f) != 1) throw std::runtime_error("cannot write " + tmp);
-        fclose(f);
-        if (rename(tmp.c_str(), id_file.c_str()) != 0) throw std::runtime_error("cannot publish " + id_file);
+        rendezvousPublish(id_file, &id, sizeof(id), nonce);
     } else {
-        const auto t0 = std::chrono::steady_clock::now();
-        for (;;) {
-            FILE* f = fopen(id_file.c_str(), "rb");
-            if (f) {
-                const size_t n = fread(&id, sizeof(id), 1, f);
-                fclose(f);
-                if (n == 1) break;
-            }
-            if (std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count() > timeout_s)
-                throw std::runtime_error("timed out waiting for the NCCL id file " + id_file);
-            std::this_thread::sleep_for(std::chrono::milliseconds(20));
-        }
+        // a record must not predate this rank's start by more than the time ranks may take to come up
+        rendezvousWait(id_file, &id, sizeof(id), nonce, timeout_s, timeout_s);
     }
     ncclComm_t c;
     NCCL_TRY(ncclCommInitRank(&c, world, id, rank));
     comm_ = c;
+    // ncclCommInitRank returns once every rank has joined, i.e. has read the record
+    if (rank == 0) std::remove(id_file.c_str());
     cudaStream_t s;
     CHECK(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
     stream_ = s;
@@ -68,7 +136,7 @@ Communicator* Communicator::fromEnvironment() {
 }
 
 Communicator::~Communicator() {
-    if (comm_) ncclCommDestroy(static_cast<ncclComm_t>(comm_));
+    if (comm_ && !aborted_) ncclCommDestroy(static_cast<ncclComm_t>(comm_));
     if (stream_) cudaStreamDestroy(static_cast<cudaStream_t>(stream_));
     if (scalar_) cudaFree(scalar_);
 }
@@ -101,6 +169,34 @@ float Communicator::allReduceSumHost(float v) {
 }
 
 void Communicator::barrier() { (void)allReduceSumHost(0.f); }
+
+void Communicator::waitHealthy(double deadline_s) {
+    if (world_ <= 1 || aborted_) return;
+    cudaStream_t s = static_cast<cudaStream_t>(stream_);
+    ncclComm_t c = static_cast<ncclComm_t>(comm_);
+    CollectiveWatchdog w;
+    w.deadline_s = deadline_s;
+    w.poll = [&]() -> int {
+        ncclResult_t state = ncclSuccess;
+        const ncclResult_t q = ncclCommGetAsyncError(c, &state);
+        if (q != ncclSuccess) return 100 + (int)q;
+        if (state != ncclSuccess && state != ncclInProgress) return 100 + (int)state;
+        const cudaError_t e = cudaStreamQuery(s);
+        if (e == cudaSuccess) return 0;
+        if (e == cudaErrorNotReady) return 1;
+        return 1000 + (int)e;
+    };
+    w.abort = [&]() {
+        ncclCommAbort(c);
+        aborted_ = true;
+    };
+    const auto out = w.wait();
+    if (out == CollectiveWatchdog::Failed)
+        throw std::runtime_error("NCCL reported an asynchronous error (code " + std::to_string(w.last_code) +
+                                 "); the communicator was aborted");
+    if (out == CollectiveWatchdog::TimedOut)
+        throw std::runtime_error("collectives did not finish within the host deadline; the communicator was aborted");
+}
 
 }  // namespace nz::dist
 
@@ -147,6 +243,50 @@ int nzb_dp_world(void* comm, int* rank_out, int* world_out) {
     if (rank_out) *rank_out = c->rank();
     if (world_out) *world_out = c->world();
     return NZB_OK;
+}
+
+int nzb_dp_wait_healthy(void* comm, double deadline_s) {
+    if (!comm) return dp_fail(NZB_ERR_BAD_ARG, "null communicator");
+    try {
+        static_cast<nz::dist::Communicator*>(comm)->waitHealthy(deadline_s > 0 ? deadline_s : 30.0);
+    } catch (const std::exception& e) {
+        return dp_fail(NZB_ERR_CUDA, e.what());
+    }
+    return NZB_OK;
+}
+
+int nzb_dp_rendezvous_publish(const char* file, const void* payload, size_t bytes, uint64_t nonce) {
+    if (!file || !payload) return dp_fail(NZB_ERR_BAD_ARG, "null argument");
+    try {
+        nz::dist::rendezvousPublish(file, payload, bytes, nonce);
+    } catch (const std::exception& e) {
+        return dp_fail(NZB_ERR_CUDA, e.what());
+    }
+    return NZB_OK;
+}
+
+int nzb_dp_rendezvous_wait(const char* file, void* payload, size_t bytes, uint64_t nonce, double timeout_s,
+                           double max_age_s) {
+    if (!file || !payload) return dp_fail(NZB_ERR_BAD_ARG, "null argument");
+    try {
+        nz::dist::rendezvousWait(file, payload, bytes, nonce, timeout_s, max_age_s);
+    } catch (const std::exception& e) {
+        return dp_fail(NZB_ERR_CUDA, e.what());
+    }
+    return NZB_OK;
+}
+
+int nzb_dp_watchdog_run(const int* poll_script, int n, double deadline_s, int* polls_out, int* aborted_out) {
+    if (!poll_script || n < 1) return dp_fail(NZB_ERR_BAD_ARG, "empty poll script");
+    nz::dist::CollectiveWatchdog w;
+    int i = 0, aborts = 0;
+    w.deadline_s = deadline_s;
+    w.poll = [&]() { return poll_script[i < n - 1 ? i++ : n - 1]; };  // the last entry repeats
+    w.abort = [&]() { aborts++; };
+    const int out = (int)w.wait();
+    if (polls_out) *polls_out = w.polls;
+    if (aborted_out) *aborted_out = aborts;
+    return out;
 }
 
 int nzb_dp_finalize(void* comm) {

@@ -9,6 +9,10 @@ from neuzephyr_b200 import _capi as C
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+# counters of the in-kernel operand staging that follow the two fp16 copies in a GEMM workspace
+SYNC = 16384
+
+
 def declared_symbols():
     text = open(os.path.join(ROOT, "include", "nzb.h")).read()
     return sorted(set(re.findall(r"NZB_API\s+[\w\s\*]+?\b(nzb_\w+)\s*\(", text)))
@@ -38,16 +42,16 @@ def test_workspace_sizing_and_validation():
     assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.OK
     # A (M x K) is staged K-major [M][Kp]; B (K x N, N > 32) keeps its layout, MN-major [K][Np]
     kp, np_ = 192, 192
-    assert n.value == (127 * kp * 2 + 255) // 256 * 256 + (131 * np_ * 2 + 255) // 256 * 256
+    assert n.value == (127 * kp * 2 + 255) // 256 * 256 + (131 * np_ * 2 + 255) // 256 * 256 + SYNC
     d.batch[0], d.batch[1] = 4, 3
     d.strideA[0], d.strideA[1] = 3 * 127 * 131, 127 * 131
     d.strideB[0], d.strideB[1] = 0, 131 * 129
     assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.OK
-    assert n.value == (12 * 127 * kp * 2 + 255) // 256 * 256 + (3 * 131 * np_ * 2 + 255) // 256 * 256
+    assert n.value == (12 * 127 * kp * 2 + 255) // 256 * 256 + (3 * 131 * np_ * 2 + 255) // 256 * 256 + SYNC
     d.transB = 1  # B stored N x K: K-major copy [N][Kp]
     d.ldb = 131
     assert L.nzb_gemm_workspace_bytes(ctypes.byref(d), ctypes.byref(n)) == C.OK
-    assert n.value == (12 * 127 * kp * 2 + 255) // 256 * 256 + (3 * 129 * kp * 2 + 255) // 256 * 256
+    assert n.value == (12 * 127 * kp * 2 + 255) // 256 * 256 + (3 * 129 * kp * 2 + 255) // 256 * 256 + SYNC
     d.transB = 0
     d.ldb = 129
     d.ldc = 5
@@ -64,7 +68,7 @@ def test_shape_entry_points_validate_without_a_device():
     n = ctypes.c_size_t(0)
     sa, sb, sc = C.shape4((2, 1, 8, 16)), C.shape4((1, 3, 16, 4)), C.shape4((2, 3, 8, 4))
     assert L.nzb_tensorcore_gemm_workspace_bytes(sa, sb, sc, ctypes.byref(n)) == C.OK
-    assert n.value == (2 * 8 * 64 * 2 + 255) // 256 * 256 + (3 * 4 * 64 * 2 + 255) // 256 * 256
+    assert n.value == (2 * 8 * 64 * 2 + 255) // 256 * 256 + (3 * 4 * 64 * 2 + 255) // 256 * 256 + SYNC
     bad = C.shape4((2, 3, 8, 5))
     assert L.nzb_tensorcore_gemm_workspace_bytes(sa, sb, bad, ctypes.byref(n)) == C.ERR_BAD_ARG
     incompatible = C.shape4((3, 1, 8, 16))
@@ -83,7 +87,8 @@ def test_dp_library_exports_and_validates():
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     hdr = open(os.path.join(root, "include", "nzb_dp.h")).read()
     names = re.findall(r"NZB_API\s+[\w\s\*]+?\b(nzb_dp_\w+)\s*\(", hdr)
-    assert sorted(names) == sorted(["nzb_dp_init", "nzb_dp_allreduce_avg", "nzb_dp_world", "nzb_dp_finalize",
+    assert sorted(names) == sorted(["nzb_dp_init", "nzb_dp_allreduce_avg", "nzb_dp_world", "nzb_dp_finalize", "nzb_dp_wait_healthy",
+                                    "nzb_dp_rendezvous_publish", "nzb_dp_rendezvous_wait", "nzb_dp_watchdog_run",
                                     "nzb_dp_last_error_string"])
     lib_path = os.path.join(root, "neuzephyr_b200", "libneuzephyr_host.so")
     assert os.path.exists(lib_path), "build the host layer first (python -c 'import __graft_entry__ as g; g.build()')"

@@ -69,13 +69,18 @@ def test_sharded_gradients_against_fp64_host_gradient(tmp_path, world):
     x, t = ld("x", (B, 3, S, S)), ld("t", (B, 1, 16, 1))
     params = [ld("p%d" % i, shp) for i, shp in enumerate(shapes)]
     _, truth = MS.seg_model_gradients(x, t, params, exact=True)
+    _, rounded = MS.seg_model_gradients(x, t, params, exact=False)
     worst = 0.0
     for i, shp in enumerate(shapes):
         den = np.max(np.abs(truth[i]))
         e_sh = float(np.max(np.abs(ld("sharded_g%d" % i, shp) - truth[i])) / den)
         e_full = float(np.max(np.abs(ld("full_g%d" % i, shp) - truth[i])) / den)
+        # what the reference's own arithmetic (fp16-rounded GEMM operands, no loss scaling) loses on this
+        # tensor: gradients that reach the first layers are 1e-5 and below, in fp16's subnormal range
+        e_alg = float(np.max(np.abs(rounded[i] - truth[i])) / den)
         worst = max(worst, e_sh, e_full)
-        assert e_sh <= 1e-2 and e_full <= 1e-2, (i, e_sh, e_full)
+        bound = max(1e-2, 2 * e_alg)
+        assert e_sh <= bound and e_full <= bound, (i, e_sh, e_full, e_alg)
         assert e_sh <= 2 * e_full + 2e-4, (i, e_sh, e_full)
     # the tool's own tolerance between the two is of the size of their distance to the truth
     assert out["max_rel_grad_diff"] <= 2e-3 and out["max_rel_grad_diff"] <= 2 * worst + 2e-4
