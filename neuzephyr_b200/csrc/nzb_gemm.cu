@@ -469,6 +469,8 @@ gemm_f16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_co
 // per-CTA TMA copies; only barrier arrivals cross between the CTAs.
 // ---------------------------------------------------------------------------
 // ---- in-kernel staging for the CTA-pair kernel ------------------------------------------------
+constexpr int kFuseChunk = 8192;  // floats per unit of conversion work
+constexpr int kFuseWarps = 14;    // converter warps per CTA: as many as the register file allows beside the GEMM roles
 // One fp32 operand as stored (rows x cols, row-major) and its fp16 copy of the same layout. The
 // tensor core consumes the copy in panels of 256 output rows / columns: for a K-major copy a panel
 // is 256 storage rows, for an MN-major copy it is 256 storage columns over all rows.
@@ -478,8 +480,8 @@ struct FuseOperand {
     int64_t ld_src, ld_dst;
     int32_t rows, cols;
     int32_t by_cols;            // panels are column ranges (MN-major copy)
-    uint32_t segs;              // by rows: 2048-float segments per storage row
-    uint32_t chunks_per_panel;  // by rows: 256 * segs; by cols: ceil(rows / 8)
+    uint32_t segs;              // by rows: chunk-sized segments per storage row
+    uint32_t chunks_per_panel;  // by rows: 256 * segs; by cols: ceil(rows / rows-per-chunk)
     uint32_t panels;
 };
 struct FuseParams {
@@ -489,8 +491,9 @@ struct FuseParams {
     uint32_t total_chunks;
 };
 
-// A chunk is 2048 floats: one segment of a storage row (row panels) or 8 rows x 256 columns (column
-// panels); every lane moves 16 float4, in two rounds of 8 loads followed by 8 stores.
+// A chunk is kFuseChunk floats: one segment of a storage row (row panels) or kFuseChunk / 256 rows x 256
+// columns (column panels), moved in rounds of 8 float4 loads followed by 8 half4 stores per lane. Large
+// chunks amortise what every chunk pays once: the atomic that hands it out, the fences and the counter.
 __device__ __forceinline__ void store_half4(__half* d, const float4& v) {
     const __half2 lo = __floats2half2_rn(v.x, v.y), hi = __floats2half2_rn(v.z, v.w);
     uint2 u;
@@ -502,12 +505,13 @@ __device__ __forceinline__ void convert_chunk(const FuseOperand& o, uint32_t pan
     if (!o.by_cols) {
         const int64_t row = static_cast<int64_t>(panel) * 256 + within / o.segs;
         if (row >= o.rows) return;
-        const int32_t c0 = static_cast<int32_t>(within % o.segs) * 2048;
-        const int32_t n = min(2048, o.cols - c0);
+        const int32_t c0 = static_cast<int32_t>(within % o.segs) * kFuseChunk;
+        const int32_t n = min(kFuseChunk, o.cols - c0);
         const float* s = o.src + row * o.ld_src + c0 + lane * 4;
         __half* d = o.dst + row * o.ld_dst + c0 + lane * 4;
 #pragma unroll 1
-        for (int h = 0; h < 2; h++) {
+        for (int h = 0; h < kFuseChunk / 1024; h++) {
+            if (h * 1024 >= n) break;
             float4 v[8];
             const int base = h * 1024 + lane * 4;
 #pragma unroll
@@ -520,12 +524,13 @@ __device__ __forceinline__ void convert_chunk(const FuseOperand& o, uint32_t pan
             }
         }
     } else {
-        const int32_t k0 = static_cast<int32_t>(within) * 8;
+        const int32_t k0 = static_cast<int32_t>(within) * (kFuseChunk / 256);
         const int32_t col = static_cast<int32_t>(panel) * 256 + lane * 4;
         const float* s = o.src + static_cast<int64_t>(k0) * o.ld_src + col;
         __half* d = o.dst + static_cast<int64_t>(k0) * o.ld_dst + col;
 #pragma unroll 1
-        for (int h = 0; h < 2; h++) {
+        for (int h = 0; h < kFuseChunk / 1024; h++) {
+            if (k0 + h * 4 >= o.rows) break;
             float4 v[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) {
@@ -586,13 +591,13 @@ struct PairCfg {
     static_assert(SMEM_BYTES <= 232448, "exceeds the 227 KB shared memory of an sm_100 CTA");
 };
 
-// FUSED adds eight converter warps per CTA (448 threads) that stage the fp32 operands as fp16 while the
-// GEMM runs: they take 2048-float chunks from one global counter, in the order the tile schedule needs
+// FUSED adds kFuseWarps converter warps per CTA that stage the fp32 operands as fp16 while the
+// GEMM runs: they take kFuseChunk-float chunks from one global counter, in the order the tile schedule needs
 // the panels, and count finished chunks per panel; a producer warp starts a tile's loads only once the
 // tile's A panel and B panel are complete. Converters never wait for anything, so the kernel cannot
 // deadlock on itself; the producers' waits are bounded like every other wait.
 template <bool FUSED>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSED ? 448 : 192, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(FUSED ? 192 + 32 * kFuseWarps : 192, 1)
 gemm_f16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                              const GemmParams p, const FuseParams f) {
     using namespace ptx;
@@ -899,10 +904,10 @@ static FuseOperand fuse_operand(const float* src, int64_t ld_src, const __half* 
     if (mn) {  // stored K x extent
         o.rows = (int32_t)K; o.cols = (int32_t)out_extent; o.ld_dst = ld_mn;
         o.segs = 1;
-        o.chunks_per_panel = (uint32_t)((K + 7) / 8);
+        o.chunks_per_panel = (uint32_t)((K + kFuseChunk / 256 - 1) / (kFuseChunk / 256));
     } else {  // stored extent x K
         o.rows = (int32_t)out_extent; o.cols = (int32_t)K; o.ld_dst = Kp;
-        o.segs = (uint32_t)((K + 2047) / 2048);
+        o.segs = (uint32_t)((K + kFuseChunk - 1) / kFuseChunk);
         o.chunks_per_panel = 256 * o.segs;
     }
     return o;
@@ -933,7 +938,7 @@ static int launch_pair(const GemmLaunch& g, GemmParams& p, const DeviceState& ds
         if (total >= 0xffffffffull || f.a.panels + f.b.panels > (uint64_t)kFuseMaxPanels)
             return fail(NZB_ERR_UNSUPPORTED, "operands too large for in-kernel staging");
         f.total_chunks = (uint32_t)total;
-        gemm_f16_tcgen05_pair_kernel<true><<<(unsigned)(2 * pairs), 448, PairCfg::SMEM_BYTES, stream>>>(tmA, tmB, p, f);
+        gemm_f16_tcgen05_pair_kernel<true><<<(unsigned)(2 * pairs), 192 + 32 * kFuseWarps, PairCfg::SMEM_BYTES, stream>>>(tmA, tmB, p, f);
     } else {
         rc = ensure_dynamic_smem(smem_set[0], reinterpret_cast<const void*>(gemm_f16_tcgen05_pair_kernel<false>),
                                  PairCfg::SMEM_BYTES);

@@ -50,7 +50,7 @@ static void linear_sizes(const nzb_linear_desc* d, LinearSizes* z) {
     z->Inp = round_up(z->In, 64); z->Outp = round_up(z->Out, 64); z->Bp = round_up(z->B, 64);
     z->x16 = (size_t)round_up(z->B * z->Inp * 2, 256);
     z->w16 = (size_t)round_up(z->Out * z->Inp * 2, 256);
-    z->total_fwd = z->x16 + z->w16;
+    z->total_fwd = z->x16 + z->w16 + kFuseSyncBytes;  // the forward is one nzb_gemm call
     z->dy16 = (size_t)round_up(z->B * z->Outp * 2, 256);
     z->total_bwd = z->dy16 + z->w16 + z->x16;
 }

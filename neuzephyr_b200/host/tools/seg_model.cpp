@@ -10,7 +10,8 @@
 //   seg_model check  <global_batch> <size> emulate <W> [dir]  the same comparison on ONE GPU: the W shards run one after the
 //                                                             other and their gradients are averaged on the host; with dir,
 //                                                             writes sharded_g<i>.bin / full_g<i>.bin (the gradients compared)
-//   seg_model step_file <dir> <batch> <size> <steps> <shared> reads x.bin, t.bin, p0..p5.bin (float32) from dir, runs `steps`
+//   seg_model step_file <dir> <batch> <size> <steps> <shared> [lr]  (Adam learning rate, default 0.01)
+//                                                             reads x.bin, t.bin, p0..p5.bin (float32) from dir, runs `steps`
 //                                                             training steps, writes loss.txt, g0..g5.bin (gradients of the first
 //                                                             backward) and q<step>_<i>.bin (parameters after each update);
 //                                                             shared = 0 gives every sample its own convolution weights, as
@@ -90,7 +91,7 @@ static void write_bin(const std::string& path, const std::vector<float>& v) {
     fclose(f);
 }
 // step_file: a training run on injected data and parameters, results written as raw float32 files
-static int step_file(const std::string& dir, size_t B, size_t S, int steps, bool shared) {
+static int step_file(const std::string& dir, size_t B, size_t S, int steps, bool shared, float lr) {
     SegModel model(B, S, !shared);
     auto x = read_bin(dir + "/x.bin", B * 3 * S * S), t = read_bin(dir + "/t.bin", B * 16);
     model.input.dataInject(x.data());
@@ -101,7 +102,7 @@ static int step_file(const std::string& dir, size_t B, size_t S, int steps, bool
         params[i]->dataInject(p.data());
     }
     model.graph().zeroGrad();
-    opt::Adam adam(0.01f, 0.9f, 0.999f);
+    opt::Adam adam(lr, 0.9f, 0.999f);
     FILE* lf = fopen((dir + "/loss.txt").c_str(), "w");
     for (int s = 0; s < steps; s++) {
         model.forward();
@@ -156,12 +157,13 @@ int main(int argc, char** argv) {
     }
     const std::string mode = argv[1];
     if (mode == "step_file") {
-        if (argc != 7) {
-            fprintf(stderr, "usage: seg_model step_file <dir> <batch> <size> <steps> <shared>\n");
+        if (argc != 7 && argc != 8) {
+            fprintf(stderr, "usage: seg_model step_file <dir> <batch> <size> <steps> <shared> [learning rate]\n");
             return 2;
         }
         CHECK(cudaSetDevice(getenv("LOCAL_RANK") ? atoi(getenv("LOCAL_RANK")) : 0));
-        return step_file(argv[2], atoll(argv[3]), atoll(argv[4]), atoi(argv[5]), atoi(argv[6]) != 0);
+        return step_file(argv[2], atoll(argv[3]), atoll(argv[4]), atoi(argv[5]), atoi(argv[6]) != 0,
+                         argc == 8 ? (float)atof(argv[7]) : 0.01f);
     }
     const size_t B = atoll(argv[2]), S = atoll(argv[3]);
     if (mode == "check" && argc >= 6 && std::string(argv[4]) == "emulate") {

@@ -73,9 +73,14 @@ struct Chain {
         for (Node* n : nodes) n->forward();
     }
     void backward(float* dy) {
+        // full synchronisation between the phases: the library orders its launches per data pointer,
+        // and nothing here should depend on how it orders a clear against a later accumulation
+        cudaDeviceSynchronize();
         for (Node* n : nodes)
             if (n->output->requiresGrad()) n->output->zeroGrad();
+        cudaDeviceSynchronize();
         nodes.back()->output->dataInject(dy, true);
+        cudaDeviceSynchronize();
         for (auto it = nodes.rbegin(); it != nodes.rend(); ++it) (*it)->backward();
         cudaDeviceSynchronize();
     }
@@ -282,11 +287,16 @@ int main(int argc, char** argv) {
             auto hp = read_bin(in_dir(dir, "p" + std::to_string(i) + ".bin").c_str(), m.params[i]->output->size());
             m.params[i]->output->dataInject(hp.data());
         }
-        m.g.zeroGrad();
+        // ComputeGraph::zeroGrad() would dereference the loss node's output, which the reference only
+        // sets in OutputNode::forward(): clear the gradients node by node instead
+        for (Node* n : m.owned)
+            if (n->output && n->output->requiresGrad()) n->output->zeroGrad();
+        cudaDeviceSynchronize();
         nz::opt::Adam adam(0.01f, 0.9f, 0.999f);
         FILE* lf = fopen(in_dir(dir, "ref_loss.txt").c_str(), "w");
         for (int s = 0; s < steps; s++) {
             m.g.forward();
+            cudaDeviceSynchronize();
             fprintf(lf, "%.9g\n", m.g.getLoss());  // accumulates over steps, as the reference's loss node does
             m.g.backward();
             cudaDeviceSynchronize();

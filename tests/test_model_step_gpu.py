@@ -7,6 +7,7 @@ compared on the same injected inputs and parameters with
   * NeuZephyr itself rebuilt for sm_100 (oracle/_ref/ref_harness model_file), which builds the same
     node sequence Model's builders create and runs ComputeGraph::forward/backward/update + zeroGrad.
 
+(The reference's backward is only partly defined for this model, see test_step_against_reference.)
 Acceptance per gradient tensor: e_max = max|g - g64| / max|g64| <= max(1e-2, 2 * e_max(the rounded oracle))
 and <= 2 * e_max(reference) -- gradients reaching the first layers are 1e-5 and smaller, inside fp16's
 subnormal range, so the reference's own arithmetic (fp16 GEMM operands, no loss scaling) already loses
@@ -82,11 +83,14 @@ def _param_diff(q, q_ref, g_ref):
 @pytest.mark.parametrize("N,S,per_sample", [(2, 32, False), (3, 20, True)])
 def test_two_steps_against_oracle(tmp_path, N, S, per_sample):
     x, t, params = _case(tmp_path, N, S, per_sample, 100 + N)
-    r = subprocess.run([_tool(), "step_file", str(tmp_path), str(N), str(S), "2", "0" if per_sample else "1"],
+    # a learning rate that keeps the second step's softmax away from saturation (at 0.01 one update moves
+    # a logit by several units through the linear layer's thousands of inputs)
+    lr = 1e-3
+    r = subprocess.run([_tool(), "step_file", str(tmp_path), str(N), str(S), "2", "0" if per_sample else "1", str(lr)],
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     g, q, losses = _load(tmp_path, "", params, 2)
-    o_losses, o_g, o_q = MS.seg_model_steps(x, t, params, 2)
+    o_losses, o_g, o_q = MS.seg_model_steps(x, t, params, 2, lr=lr)
     x_loss, x_g = MS.seg_model_gradients(x, t, params, exact=True)
     assert abs(losses[0] - o_losses[0]) <= 2e-5 * abs(o_losses[0])
     assert abs(losses[0] - x_loss) <= 1e-3 * abs(x_loss)
@@ -102,41 +106,56 @@ def test_two_steps_against_oracle(tmp_path, N, S, per_sample):
         assert e_x <= max(1e-2, 2 * e_alg), (name, e_x, e_alg)
         for s in range(2):
             d = _param_diff(q[s][i], o_q[s][i], o_g[i])
-            assert d <= 1e-4, (name, s, d)
+            assert d <= 1e-2 * lr, (name, s, d)  # a hundredth of one Adam step
     print(json.dumps(report))
 
 
 @needs_ref
 @pytest.mark.parametrize("N,S,shared", [(1, 32, False), (2, 24, False), (2, 24, True)])
 def test_step_against_reference(tmp_path, N, S, shared):
-    """A/B with NeuZephyr: same inputs, same injected parameters, two steps each."""
+    """A/B with NeuZephyr: same inputs, same injected parameters, one training step each.
+
+    What can be compared is bounded by a defect of the reference: its transpose launches a grid that
+    covers the whole matrix only when both extents span equally many 32-wide tiles
+    (src/TensorOperations.cu:122-126 against src/OperationKernels.cu:125-146), and MatMulNode::backward
+    transposes both operands (src/Nodes.cu:169-182). In this model only the loss, the linear layer's bias
+    gradient and the first 32 input columns of the linear layer's weight gradient are therefore defined in
+    the reference (x^T of an {in, 1} vector is transposed for its first 32 rows only; everything upstream
+    goes through W^T, of which only 32 columns exist). Those are compared, together with the
+    parameters they update: the linear bias is the LAST parameter the reference's optimizer steps, so its
+    update checks the per-call Adam time step (t = 17, after every earlier node's tick) end to end."""
     x, t, params = _case(tmp_path, N, S, not shared, 200 + 7 * N + int(shared))
-    r = subprocess.run([_tool(), "step_file", str(tmp_path), str(N), str(S), "2", "1" if shared else "0"],
+    r = subprocess.run([_tool(), "step_file", str(tmp_path), str(N), str(S), "1", "1" if shared else "0"],
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
-    r = subprocess.run([HARNESS, "model_file", str(tmp_path), str(N), str(S), "2", "1" if shared else "0"],
+    r = subprocess.run([HARNESS, "model_file", str(tmp_path), str(N), str(S), "1", "1" if shared else "0"],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
-    g, q, losses = _load(tmp_path, "", params, 2)
-    rg, rq, rlosses = _load(tmp_path, "ref_", params, 2)
+    g, q, losses = _load(tmp_path, "", params, 1)
+    rg, rq, rlosses = _load(tmp_path, "ref_", params, 1)
     x_loss, x_g = MS.seg_model_gradients(x, t, params, exact=True)
     assert abs(losses[0] - rlosses[0]) <= 1e-4 * abs(rlosses[0])
+    assert abs(losses[0] - x_loss) <= 1e-3 * abs(x_loss)
     report = {}
-    for i, name in enumerate(NAMES):
-        is_bias = name.endswith(".b")
-        e_ours, e_ref = emax(g[i], x_g[i]), emax(rg[i], x_g[i])
-        report[name] = {"e_ours": e_ours, "e_ref": e_ref}
-        assert e_ours <= max(1e-2, 2 * e_ref), (name, e_ours, e_ref)
-        if is_bias and N > 1:
-            # racy in the reference: each element is a sum over some subset of samples. With two
-            # samples that is one of {g0 + g1, g0, g1}; count how often the full sum came out
-            report[name]["ref_full_sum_fraction"] = float(np.mean(np.abs(rg[i] - g[i]) <= 1e-3 * np.max(np.abs(g[i]))))
+    for i, cols in ((4, 32), (5, None)):  # linear.w (first 32 input columns), linear.b
+        sl = (Ellipsis, slice(0, cols)) if cols else Ellipsis
+        ours, ref, truth = g[i][sl], rg[i][sl], x_g[i][sl]
+        den = np.max(np.abs(x_g[i]))
+        e_ours = float(np.max(np.abs(ours - truth)) / den)
+        e_ref = float(np.max(np.abs(ref - truth)) / den)
+        report[NAMES[i]] = {"e_ours": e_ours, "e_ref": e_ref}
+        if i == 5 and N > 1:
+            # the racy bias gradient (see the module docstring): report how often every term survived
+            report[NAMES[i]]["ref_full_sum_fraction"] = float(np.mean(np.abs(ref - ours) <= 1e-3 * den))
             continue
-        assert e_ours <= 2 * e_ref + 1e-6, (name, e_ours, e_ref)
-        assert emax(g[i], rg[i]) <= max(2e-3, e_ref), (name, emax(g[i], rg[i]), e_ref)
-        # both sides use the per-call Adam time steps of the default configuration. With several samples
-        # the reference's racy bias gradient feeds its second step, so only the first update is compared
-        for s in range(2 if N == 1 else 1):
-            d = _param_diff(q[s][i], rq[s][i], x_g[i])
-            assert d <= 1e-4, (name, s, d)
+        assert e_ours <= max(1e-2, 2 * e_ref) and e_ours <= 2 * e_ref + 1e-6, (NAMES[i], e_ours, e_ref)
+        assert float(np.max(np.abs(ours - ref)) / den) <= max(2e-3, e_ref), NAMES[i]
+        # parameters after the update: both sides use the per-call Adam time steps (t = 15 and t = 17)
+        gmax = np.max(np.abs(truth))
+        mask = np.abs(truth) > 1e-2 * gmax
+        d = float(np.max(np.abs(q[0][i][sl] - rq[0][i][sl])[mask]))
+        assert d <= 1e-4, (NAMES[i], d)
+        # and a wrong time step would show: t = 1 instead of 17 moves a weight 1.8 times as far
+        moved = float(np.max(np.abs(q[0][i][sl] - params[i][sl])[mask]))
+        assert moved > 3e-3, moved
     print(json.dumps(report))

@@ -92,12 +92,26 @@ def _subset_sum_ok(ref, parts, tol):
     return bool(np.all(best <= tol)), float(np.mean(full))
 
 
+def ref_transpose_ok(rows, cols):
+    """NeuZephyr's iTranspose sizes its grid as (ceil(rows/32), ceil(cols/32)) while TransposeKernel walks
+    columns with blockIdx.x and rows with blockIdx.y (src/TensorOperations.cu:122-126,
+    src/OperationKernels.cu:125-146): unless both extents span the same number of 32-wide tiles, part of
+    the transposed matrix is never written. MatMulNode::backward transposes both operands
+    (src/Nodes.cu:169-182), so the reference's dA / dB are only defined for such shapes; elsewhere this
+    suite compares the forward pass only and relies on the host oracle for the gradients."""
+    return (rows + 31) // 32 == (cols + 31) // 32
+
+
 @needs_ref
 @pytest.mark.parametrize("N,C,H,W,Co,k,stride,pad,shared,relu", [
-    (2, 3, 12, 40, 16, 3, 1, 1, True, True),     # TMA im2col kernels, shared weights, fused ReLU
-    (2, 16, 10, 48, 16, 3, 1, 1, False, False),  # one weight matrix per sample, as Model::Conv2d allocates
-    (1, 8, 11, 9, 24, 3, 1, 1, True, True),      # narrow rows: gather kernels
-    (1, 5, 13, 36, 20, 3, 2, 0, True, False),    # stride 2 (forward, dW, db)
+    (2, 3, 12, 40, 16, 3, 1, 1, True, True),     # TMA im2col kernels, shared weights, fused ReLU (forward, db)
+    (2, 16, 10, 48, 16, 3, 1, 1, False, False),  # one weight matrix per sample, as Model::Conv2d allocates (forward, db)
+    (1, 8, 11, 9, 24, 3, 1, 1, True, True),      # narrow rows: gather kernels (forward, db)
+    (1, 5, 13, 36, 20, 3, 2, 0, True, False),    # stride 2 (forward, db)
+    # shapes whose transposes the reference completes: Ho*Wo, C*k*k and Cout span equally many 32-tiles
+    (2, 16, 4, 36, 144, 3, 1, 1, True, True),    # TMA kernels, all gradients
+    (2, 16, 12, 12, 144, 3, 1, 1, False, False), # per-sample weights, gather kernels, all gradients
+    (3, 3, 4, 8, 16, 3, 1, 1, True, True),       # the first layer's K = 27
 ])
 def test_conv2d_composition_against_reference(tmp_path, N, C, H, W, Co, k, stride, pad, shared, relu):
     """Model::Conv2d's node chain (Img2Col -> MatMul -> Add -> Col2Img [-> ReLU], src/Model.cu:244-263) run by
@@ -120,11 +134,17 @@ def test_conv2d_composition_against_reference(tmp_path, N, C, H, W, Co, k, strid
     xd, wd, bd, dyd = dev(x), dev(w), dev(b), dev(dy)
     y = nz.conv2d_forward(xd, wd, bd, k, k, stride, pad, relu=relu)
     dx, dw, db = torch.zeros_like(xd), torch.zeros_like(wd), torch.zeros_like(bd)
-    if stride == 1:
+    from neuzephyr_b200._capi import NzbError
+    try:
+        # one call: ReLU mask, bias gradient, dX, dW (stride 1, rows of 32+ pixels)
         nz.conv2d_backward(xd, wd, dyd, k, k, stride, pad, dx=dx, dw=dw, dbias=db, y=y if relu else None)
-    else:
-        nz.conv2d_backward_weight(xd, dyd, w.shape, k, k, stride, pad, dw)
-        nz.conv2d_backward_bias(dyd, x.shape, w.shape, k, k, stride, pad, db)
+    except NzbError:
+        # other shapes: the separate entry points, on the masked upstream gradient
+        dym = torch.where(y > 0, dyd, torch.zeros_like(dyd)) if relu else dyd
+        nz.conv2d_backward_weight(xd, dym, w.shape, k, k, stride, pad, dw)
+        nz.conv2d_backward_bias(dym, x.shape, w.shape, k, k, stride, pad, db)
+        if stride == 1:
+            nz.conv2d_backward_data(dym, wd, x.shape, k, k, stride, pad, dx)
     torch.cuda.synchronize()
     assert nz.device_status() == 0
     y, dx, dw, db = y.cpu().numpy(), dx.cpu().numpy(), dw.cpu().numpy(), db.cpu().numpy()
@@ -132,11 +152,15 @@ def test_conv2d_composition_against_reference(tmp_path, N, C, H, W, Co, k, strid
     y_t = O.conv2d_forward(x, w, b, k, k, stride, pad, False, relu=relu)
     dy_eff = dy * (y_ref > 0) if relu else dy
     dx_t, dw_t, db_t = O.conv2d_backward(dy_eff, x, w, k, k, stride, pad, round_operands=False)
-    for name, ours, ref, truth in (("y", y, y_ref, y_t), ("dw", dw, dw_ref, dw_t)) + \
-            ((("dx", dx, dx_ref, dx_t),) if stride == 1 else ()):
+    grads_defined = ref_transpose_ok(Ho * Wo, K) and ref_transpose_ok(K, Co)
+    for name, ours, ref, truth in (("y", y, y_ref, y_t),) + \
+            ((("dw", dw, dw_ref, dw_t),) if grads_defined else ()) + \
+            ((("dx", dx, dx_ref, dx_t),) if grads_defined and stride == 1 else ()):
         e_o, e_r = emax(ours, truth), emax(ref, truth)
         assert e_o <= 1e-2 and e_o <= 2 * e_r + 1e-6, (name, e_o, e_r)
         assert emax(ours, ref) <= 1e-4, (name, emax(ours, ref))
+    # our gradients against the host oracle, whatever the reference could do with them
+    assert emax(dw, dw_t) <= 1e-2 and (stride != 1 or emax(dx, dx_t) <= 1e-2)
     assert emax(db, db_t) <= 1e-5
     parts = dy_eff.reshape(N, Co, Ho * Wo).transpose(0, 2, 1).reshape(N, 1, Ho * Wo, Co)
     explained, full = _subset_sum_ok(db_ref.astype(np.float64)[0], parts, 1e-5 * max(np.max(np.abs(db_t)), 1.0))
@@ -145,7 +169,8 @@ def test_conv2d_composition_against_reference(tmp_path, N, C, H, W, Co, k, strid
 
 
 @needs_ref
-@pytest.mark.parametrize("B,In,Out,relu", [(1, 300, 40, True), (5, 130, 24, True), (3, 64, 16, False)])
+@pytest.mark.parametrize("B,In,Out,relu", [(1, 300, 40, True), (5, 130, 24, True), (3, 64, 16, False),
+                                           (5, 32, 24, True), (1, 20, 32, False)])  # the last two: gradients too
 def test_linear_composition_against_reference(tmp_path, B, In, Out, relu):
     """Model::Linear's chain (MatMul(W, x) -> Add(bias) [-> ReLU], src/Model.cu:87-103) run by NeuZephyr,
     against nzb_linear_forward / nzb_linear_backward."""
@@ -175,7 +200,10 @@ def test_linear_composition_against_reference(tmp_path, B, In, Out, relu):
         y_t = np.maximum(y_t, 0)
     dym = (dy * (y_ref > 0) if relu else dy).astype(np.float64)
     truths = {"y": y_t, "dx": dym @ w64, "dw": dym.T @ x64}
-    for name, ours, ref in (("y", y, y_ref), ("dx", dx, dx_ref), ("dw", dw, dw_ref)):
+    assert emax(dx, truths["dx"]) <= 1e-2 and emax(dw, truths["dw"]) <= 1e-2
+    # MatMul(W {Out,In}, x {In,1}): the backward transposes W (Out x In) and x (In x 1)
+    grads_defined = ref_transpose_ok(Out, In) and ref_transpose_ok(In, 1)
+    for name, ours, ref in (("y", y, y_ref),) + ((("dx", dx, dx_ref), ("dw", dw, dw_ref)) if grads_defined else ()):
         e_o, e_r = emax(ours, truths[name]), emax(ref, truths[name])
         assert e_o <= 1e-2 and e_o <= 2 * e_r + 1e-6, (name, e_o, e_r)
         assert emax(ours, ref) <= 1e-4, (name, emax(ours, ref))
