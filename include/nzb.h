@@ -100,7 +100,7 @@ NZB_API int nzb_selftest_wait_timeout(long long limit_cycles, int* roles_left_de
 
 /* GEMM -------------------------------------------------------------------- */
 
-/* Scratch bytes nzb_gemm needs for this descriptor (fp16 operand copies). */
+/* Scratch bytes nzb_gemm needs for this descriptor (fp16 operand copies + 16 KiB of staging counters). */
 NZB_API int nzb_gemm_workspace_bytes(const nzb_gemm_desc* desc, size_t* bytes_out);
 
 /*
@@ -114,6 +114,16 @@ NZB_API int nzb_gemm_workspace_bytes(const nzb_gemm_desc* desc, size_t* bytes_ou
  */
 NZB_API int nzb_gemm(const nzb_gemm_desc* desc, const float* A, const float* B, float* C, const float* bias,
                      void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Number of kernels nzb_gemm launches for this descriptor and these operand addresses on the current
+ * device: 1 when the GEMM kernel stages its own operands (one matrix product of at least 148 output
+ * tiles of 256 x 256, rows that are multiples of four floats, 16-byte aligned operands; converter warps
+ * inside the CTA-pair kernel round the fp32 operands to fp16 panel by panel while its tensor-core warps
+ * consume finished panels), 3 otherwise (two staging kernels and the GEMM). The environment variable
+ * NZB_FUSED_STAGING=0, read once per process, forces the three-kernel form.
+ */
+NZB_API int nzb_gemm_kernel_launches(const nzb_gemm_desc* desc, const float* A, const float* B, int* launches_out);
 
 /*
  * Same seam as nz::data::iTensorCoreGEMM(float* A, float* B, float* C, const Dimension&

@@ -12,7 +12,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 
 EXPORTS = [
     "nzb_version", "nzb_last_error_string", "nzb_device_status", "nzb_device_status_reset", "nzb_selftest_wait_timeout",
-    "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_gemm_f16", "nzb_gemm_static", "nzb_gemm_static_status", "nzb_gemm_static_status_reset", "nzb_gemm_host_workspace_bytes", "nzb_gemm_host", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
+    "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_gemm_kernel_launches", "nzb_gemm_f16", "nzb_gemm_static", "nzb_gemm_static_status", "nzb_gemm_static_status_reset", "nzb_gemm_host_workspace_bytes", "nzb_gemm_host", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
     "nzb_gemm_backward", "nzb_cast_f32_f16",
     "nzb_linear_workspace_bytes", "nzb_linear_forward", "nzb_linear_backward",
     "nzb_conv2d_workspace_bytes", "nzb_conv2d_forward", "nzb_conv2d_backward_data", "nzb_conv2d_backward_weight",
@@ -70,6 +70,7 @@ def lib():
         vp, sz = ctypes.c_void_p, ctypes.c_size_t
         L.nzb_gemm_workspace_bytes.argtypes = [ctypes.POINTER(GemmDesc), ctypes.POINTER(sz)]
         L.nzb_gemm.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp, sz, vp]
+        L.nzb_gemm_kernel_launches.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, ctypes.POINTER(ctypes.c_int)]
         L.nzb_gemm_static.argtypes = [ctypes.POINTER(GemmDesc), vp, vp, vp, vp, vp]
         L.nzb_gemm_static_status.argtypes = [ctypes.POINTER(ctypes.c_int), vp]
         L.nzb_gemm_static_status_reset.argtypes = [vp]

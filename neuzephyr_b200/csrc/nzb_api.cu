@@ -271,6 +271,20 @@ int nzb_gemm_workspace_bytes(const nzb_gemm_desc* desc, size_t* bytes_out) {
     return NZB_OK;
 }
 
+int nzb_gemm_kernel_launches(const nzb_gemm_desc* desc, const float* A, const float* B, int* launches_out) {
+    if (!launches_out) return fail(NZB_ERR_BAD_ARG, "launches_out is null");
+    Plan pl;
+    int rc = make_plan(desc, &pl);
+    if (rc != NZB_OK) return rc;
+    DeviceState* ds;
+    rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B)) & 15) == 0;
+    const bool fused = pl.fusable && aligned && fused_staging_enabled() && gemm_uses_pair_kernel(pl.g, ds->sm_count);
+    *launches_out = (desc->M == 0 || desc->N == 0) ? 0 : (fused ? 1 : 3);
+    return NZB_OK;
+}
+
 int nzb_gemm(const nzb_gemm_desc* desc, const float* A, const float* B, float* C, const float* bias, void* workspace,
              size_t workspace_bytes, void* stream) {
     return run_gemm(desc, A, B, C, bias, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));

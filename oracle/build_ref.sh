@@ -8,7 +8,8 @@
 # brace construction (src/Dimension.cu:129, src/Tensor.cu:89). Those two edits are applied
 # to a scratch copy under a temporary directory; only binaries are written to _ref/.
 set -euo pipefail
-REF="${1:-/root/reference}"
+REF="${1:-${NEUZEPHYR_SRC:-}}"
+[ -n "$REF" ] || { echo "usage: build_ref.sh /path/to/NeuZephyr (or set NEUZEPHYR_SRC)" >&2; exit 3; }
 HERE="$(cd "$(dirname "$0")" && pwd)"
 OUT="$HERE/_ref"
 NVCC="${NVCC:-/usr/local/cuda/bin/nvcc}"

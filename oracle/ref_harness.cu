@@ -366,16 +366,17 @@ int main(int argc, char** argv) {
         };
         for (int i = 0; i < warmup; i++) step();
         cudaDeviceSynchronize();
-        // every step timed on its own (the library allocates and frees about 1 GB per call from the
-        // stream-ordered pool, and an occasional pool re-map costs hundreds of milliseconds): the
-        // median is the steady-state figure, the list shows the outliers
+        // every step timed on its own, closed by the library's own completion wait (Tensor::sync inside
+        // step(), or the blocking hostData copy): no device-wide synchronisation inside the loop, which
+        // would make the stream-ordered pool give its memory back and re-map about 1 GB on the next call.
+        // The median is the steady-state figure, the list shows the outliers.
         std::vector<double> each(steps);
         for (int i = 0; i < steps; i++) {
             const double t0 = now_ms();
             step();
-            cudaDeviceSynchronize();
             each[i] = now_ms() - t0;
         }
+        cudaDeviceSynchronize();
         std::vector<double> sorted = each;
         std::sort(sorted.begin(), sorted.end());
         const double ms = sorted[sorted.size() / 2];

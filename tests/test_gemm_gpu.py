@@ -320,3 +320,31 @@ def test_gemm_host_pipeline_matches_device_call(nz, M, N, K, tB):
     assert np.array_equal(hC1.numpy(), hC2.numpy())
     check_status(nz)
     assert emax(hC2.numpy(), O.gemm_f64(A, B, True)) <= TOL_ROUNDED
+
+
+@pytest.mark.parametrize("tA,tB", [(False, False), (True, False), (False, True), (True, True)])
+def test_gemm_in_kernel_staging_odd_shapes(nz, tA, tB):
+    """One matrix product with 148 or more 256x256 tiles takes the CTA-pair kernel with its own converter
+    warps (fp32 -> fp16 staging inside the GEMM kernel, panel by panel behind counters): extents that are
+    not multiples of the tile or chunk sizes, every storage combination, a second call on the same
+    workspace (the counters are cleared per call), and the fused epilogue."""
+    from neuzephyr_b200 import _capi as C
+    M, N, K = 3100, 3332, 1000
+    rng = np.random.default_rng(77)
+    A = rng.uniform(-1, 1, (M, K)).astype(np.float32)
+    B = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    As = np.ascontiguousarray(A.T) if tA else A
+    Bs = np.ascontiguousarray(B.T) if tB else B
+    Ad, Bd = dev(As), dev(Bs)
+    bias = rng.uniform(-1, 1, N).astype(np.float32)
+    out = None
+    for _ in range(2):
+        out = nz.gemm(Ad, Bd, transA=tA, transB=tB, bias=dev(bias), bias_mode=C.BIAS_ROW, relu=True).cpu().numpy()
+    check_status(nz)
+    rows = np.unique(np.concatenate([[0, 255, 256, M - 1], rng.integers(0, M, 40)]))
+    cols = np.unique(np.concatenate([[0, 255, 256, N - 1], rng.integers(0, N, 40)]))
+    ref_r = np.maximum(O.gemm_f64_rows(A, B, rows, True) + bias[None, :], 0)
+    ref_c = np.maximum(O.gemm_f64_rows(np.ascontiguousarray(B.T), np.ascontiguousarray(A.T), cols, True)
+                       + bias[cols][:, None], 0)
+    assert emax(out[rows], ref_r) <= TOL_ROUNDED
+    assert emax(out[:, cols].T, ref_c) <= TOL_ROUNDED
