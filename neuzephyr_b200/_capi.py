@@ -13,7 +13,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 EXPORTS = [
     "nzb_version", "nzb_last_error_string", "nzb_device_status", "nzb_device_status_reset", "nzb_selftest_wait_timeout",
     "nzb_gemm_workspace_bytes", "nzb_gemm", "nzb_gemm_kernel_launches", "nzb_gemm_f16", "nzb_gemm_static", "nzb_gemm_static_status", "nzb_gemm_static_status_reset", "nzb_gemm_host_workspace_bytes", "nzb_gemm_host", "nzb_tensorcore_gemm_workspace_bytes", "nzb_tensorcore_gemm",
-    "nzb_gemm_backward", "nzb_cast_f32_f16",
+    "nzb_gemm_backward", "nzb_matmul_f32_workspace_bytes", "nzb_matmul_f32", "nzb_cast_f32_f16",
     "nzb_linear_workspace_bytes", "nzb_linear_forward", "nzb_linear_backward",
     "nzb_conv2d_workspace_bytes", "nzb_conv2d_forward", "nzb_conv2d_backward_data", "nzb_conv2d_backward_weight",
     "nzb_conv2d_backward_bias", "nzb_conv2d_backward_workspace_bytes", "nzb_conv2d_backward",
@@ -80,6 +80,8 @@ def lib():
         L.nzb_tensorcore_gemm_workspace_bytes.argtypes = [i64p, i64p, i64p, ctypes.POINTER(sz)]
         L.nzb_tensorcore_gemm.argtypes = [vp, vp, vp, i64p, i64p, i64p, vp, sz, vp]
         L.nzb_gemm_backward.argtypes = [vp, vp, vp, i64p, i64p, i64p, vp, sz, vp]
+        L.nzb_matmul_f32_workspace_bytes.argtypes = [i64p, i64p, i64p, ctypes.POINTER(sz)]
+        L.nzb_matmul_f32.argtypes = [vp, vp, vp, i64p, i64p, i64p, vp, sz, vp]
         L.nzb_cast_f32_f16.argtypes = [vp, vp, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
                                        ctypes.c_int, vp]
         L.nzb_device_status.argtypes = [ctypes.POINTER(ctypes.c_int)]

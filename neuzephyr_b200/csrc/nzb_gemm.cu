@@ -42,6 +42,7 @@ struct GemmParams {
     int32_t a_mn, b_mn;   // operand copy is stored [k][m] / [k][n] (contiguous along the output dimension)
     int32_t trans_out;    // the kernel computes C^T (operands swapped by the host): element (r, c) goes to C[c][r]
     int64_t total_tiles;
+    const float* alpha;   // device scalar multiplied into the product before accumulate / bias (null: 1)
     int* status;
 };
 
@@ -136,6 +137,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
                                                   float* Cb, int32_t row0, int32_t col_tile, bool first_split = true) {
     using namespace ptx;
     constexpr int BN = Cfg::BN;
+    const float al = p.alpha ? __ldg(p.alpha) : 1.0f;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += Cfg::CHUNK) {
         const uint32_t taddr = tmem_acc + c0;
@@ -171,6 +173,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
                 const int32_t gr = row0 + r;
                 if (gr < p.M && gc < p.N) {  // N % 4 == 0 on this path: the whole float4 is in range
                     float4 x = *reinterpret_cast<const float4*>(stage + r * Cfg::EPI_STRIDE + cl);
+                    x.x *= al; x.y *= al; x.z *= al; x.w *= al;
                     float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
                     if (p.accumulate) {
                         const float4 o = *reinterpret_cast<const float4*>(cp);
@@ -203,7 +206,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, uint32_t 
                 const int r = rr + lane / Cfg::CHUNK;
                 const int32_t gr = row0 + r;
                 if (gr < p.M && gc < p.N) {
-                    float x = stage[r * Cfg::EPI_STRIDE + cl];
+                    float x = stage[r * Cfg::EPI_STRIDE + cl] * al;
                     float* cp = Cb + static_cast<int64_t>(gr) * p.ldc + gc;
                     if (p.splits > 1) {
                         // partial sum of one k slice; C was zeroed or holds the addend. The slice that
@@ -247,6 +250,7 @@ __device__ __forceinline__ void drain_accumulator_transposed(const GemmParams& p
     const bool with_bias = p.bias_mode != NZB_BIAS_NONE && (p.splits == 1 || first_split);
     const float floor_v = (p.relu && p.splits == 1) ? 0.f : -INFINITY;
     const float bias_row = (with_bias && p.bias_mode == NZB_BIAS_ROW && row_ok) ? p.bias[gr] : 0.f;
+    const float al = p.alpha ? __ldg(p.alpha) : 1.0f;
 #pragma unroll 1
     for (int c0 = 0; c0 < BN; c0 += G) {
         const int32_t gc0 = col_tile + c0;  // caller's first row of this group
@@ -277,14 +281,14 @@ __device__ __forceinline__ void drain_accumulator_transposed(const GemmParams& p
         if (p.splits > 1) {
 #pragma unroll
             for (int j = 0; j < G; j++)
-                if (whole || gc0 + j < p.N) atomicAdd(cg + static_cast<int64_t>(j) * p.ldc, __uint_as_float(v[j]) + add[j]);
+                if (whole || gc0 + j < p.N) atomicAdd(cg + static_cast<int64_t>(j) * p.ldc, __uint_as_float(v[j]) * al + add[j]);
         } else if (whole) {
 #pragma unroll
-            for (int j = 0; j < G; j++) cg[static_cast<int64_t>(j) * p.ldc] = fmaxf(__uint_as_float(v[j]) + add[j], floor_v);
+            for (int j = 0; j < G; j++) cg[static_cast<int64_t>(j) * p.ldc] = fmaxf(__uint_as_float(v[j]) * al + add[j], floor_v);
         } else {
 #pragma unroll
             for (int j = 0; j < G; j++)
-                if (gc0 + j < p.N) cg[static_cast<int64_t>(j) * p.ldc] = fmaxf(__uint_as_float(v[j]) + add[j], floor_v);
+                if (gc0 + j < p.N) cg[static_cast<int64_t>(j) * p.ldc] = fmaxf(__uint_as_float(v[j]) * al + add[j], floor_v);
         }
     }
 }
@@ -1011,6 +1015,7 @@ int launch_gemm_on(const GemmLaunch& g_in, const DeviceState& dstate, cudaStream
     p.k_blocks = (int32_t)((g.K + 63) / 64);
     p.last_ksteps = (int32_t)((g.K - (int64_t)(p.k_blocks - 1) * 64 + 15) / 16);
     p.status = ds->status_dev;
+    p.alpha = g.alpha;
     bool v4 = (g.N % 4 == 0) && (g.ldc % 4 == 0) && ((reinterpret_cast<uintptr_t>(g.C) & 15) == 0) &&
               (g.c_stride[0] % 4 == 0) && (g.c_stride[1] % 4 == 0);
     if (p.bias_mode == NZB_BIAS_ROW) v4 = v4 && ((reinterpret_cast<uintptr_t>(g.bias) & 15) == 0);

@@ -85,6 +85,8 @@ struct GemmLaunch {
     const float* B32;
     int64_t lda32, ldb32;
     unsigned* fuse_sync;
+    // device scalar multiplied into every product before accumulate / bias (null: none)
+    const float* alpha;
 };
 // Counters of the in-kernel staging: next chunk, then one finished-chunk count per 256-wide panel.
 constexpr size_t kFuseSyncBytes = 16384;

@@ -70,6 +70,9 @@ public:
     // (src/Tensor.cu:506-548); compares gradients too when both tensors require them
     bool operator==(const Tensor& other) const;
     bool operator!=(const Tensor& other) const { return !(*this == other); }
+    // batched matrix product at fp32 accuracy with N / C broadcast (src/Tensor.cu:343-350): on the tensor
+    // cores through a two-fp16 split of each operand, see tensorGeneralMatrixMul
+    Tensor operator*(const Tensor& other) const;
 
     friend std::ostream& operator<<(std::ostream& os, const Tensor& t);
 

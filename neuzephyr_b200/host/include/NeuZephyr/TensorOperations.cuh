@@ -14,6 +14,13 @@ void iTensorCoreGEMM(float* A, float* B, float* C, const Dimension& shapeA, cons
 // C += A x B, summed over broadcast batch dimensions of C (:1026-1031).
 void iGEMMBackward(float* A, float* B, float* C, const Dimension& shapeA, const Dimension& shapeB,
                    const Dimension& shapeC);
+// C = A x B at fp32 accuracy: the seam of iGeneralMatrixMul (src/TensorOperations.cu:104-110), taking the
+// operands' shapes instead of precomputed offset lists; overwrite, N / C of extent 1 broadcast.
+void iGeneralMatrixMul(float* A, float* B, float* C, const Dimension& shapeA, const Dimension& shapeB,
+                       const Dimension& shapeC);
+// out = lhs x rhs (include/NeuZephyr/TensorOperations.cuh:998-1019); throws std::invalid_argument for
+// shapes that are not broadcast compatible, as the reference does.
+void tensorGeneralMatrixMul(Tensor& out, const Tensor& lhs, const Tensor& rhs);
 // General form with transposed operands and fused epilogue (no reference counterpart; used by the
 // fused nodes): C (op)= op(A) op(B) for single matrices.
 void iGemm(const float* A, const float* B, float* C, size_t M, size_t N, size_t K, bool transA, bool transB,

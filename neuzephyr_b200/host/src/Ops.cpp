@@ -3,6 +3,8 @@
 
 #include <nzb.h>
 
+#include <algorithm>
+
 namespace nz::data {
 
 using SM = cuStrm::StreamManager<float>;
@@ -31,6 +33,32 @@ void iTensorCoreGEMM(float* A, float* B, float* C, const Dimension& sa, const Di
 }
 void iGEMMBackward(float* A, float* B, float* C, const Dimension& sa, const Dimension& sb, const Dimension& sc) {
     gemm4(true, A, B, C, sa, sb, sc);
+}
+
+void iGeneralMatrixMul(float* A, float* B, float* C, const Dimension& sa, const Dimension& sb, const Dimension& sc) {
+    int64_t a[4], b[4], c[4];
+    shape4(sa, a); shape4(sb, b); shape4(sc, c);
+    size_t bytes = 0;
+    NZB_CHECK(nzb_matmul_f32_workspace_bytes(a, b, c, &bytes));
+    SM::Instance().run({C}, {A, B}, [&](cudaStream_t s) {
+        void* ws = SM::Instance().scratch(bytes, s);
+        const int rc = nzb_matmul_f32(A, B, C, a, b, c, ws, bytes, s);
+        SM::Instance().releaseScratch(ws, s);
+        NZB_CHECK(rc);
+    });
+}
+void tensorGeneralMatrixMul(Tensor& out, const Tensor& lhs, const Tensor& rhs) {
+    if (!lhs.shape().isBroadcastCompatible(rhs.shape()) || lhs.shape().W() != rhs.shape().H())
+        throw std::invalid_argument("Shapes are not broadcast compatible.");
+    iGeneralMatrixMul(lhs.data(), rhs.data(), out.data(), lhs.shape(), rhs.shape(), out.shape());
+}
+
+Tensor Tensor::operator*(const Tensor& other) const {
+    Tensor result(Dimension(std::max(shape_.N(), other.shape_.N()), std::max(shape_.C(), other.shape_.C()), shape_.H(),
+                            other.shape_.W()),
+                  requires_grad_ || other.requires_grad_);
+    tensorGeneralMatrixMul(result, *this, other);
+    return result;
 }
 
 void iGemm(const float* A, const float* B, float* C, size_t M, size_t N, size_t K, bool transA, bool transB,

@@ -129,6 +129,21 @@ def tensorcore_gemm(A, B, out=None):
     return out
 
 
+def matmul_f32(A, B, out=None):
+    """4-D batched product with N/C broadcast at fp32 accuracy (the Tensor::operator* seam, nzb_matmul_f32)."""
+    _check_f32_cuda(A, B, out)
+    sc = (max(A.shape[0], B.shape[0]), max(A.shape[1], B.shape[1]), A.shape[2], B.shape[3])
+    if out is None:
+        out = torch.empty(sc, dtype=torch.float32, device=A.device)
+    n = ctypes.c_size_t(0)
+    C.check(C.lib().nzb_matmul_f32_workspace_bytes(C.shape4(A.shape), C.shape4(B.shape), C.shape4(out.shape),
+                                                   ctypes.byref(n)))
+    ws = _workspace(n.value, A.device)
+    C.check(C.lib().nzb_matmul_f32(_ptr(A), _ptr(B), _ptr(out), C.shape4(A.shape), C.shape4(B.shape),
+                                   C.shape4(out.shape), _ptr(ws), ws.numel(), _stream()))
+    return out
+
+
 def gemm_backward(A, B, out):
     """out += A @ B reduced over broadcast batch dims of out (the iGEMMBackward seam)."""
     _check_f32_cuda(A, B, out)

