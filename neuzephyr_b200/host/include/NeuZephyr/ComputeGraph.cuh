@@ -1,8 +1,10 @@
 // nz::graph::ComputeGraph: node container, Kahn topological sort, forward / backward /
-// update / zeroGrad loops (mirrors include/NeuZephyr/ComputeGraph.cuh,
-// src/ComputeGraph.cu:258-296, 405-438, 541-547). Serialisation is not part of this path.
+// update / zeroGrad loops, save / load (mirrors include/NeuZephyr/ComputeGraph.cuh,
+// src/ComputeGraph.cu:258-296, 405-438, 541-547, 553-811).
 #pragma once
 #include <functional>
+#include <memory>
+#include <string>
 #include <vector>
 
 #include "Nodes.cuh"
@@ -42,6 +44,23 @@ public:
     // node that is added, or at the end of the list.
     void addPhantomSteps(int n) { pending_ticks_ += n; }
     float getLoss() const;
+    // Checkpoint of the whole graph in the reference's text layout (src/ComputeGraph.cu:553-639): a JSON
+    // array with one object per node in topological order -- "type", "name", "pre", "post", "shape",
+    // "data", "requires_grad", "grad", one key per line. Three things differ from the reference's files:
+    // "shape" holds all four extents (the reference writes the first two and reloads every tensor as
+    // {N, C, 1, 1}-sized, :598-600, :752-753), numbers are printed with nine significant digits so that
+    // fp32 values survive the round trip, and nodes whose constructors take more than their inputs carry
+    // them in "attr". With an optimizer, its per-node state ("opt_state") and a trailing
+    // {"type": "Optimizer", ...} object with its per-call counter are written too, so that training
+    // resumes with the same Adam moments and time steps.
+    void save(const std::string& path, const opt::Optimizer* optimizer = nullptr);
+    // Rebuilds a graph from such a file into this (empty) graph: nodes are created by type from their
+    // saved inputs and attributes, data and gradients injected, optimizer state restored when both the
+    // file and the call provide an optimizer. Files written by the reference itself load as far as they
+    // go: their two-extent "shape" is read as {N, C, count / (N*C), 1}. The graph owns the nodes it loads.
+    void load(const std::string& path, opt::Optimizer* optimizer = nullptr);
+    // node by its saved / generated name ("<type>_<index in topological order>")
+    nodes::Node* operator[](const std::string& name) const;
     const std::vector<nodes::Node*>& getNodes() const { return nodes_; }
     const std::vector<nodes::io::OutputNode*>& getOutputs() const { return outputs_; }
 
@@ -49,6 +68,8 @@ private:
     std::vector<nodes::Node*> nodes_, sorted_nodes_;
     std::vector<nodes::io::InputNode*> inputs_;
     std::vector<nodes::io::OutputNode*> outputs_;
+    std::vector<std::unique_ptr<nodes::Node>> owned_;  // nodes created by load()
+    std::vector<std::string> names_;                  // per entry of sorted_nodes_ after save / load
     std::vector<int> ticks_before_;  // per entry of nodes_: phantom optimizer ticks that precede it
     int pending_ticks_ = 0;
     bool sorted_ = false;

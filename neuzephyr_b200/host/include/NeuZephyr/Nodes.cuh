@@ -23,6 +23,9 @@ public:
     virtual ~Node() = default;
     virtual void forward() = 0;
     virtual void backward() = 0;
+    // constructor arguments beyond the input nodes (kernel sizes, strides, flags ...), in constructor
+    // order: what ComputeGraph::save writes so that ComputeGraph::load can rebuild the node
+    virtual std::vector<size_t> attributes() const { return {}; }
     void dataInject(Tensor::value_type* data, bool grad = false) const { output->dataInject(data, grad); }
     template <typename It>
     void dataInject(It begin, It end, bool grad = false) const { output->dataInject(begin, end, grad); }
@@ -83,6 +86,10 @@ public:
     ReshapeNode(Node* input, const Tensor::shape_type& shape);
     void forward() override;
     void backward() override;
+    std::vector<size_t> attributes() const override {
+        const auto s = output->shape();
+        return {s[0], s[1], s[2], s[3]};
+    }
 };
 
 class ExpandNode : public Node {
@@ -90,6 +97,7 @@ public:
     ExpandNode(Node* input, Tensor::size_type newBatch);
     void forward() override;
     void backward() override;
+    std::vector<size_t> attributes() const override { return {output->shape().N()}; }
 };
 
 class Img2ColNode : public Node {
@@ -98,6 +106,7 @@ public:
                 Tensor::size_type stride, Tensor::size_type padding);
     void forward() override;
     void backward() override;
+    std::vector<size_t> attributes() const override { return {kh_, kw_, stride_, pad_}; }
 
 private:
     Tensor::size_type kh_, kw_, stride_, pad_, ho_, wo_;
@@ -108,6 +117,7 @@ public:
     Col2ImgNode(Node* input, Tensor::size_type outputHeight, Tensor::size_type outputWidth);
     void forward() override;
     void backward() override;
+    std::vector<size_t> attributes() const override { return {ho_, wo_}; }
 
 private:
     Tensor::size_type ho_, wo_, cout_;
@@ -119,6 +129,7 @@ public:
                        Tensor::size_type padding);
     void forward() override;
     void backward() override;
+    std::vector<size_t> attributes() const override { return {pool_, stride_, pad_}; }
 
 private:
     Tensor::size_type pool_, stride_, pad_;
@@ -142,6 +153,7 @@ public:
                Tensor::size_type stride, Tensor::size_type padding, bool relu);
     void forward() override;
     void backward() override;
+    std::vector<size_t> attributes() const override { return {kh_, kw_, stride_, pad_, relu_ ? 1u : 0u}; }
 
 private:
     Tensor::size_type kh_, kw_, stride_, pad_;
@@ -156,6 +168,7 @@ public:
     LinearNode(Node* x, Node* weight, Node* bias, bool relu);
     void forward() override;
     void backward() override;
+    std::vector<size_t> attributes() const override { return {relu_ ? 1u : 0u}; }
 
 private:
     bool relu_;

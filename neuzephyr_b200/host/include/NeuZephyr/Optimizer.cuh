@@ -4,6 +4,7 @@
 #pragma once
 #include <memory>
 #include <unordered_map>
+#include <vector>
 
 #include "Nodes.cuh"
 
@@ -16,6 +17,13 @@ public:
     // `n` step() calls the reference would have made on nodes this graph does not step
     // (activations, nodes folded into a fused node): only per-call state advances.
     virtual void skip(int n) { (void)n; }
+    // Checkpointing (ComputeGraph::save / load): a name, the per-call counter, and per node the state
+    // vectors the optimizer keeps (empty when it keeps none for that node).
+    virtual const char* name() const { return "Optimizer"; }
+    virtual long counter() const { return 0; }
+    virtual void setCounter(long) {}
+    virtual std::vector<std::vector<float>> exportState(nodes::Node*) const { return {}; }
+    virtual void importState(nodes::Node*, const std::vector<std::vector<float>>&) {}
 
 protected:
     float learning_rate = 0.f;
@@ -25,6 +33,7 @@ class SGD : public Optimizer {
 public:
     explicit SGD(float learning_rate);
     void step(nodes::Node* input) override;
+    const char* name() const override { return "SGD"; }
 };
 
 class Adam : public Optimizer {
@@ -32,6 +41,12 @@ public:
     Adam(float learning_rate, float beta1, float beta2);
     void step(nodes::Node* input) override;
     void skip(int n) override { it_ += n; }
+    const char* name() const override { return "Adam"; }
+    long counter() const override { return it_; }
+    void setCounter(long it) override { it_ = (int)it; }
+    // {first moments, second moments} of a node, in host memory
+    std::vector<std::vector<float>> exportState(nodes::Node* node) const override;
+    void importState(nodes::Node* node, const std::vector<std::vector<float>>& state) override;
     // false restores "one time step per optimisation step" semantics: call nextIteration() once
     // per Model::update and every parameter uses the same t
     bool perCallTimeStep = true;

@@ -6,7 +6,12 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
 #include <queue>
+#include <string>
 #include <unordered_map>
 
 #include <nzb.h>
@@ -81,6 +86,221 @@ void ComputeGraph::update(opt::Optimizer* optimizer, const std::function<void()>
     }
     if (pending_ticks_) optimizer->skip(pending_ticks_);
 }
+// ---- save / load (src/ComputeGraph.cu:553-811) -------------------------------------------------
+namespace {
+void write_floats(FILE* f, const std::vector<float>& v) {
+    fputc('[', f);
+    for (size_t i = 0; i < v.size(); i++) fprintf(f, i ? ", %.9g" : "%.9g", (double)v[i]);
+    fputc(']', f);
+}
+// text between the first '[' and the matching last ']' after `key` on this line
+bool bracket_body(const std::string& line, const char* key, std::string* body) {
+    const size_t k = line.find(key);
+    if (k == std::string::npos) return false;
+    const size_t a = line.find('[', k), b = line.rfind(']');
+    if (a == std::string::npos || b == std::string::npos || b < a) return false;
+    *body = line.substr(a + 1, b - a - 1);
+    return true;
+}
+template <class T>
+std::vector<T> parse_numbers(const std::string& body) {
+    std::vector<T> out;
+    const char* p = body.c_str();
+    while (*p) {
+        while (*p == ' ' || *p == ',' || *p == '\t') p++;
+        if (!*p) break;
+        char* end = nullptr;
+        const double v = strtod(p, &end);
+        if (end == p) break;
+        out.push_back((T)v);
+        p = end;
+    }
+    return out;
+}
+std::string quoted_value(const std::string& line, const char* key) {
+    const size_t k = line.find(key);
+    if (k == std::string::npos) return "";
+    const size_t a = line.find('"', k + strlen(key)), b = a == std::string::npos ? a : line.find('"', a + 1);
+    return b == std::string::npos ? "" : line.substr(a + 1, b - a - 1);
+}
+}  // namespace
+
+void ComputeGraph::save(const std::string& path, const opt::Optimizer* optimizer) {
+    if (path.empty()) throw std::runtime_error("Path cannot be empty");
+    if (!sorted_) topologicalSort();
+    if (sorted_nodes_.empty()) throw std::runtime_error("Graph not sorted");
+    FILE* f = fopen(path.c_str(), "w");
+    if (!f) throw std::runtime_error("Failed to open file for writing");
+    auto index_of = [&](Node* n) {
+        return (long)(std::find(sorted_nodes_.begin(), sorted_nodes_.end(), n) - sorted_nodes_.begin());
+    };
+    names_.resize(sorted_nodes_.size());
+    fprintf(f, "[\n");
+    for (size_t i = 0; i < sorted_nodes_.size(); i++) {
+        Node* n = sorted_nodes_[i];
+        if (names_[i].empty()) names_[i] = n->type + "_" + std::to_string(i);
+        fprintf(f, "  {\n    \"type\": \"%s\",\n    \"name\": \"%s\",\n    \"pre\": [", n->type.c_str(), names_[i].c_str());
+        for (size_t j = 0; j < n->inputs.size(); j++) fprintf(f, j ? ", %ld" : "%ld", index_of(n->inputs[j]));
+        fprintf(f, "],\n    \"post\": [");
+        bool first = true;
+        for (Node* u : sorted_nodes_)
+            if (std::find(u->inputs.begin(), u->inputs.end(), n) != u->inputs.end()) {
+                fprintf(f, first ? "%ld" : ", %ld", index_of(u));
+                first = false;
+            }
+        const auto shape = n->output->shape();
+        fprintf(f, "],\n    \"shape\": [%zu, %zu, %zu, %zu],\n", shape[0], shape[1], shape[2], shape[3]);
+        const size_t pos = (size_t)(std::find(nodes_.begin(), nodes_.end(), n) - nodes_.begin());
+        fprintf(f, "    \"order\": %zu,\n    \"ticks\": %d,\n    \"attr\": [", pos, pos < ticks_before_.size() ? ticks_before_[pos] : 0);
+        const auto attr = n->attributes();
+        for (size_t j = 0; j < attr.size(); j++) fprintf(f, j ? ", %zu" : "%zu", attr[j]);
+        fprintf(f, "],\n    \"data\": ");
+        write_floats(f, n->output->hostData());
+        fprintf(f, ",\n    \"requires_grad\": %s,\n    \"grad\": ", n->output->requiresGrad() ? "true" : "false");
+        write_floats(f, n->output->requiresGrad() ? n->output->hostGrad() : std::vector<float>());
+        if (optimizer) {
+            const auto state = optimizer->exportState(n);
+            for (size_t k = 0; k < state.size(); k++) {
+                fprintf(f, ",\n    \"opt_state_%zu\": ", k);
+                write_floats(f, state[k]);
+            }
+        }
+        fprintf(f, "\n  },\n");
+    }
+    // trailer: what belongs to the graph as a whole
+    fprintf(f, "  {\n    \"type\": \"Optimizer\",\n    \"name\": \"%s\",\n    \"counter\": %ld,\n    \"pending_ticks\": %d\n  }\n]\n",
+            optimizer ? optimizer->name() : "none", optimizer ? optimizer->counter() : 0L, pending_ticks_);
+    if (fclose(f) != 0) throw std::runtime_error("Failed to write " + path);
+}
+
+void ComputeGraph::load(const std::string& path, opt::Optimizer* optimizer) {
+    if (path.empty()) throw std::runtime_error("Path cannot be empty");
+    if (!nodes_.empty()) throw std::runtime_error("Graph already loaded");
+    std::ifstream in(path);
+    if (!in.is_open()) throw std::runtime_error("Failed to open file for reading");
+    struct Rec {
+        std::string type, name;
+        std::vector<long> pre, shape, attr;
+        std::vector<float> data, grad;
+        std::vector<std::vector<float>> opt;
+        bool requires_grad = false;
+        long order = -1, ticks = 0, counter = 0, pending = 0;
+    };
+    std::vector<Rec> recs;
+    Rec cur;
+    bool open = false;
+    std::string line, body;
+    while (std::getline(in, line)) {
+        if (!open) {
+            if (line.find('{') != std::string::npos) {
+                open = true;
+                cur = Rec();
+            }
+            continue;
+        }
+        if (line.find("\"type\":") != std::string::npos) cur.type = quoted_value(line, "\"type\":");
+        else if (line.find("\"name\":") != std::string::npos) cur.name = quoted_value(line, "\"name\":");
+        else if (bracket_body(line, "\"pre\":", &body)) cur.pre = parse_numbers<long>(body);
+        else if (line.find("\"post\":") != std::string::npos) {}
+        else if (bracket_body(line, "\"shape\":", &body)) cur.shape = parse_numbers<long>(body);
+        else if (bracket_body(line, "\"attr\":", &body)) cur.attr = parse_numbers<long>(body);
+        else if (bracket_body(line, "\"data\":", &body)) cur.data = parse_numbers<float>(body);
+        else if (line.find("\"requires_grad\":") != std::string::npos) cur.requires_grad = line.find("true") != std::string::npos;
+        else if (bracket_body(line, "\"grad\":", &body)) cur.grad = parse_numbers<float>(body);
+        else if (line.find("\"opt_state_") != std::string::npos && bracket_body(line, "\"opt_state_", &body)) cur.opt.push_back(parse_numbers<float>(body));
+        else if (line.find("\"order\":") != std::string::npos) cur.order = atol(line.c_str() + line.find(':') + 1);
+        else if (line.find("\"ticks\":") != std::string::npos) cur.ticks = atol(line.c_str() + line.find(':') + 1);
+        else if (line.find("\"counter\":") != std::string::npos) cur.counter = atol(line.c_str() + line.find(':') + 1);
+        else if (line.find("\"pending_ticks\":") != std::string::npos) cur.pending = atol(line.c_str() + line.find(':') + 1);
+        else if (line.find('}') != std::string::npos) {
+            open = false;
+            recs.push_back(cur);
+        }
+    }
+    using data::Dimension;
+    namespace calc = nodes::calc;
+    namespace io = nodes::io;
+    std::vector<Node*> created;
+    std::vector<std::pair<long, Node*>> order;
+    std::vector<int> ticks;
+    for (const Rec& r : recs) {
+        if (r.type == "Optimizer") {
+            if (optimizer && r.name == optimizer->name()) optimizer->setCounter(r.counter);
+            pending_ticks_ = (int)r.pending;
+            continue;
+        }
+        auto in_node = [&](size_t k) -> Node* {
+            if (k >= r.pre.size() || r.pre[k] < 0 || (size_t)r.pre[k] >= created.size())
+                throw std::runtime_error("node " + r.name + " refers to an input that is not defined before it");
+            return created[(size_t)r.pre[k]];
+        };
+        auto attr = [&](size_t k) -> size_t {
+            if (k >= r.attr.size()) throw std::runtime_error("node " + r.name + " (" + r.type + ") lacks a constructor attribute");
+            return (size_t)r.attr[k];
+        };
+        Dimension shape(1, 1, 1, 1);
+        if (r.shape.size() == 4) shape = Dimension(r.shape[0], r.shape[1], r.shape[2], r.shape[3]);
+        else if (r.shape.size() == 2) {
+            // a file written by the reference: only N and C were kept; the rest is the element count
+            const size_t nc = (size_t)std::max(1L, r.shape[0] * r.shape[1]);
+            shape = Dimension(r.shape[0], r.shape[1], std::max<size_t>(1, r.data.size() / nc), 1);
+        } else throw std::runtime_error("node " + r.name + " has no usable shape");
+        Node* n = nullptr;
+        io::OutputNode* out = nullptr;
+        if (r.type == "Input") n = new io::InputNode(shape, r.requires_grad);
+        else if (r.type == "Output") n = out = new io::OutputNode(in_node(0));
+        else if (r.type == "Add") n = new calc::AddNode(in_node(0), in_node(1));
+        else if (r.type == "MatMul") n = new calc::MatMulNode(in_node(0), in_node(1));
+        else if (r.type == "ReLU") n = new calc::ReLUNode(in_node(0));
+        else if (r.type == "Reshape") n = new calc::ReshapeNode(in_node(0), shape);
+        else if (r.type == "Expand") n = new calc::ExpandNode(in_node(0), shape[0]);
+        else if (r.type == "Img2Col") n = new calc::Img2ColNode(in_node(0), attr(0), attr(1), attr(2), attr(3));
+        else if (r.type == "Col2Img") n = new calc::Col2ImgNode(in_node(0), attr(0), attr(1));
+        else if (r.type == "AveragePooling") n = new calc::AveragePoolingNode(in_node(0), attr(0), attr(1), attr(2));
+        else if (r.type == "Softmax") n = new calc::SoftmaxNode(in_node(0));
+        else if (r.type == "Conv2d")
+            n = new calc::Conv2dNode(in_node(0), in_node(1), r.pre.size() > 2 ? in_node(2) : nullptr, attr(0), attr(1),
+                                     attr(2), attr(3), attr(4) != 0);
+        else if (r.type == "Linear")
+            n = new calc::LinearNode(in_node(0), in_node(1), r.pre.size() > 2 ? in_node(2) : nullptr, attr(0) != 0);
+        else if (r.type == "BinaryCrossEntropy") n = out = new nodes::loss::BinaryCrossEntropyNode(in_node(0), in_node(1));
+        else throw std::runtime_error("node type '" + r.type + "' is not part of this library");
+        owned_.emplace_back(n);
+        created.push_back(n);
+        names_.push_back(r.name);
+        // a loss node's output IS its input's tensor: nothing of its own to restore
+        if (!out) {
+            if (r.data.size() != n->output->size())
+                throw std::runtime_error("node " + r.name + " holds " + std::to_string(r.data.size()) + " values, its shape needs " +
+                                         std::to_string(n->output->size()));
+            n->output->dataInject(const_cast<float*>(r.data.data()));
+            if (n->output->requiresGrad() && r.grad.size() == n->output->size())
+                n->output->dataInject(const_cast<float*>(r.grad.data()), true);
+        }
+        if (optimizer && !r.opt.empty()) optimizer->importState(n, r.opt);
+        order.emplace_back(r.order >= 0 ? r.order : (long)order.size(), n);
+        ticks.push_back((int)r.ticks);
+        if (out) outputs_.push_back(out);
+        else if (r.type == "Input") inputs_.push_back(static_cast<io::InputNode*>(n));
+    }
+    // insertion order of the saved graph: it decides which per-call time step Adam gives each parameter
+    std::vector<size_t> perm(order.size());
+    for (size_t i = 0; i < perm.size(); i++) perm[i] = i;
+    std::stable_sort(perm.begin(), perm.end(), [&](size_t a, size_t b) { return order[a].first < order[b].first; });
+    for (size_t i : perm) {
+        nodes_.push_back(order[i].second);
+        ticks_before_.push_back(ticks[i]);
+    }
+    sorted_nodes_ = created;
+    sorted_ = true;
+}
+
+nodes::Node* ComputeGraph::operator[](const std::string& name) const {
+    for (size_t i = 0; i < names_.size() && i < sorted_nodes_.size(); i++)
+        if (names_[i] == name) return sorted_nodes_[i];
+    return nullptr;
+}
+
 float ComputeGraph::getLoss() const {
     if (outputs_.empty()) throw std::runtime_error("No output node");
     return outputs_[0]->getLoss();
@@ -120,6 +340,23 @@ void Adam::step(nodes::Node* input) {
         NZB_CHECK(nzb_adam(t.data(), m->data(), v->data(), t.grad(), learning_rate, beta1_, beta2_, epsilon_, tstep,
                            (int64_t)t.size(), s));
     });
+}
+
+std::vector<std::vector<float>> Adam::exportState(nodes::Node* node) const {
+    auto m = m_.find(node);
+    auto v = v_.find(node);
+    if (m == m_.end() || v == v_.end() || !m->second || !v->second) return {};
+    return {m->second->hostData(), v->second->hostData()};
+}
+void Adam::importState(nodes::Node* node, const std::vector<std::vector<float>>& state) {
+    if (state.size() != 2 || state[0].size() != node->output->size() || state[1].size() != node->output->size())
+        throw std::runtime_error("Adam state of a node does not match its size");
+    auto& m = m_[node];
+    auto& v = v_[node];
+    m = std::make_unique<data::Tensor>(node->output->shape());
+    v = std::make_unique<data::Tensor>(node->output->shape());
+    m->dataInject(const_cast<float*>(state[0].data()));
+    v->dataInject(const_cast<float*>(state[1].data()));
 }
 
 }  // namespace nz::opt

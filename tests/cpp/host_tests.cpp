@@ -585,6 +585,91 @@ TEST(Model, UpdateStepsParametersOnlyUnlessAsked) {
     EXPECT_TRUE(any);
 }
 
+// ---- ComputeGraph::save / load (src/ComputeGraph.cu:553-811) with four-extent shapes and Adam state ----
+TEST(ComputeGraph, SaveLoadRoundTripResumesTraining) {
+    const char* path = "/tmp/nz_host_tests_graph.json";
+    SegModel m(2, 12, true);
+    auto x = uniform(2 * 3 * 12 * 12, -1, 1, 70);
+    std::vector<float> tg(2 * 16);
+    std::mt19937 gen(71);
+    for (auto& v : tg) v = (gen() & 1) ? 1.f : 0.f;
+    m.input.dataInject(x.begin(), x.end());
+    m.target.dataInject(tg.begin(), tg.end());
+    for (size_t i = 0; i < m.parameters().size(); i++) {
+        auto w = uniform(m.parameters()[i]->output->size(), -0.2f, 0.2f, 72 + (unsigned)i);
+        m.parameters()[i]->dataInject(w.begin(), w.end());
+    }
+    m.graph().zeroGrad();
+    opt::Adam adam(0.001f, 0.9f, 0.999f);
+    m.forward();
+    m.backward();
+    m.update(&adam);
+    m.forward();
+    m.backward();  // saved with live gradients and one step of Adam history
+    m.graph().save(path, &adam);
+
+    graph::ComputeGraph g2;
+    opt::Adam adam2(0.001f, 0.9f, 0.999f);
+    g2.load(path, &adam2);
+    EXPECT_EQ(g2.getNodes().size(), m.graph().getNodes().size());
+    EXPECT_EQ(adam2.counter(), adam.counter());
+    // every tensor (all four extents) and every gradient came back bit for bit
+    const auto& a = m.graph().getNodes();
+    const auto& b = g2.getNodes();
+    for (size_t i = 0; i < a.size() && i < b.size(); i++) {
+        EXPECT_TRUE(a[i]->type == b[i]->type);
+        EXPECT_TRUE(a[i]->output->shape() == b[i]->output->shape());
+        EXPECT_TRUE(a[i]->output->hostData() == b[i]->output->hostData());
+        if (a[i]->output->requiresGrad()) EXPECT_TRUE(a[i]->output->hostGrad() == b[i]->output->hostGrad());
+    }
+    // and training resumes identically: same Adam moments, same per-call time steps
+    m.update(&adam);
+    g2.update(&adam2);
+    g2.zeroGrad();
+    EXPECT_EQ(adam2.counter(), adam.counter());
+    size_t pi = 0;
+    for (size_t i = 0; i < a.size(); i++)
+        if (a[i]->inputs.empty() && a[i]->output->requiresGrad()) {
+            EXPECT_TRUE(a[i]->output->hostData() == b[i]->output->hostData());
+            pi++;
+        }
+    EXPECT_EQ(pi, m.parameters().size());
+    m.forward();
+    g2.forward();
+    EXPECT_TRUE(close_vec(m.out->output->hostData(), g2.getOutputs().at(0)->inputs[0]->output->hostData(), 1e-6, 1e-5));
+    // an unknown node type and a second load are refused
+    bool threw = false;
+    try {
+        g2.load(path);
+    } catch (const std::runtime_error&) {
+        threw = true;
+    }
+    EXPECT_TRUE(threw);
+    remove(path);
+}
+
+TEST(ComputeGraph, LoadsFileInTheReferenceLayout) {
+    // what the reference's save() writes: two extents in "shape", default stream precision
+    const char* path = "/tmp/nz_host_tests_ref_layout.json";
+    FILE* f = fopen(path, "w");
+    fputs("[\n  {\n    \"type\": \"Input\",\n    \"name\": \"Input_0\",\n    \"pre\": [],\n    \"post\": [2],\n"
+          "    \"shape\": [1, 1],\n    \"data\": [1, 2, 3, 4.5],\n    \"requires_grad\": true,\n    \"grad\": [0, 0, 0, 0]\n  },\n"
+          "  {\n    \"type\": \"Input\",\n    \"name\": \"Input_1\",\n    \"pre\": [],\n    \"post\": [2],\n"
+          "    \"shape\": [1, 1],\n    \"data\": [10, 20, 30, 40],\n    \"requires_grad\": false,\n    \"grad\": []\n  },\n"
+          "  {\n    \"type\": \"Add\",\n    \"name\": \"Add_2\",\n    \"pre\": [0, 1],\n    \"post\": [],\n"
+          "    \"shape\": [1, 1],\n    \"data\": [0, 0, 0, 0],\n    \"requires_grad\": true,\n    \"grad\": [0, 0, 0, 0]\n  }\n]\n", f);
+    fclose(f);
+    graph::ComputeGraph g;
+    g.load(path);
+    EXPECT_EQ(g.getNodes().size(), (size_t)3);
+    EXPECT_TRUE(g["Add_2"] != nullptr && g["Input_1"] != nullptr && g["nope"] == nullptr);
+    EXPECT_TRUE(g["Input_0"]->output->shape() == Dimension(1, 1, 4, 1));
+    g.forward();
+    const auto sum = g["Add_2"]->output->hostData();
+    EXPECT_TRUE(sum == std::vector<float>({11.f, 22.f, 33.f, 44.5f}));
+    remove(path);
+}
+
 TEST(StreamManager, OrderingAndSync) {
     auto& sm = cuStrm::StreamManager<float>::Instance();
     EXPECT_EQ(sm.streamCount(), (size_t)16);
