@@ -253,7 +253,7 @@ NZB_API int nzb_cast_f32_f16(const float* in, void* out_f16, int64_t rows, int64
 typedef struct nzb_linear_desc {
     int64_t batch, in_features, out_features;
     int32_t relu;
-    int32_t reserved;
+    int32_t overwrite_dx;  /* backward: dx = ... instead of dx += ... (a gradient buffer with one consumer) */
 } nzb_linear_desc;
 
 NZB_API int nzb_linear_workspace_bytes(const nzb_linear_desc* desc, size_t* bytes_out);
@@ -286,6 +286,9 @@ typedef struct nzb_conv_desc {
     int32_t bias_mode;
     int32_t relu;
     int32_t accumulate;
+    int32_t overwrite_dx;  /* backward calls: dx = ... instead of dx += ... (a gradient buffer with one consumer
+                              needs neither clearing before nor reading during the backward pass) */
+    int32_t reserved;
 } nzb_conv_desc;
 
 /* Scratch bytes for any of the nzb_conv2d_* calls with this descriptor (fp16 weight staging). */
@@ -388,6 +391,11 @@ NZB_API int nzb_avgpool(float* out, const float* in, int64_t pool, int64_t strid
 NZB_API int nzb_avgpool_backward(float* gin, const float* gout, int64_t pool, int64_t stride, int64_t pad,
                                  int64_t batches, int64_t channels, int64_t H_in, int64_t W_in, int64_t H_out,
                                  int64_t W_out, void* stream);
+/* The same with overwrite != 0: gin is WRITTEN (as if it had been zero), so a gradient buffer with a single
+ * consumer needs neither clearing before nor reading during the backward pass. */
+NZB_API int nzb_avgpool_backward_ex(float* gin, const float* gout, int64_t pool, int64_t stride, int64_t pad,
+                                    int64_t batches, int64_t channels, int64_t H_in, int64_t W_in, int64_t H_out,
+                                    int64_t W_out, int overwrite, void* stream);
 
 /*
  * Softmax over each of `batches` vectors of n elements, fully on the device (the reference
@@ -411,6 +419,54 @@ NZB_API int nzb_bce_backward(float* out, const float* predict, const float* targ
 /* Adam step with explicit t (AdamKernel, src/OperationKernels.cu:753-773; opt::Adam::step, src/Optimizer.cu:86-102). */
 NZB_API int nzb_adam(float* data, float* m, float* v, const float* grad, float lr, float beta1, float beta2,
                      float eps, int t, int64_t n, void* stream);
+
+/*
+ * Adam over all tensors of a model in ONE launch: opt::Adam::step (src/Optimizer.cu:86-102) is called once
+ * per tensor by ComputeGraph::update (src/ComputeGraph.cu:541-547), one AdamKernel launch each. Every
+ * tensor carries its own time step t (the reference's counter advances per step() call). shadow_f16,
+ * when non-null, receives the updated weights rounded to fp16 (n halves): the operand copy the tensor
+ * cores read, written by the pass that already holds the new value. Same arithmetic as nzb_adam.
+ */
+typedef struct nzb_adam_tensor {
+    float* data;
+    float* m;
+    float* v;
+    const float* grad;
+    void* shadow_f16;
+    int64_t n;
+    int32_t t;
+    int32_t reserved;
+} nzb_adam_tensor;
+NZB_API int nzb_adam_multi(const nzb_adam_tensor* tensors, int count, float lr, float beta1, float beta2, float eps,
+                           void* stream);
+
+/*
+ * The softmax + binary-cross-entropy head as one kernel each way: SoftmaxNode::forward followed by
+ * BinaryCrossEntropyNode::forward (src/Nodes.cu:534-536, 822-840; the reference syncs the host once per
+ * vector for the exp-sum and once for the loss), and BinaryCrossEntropyNode::backward followed by
+ * SoftmaxNode::backward (src/Nodes.cu:842-848, 538-548). probs {batches, n} receives the softmax, *loss
+ * (device scalar) is incremented by the mean BCE over all batches*n elements; the backward OVERWRITES
+ * dlogits with J(probs) * dBCE, with J and dBCE rounded to fp16 first when round_f16 != 0 (what the
+ * reference's tensor-core product does). n <= 1024.
+ */
+NZB_API int nzb_softmax_bce_forward(float* probs, float* loss, const float* logits, const float* target,
+                                    int64_t batches, int64_t n, void* stream);
+NZB_API int nzb_softmax_bce_backward(float* dlogits, const float* probs, const float* target, int64_t batches,
+                                     int64_t n, int round_f16, void* stream);
+
+/*
+ * Max pooling (MaxPoolingKernel / MaxPoolingBackwardKernel, src/OperationKernels.cu:1507-1573; iMaxPooling
+ * / iMaxPoolingBackward): the first maximum in row-major window order wins, its index within the window is
+ * stored as a float in `position` {batches, channels, H_out, W_out}, an empty window yields 0. The backward
+ * ADDS each upstream gradient to the input element recorded as its window's maximum (gather form of the
+ * reference's atomicAdd scatter).
+ */
+NZB_API int nzb_maxpool(float* out, float* position, const float* in, int64_t pool, int64_t stride, int64_t pad,
+                        int64_t batches, int64_t channels, int64_t H_in, int64_t W_in, int64_t H_out, int64_t W_out,
+                        void* stream);
+NZB_API int nzb_maxpool_backward(float* gin, const float* position, const float* gout, int64_t pool, int64_t stride,
+                                 int64_t pad, int64_t batches, int64_t channels, int64_t H_in, int64_t W_in,
+                                 int64_t H_out, int64_t W_out, void* stream);
 
 /* FillKernel (src/OperationKernels.cu:1146-1156), ExpandKernel (:1282-1296; batch broadcast copy), in-place scale. */
 NZB_API int nzb_fill(float* data, float value, int64_t n, void* stream);

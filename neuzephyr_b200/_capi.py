@@ -18,8 +18,9 @@ EXPORTS = [
     "nzb_conv2d_workspace_bytes", "nzb_conv2d_forward", "nzb_conv2d_backward_data", "nzb_conv2d_backward_weight",
     "nzb_conv2d_backward_bias", "nzb_conv2d_backward_workspace_bytes", "nzb_conv2d_backward",
     "nzb_img2col", "nzb_img2col_backward", "nzb_col2img", "nzb_col2img_backward", "nzb_add_broadcast",
-    "nzb_add_backward", "nzb_relu", "nzb_relu_backward", "nzb_avgpool", "nzb_avgpool_backward", "nzb_softmax",
-    "nzb_softmax_backward", "nzb_bce", "nzb_bce_backward", "nzb_adam", "nzb_fill", "nzb_expand", "nzb_scale",
+    "nzb_add_backward", "nzb_relu", "nzb_relu_backward", "nzb_avgpool", "nzb_avgpool_backward", "nzb_avgpool_backward_ex", "nzb_softmax",
+    "nzb_softmax_backward", "nzb_bce", "nzb_bce_backward", "nzb_adam", "nzb_adam_multi", "nzb_softmax_bce_forward",
+    "nzb_softmax_bce_backward", "nzb_maxpool", "nzb_maxpool_backward", "nzb_fill", "nzb_expand", "nzb_scale",
 ]
 
 
@@ -40,13 +41,20 @@ class GemmDesc(ctypes.Structure):
 class ConvDesc(ctypes.Structure):
     """struct nzb_conv_desc"""
     _fields_ = [(n, ctypes.c_int64) for n in ("N", "C", "H", "W", "Cout", "Kh", "Kw", "stride", "pad")] + \
-               [(n, ctypes.c_int32) for n in ("weights_per_sample", "bias_mode", "relu", "accumulate")]
+               [(n, ctypes.c_int32) for n in ("weights_per_sample", "bias_mode", "relu", "accumulate", "overwrite_dx",
+                                              "reserved")]
 
 
 class LinearDesc(ctypes.Structure):
     """struct nzb_linear_desc"""
     _fields_ = [("batch", ctypes.c_int64), ("in_features", ctypes.c_int64), ("out_features", ctypes.c_int64),
-                ("relu", ctypes.c_int32), ("reserved", ctypes.c_int32)]
+                ("relu", ctypes.c_int32), ("overwrite_dx", ctypes.c_int32)]
+
+
+class AdamTensor(ctypes.Structure):
+    """struct nzb_adam_tensor"""
+    _fields_ = [("data", ctypes.c_void_p), ("m", ctypes.c_void_p), ("v", ctypes.c_void_p), ("grad", ctypes.c_void_p),
+                ("shadow_f16", ctypes.c_void_p), ("n", ctypes.c_int64), ("t", ctypes.c_int32), ("reserved", ctypes.c_int32)]
 
 
 class NzbError(RuntimeError):
@@ -109,11 +117,17 @@ def lib():
         L.nzb_relu_backward.argtypes = [vp, vp, vp, i64, vp]
         L.nzb_avgpool.argtypes = [vp, vp] + [i64] * 9 + [vp]
         L.nzb_avgpool_backward.argtypes = [vp, vp] + [i64] * 9 + [vp]
+        L.nzb_avgpool_backward_ex.argtypes = [vp, vp] + [i64] * 9 + [ci, vp]
         L.nzb_softmax.argtypes = [vp, vp, i64, i64, vp]
         L.nzb_softmax_backward.argtypes = [vp, vp, vp, i64, i64, ci, vp]
         L.nzb_bce.argtypes = [vp, vp, vp, i64, vp]
         L.nzb_bce_backward.argtypes = [vp, vp, vp, i64, vp]
         L.nzb_adam.argtypes = [vp, vp, vp, vp, f32, f32, f32, f32, ci, i64, vp]
+        L.nzb_adam_multi.argtypes = [ctypes.POINTER(AdamTensor), ci, f32, f32, f32, f32, vp]
+        L.nzb_softmax_bce_forward.argtypes = [vp, vp, vp, vp, i64, i64, vp]
+        L.nzb_softmax_bce_backward.argtypes = [vp, vp, vp, i64, i64, ci, vp]
+        L.nzb_maxpool.argtypes = [vp, vp, vp] + [i64] * 9 + [vp]
+        L.nzb_maxpool_backward.argtypes = [vp, vp, vp] + [i64] * 9 + [vp]
         L.nzb_fill.argtypes = [vp, f32, i64, vp]
         L.nzb_expand.argtypes = [vp, vp, i64, i64, vp]
         L.nzb_scale.argtypes = [vp, f32, i64, vp]

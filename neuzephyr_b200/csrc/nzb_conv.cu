@@ -2108,7 +2108,7 @@ int nzb_conv2d_backward_data(const nzb_conv_desc* d, const float* dy, const floa
         const TmaPlan tp = tma_plan(d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W, wN);
         if (tp.ok) {
             ConvTmaRun r{dy, dx, nullptr, w, d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->Kh - 1 - d->pad, d->H, d->W,
-                         d->C, d->Cout, d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, 1, 0, 1, nullptr};
+                         d->C, d->Cout, d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, d->overwrite_dx ? 0 : 1, 0, 1, nullptr};
             return run_conv_tma(r, tp, workspace, s);
         }
     }
@@ -2123,7 +2123,7 @@ int nzb_conv2d_backward_data(const nzb_conv_desc* d, const float* dy, const floa
     }
     // dX {N, C, H, W} += conv(dY {N, Cout, Ho, Wo}, flipped weights, pad' = Kh - 1 - pad, stride 1)
     ConvRun r{dy, dx, nullptr, d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, 1, d->Kh - 1 - d->pad, d->H, d->W,
-              d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, 1, 0};
+              d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, d->overwrite_dx ? 0 : 1, 0};
     return run_conv(r, W16, Kp2, wN, s);
 }
 
@@ -2270,7 +2270,8 @@ int nzb_conv2d_backward(const nzb_conv_desc* d, const float* x, const float* w, 
             TmaPlan pl = tma_plan(n, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W,
                                   d->weights_per_sample ? n : 1);
             ConvTmaRun r{dy_c, dx + img0 * d->C * d->H * d->W, nullptr, w_c, n, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, padb,
-                         d->H, d->W, d->C, d->Cout, d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE, 1, 0, 1, XSdy};
+                         d->H, d->W, d->C, d->Cout, d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE,
+                         d->overwrite_dx ? 0 : 1, 0, 1, XSdy};
             rc = run_conv_tma(r, pl, base, s);
             if (rc != NZB_OK) return rc;
         }

@@ -122,4 +122,17 @@ int make_plan(const nzb_gemm_desc* d, Plan* pl);
 int stage_operands(Plan* pl, const nzb_gemm_desc* d, const float* A, const float* B, __half* A16, __half* B16,
                    int sm_count, cudaStream_t stream);
 
+#ifdef __CUDACC__
+// One Adam update (AdamKernel, src/OperationKernels.cu:753-766) with every rounding step spelled out, so
+// that the per-tensor kernel and the multi-tensor kernel give bit-identical results whatever the compiler
+// would otherwise contract. c1 = 1 - beta1^t, c2 = 1 - beta2^t. Returns the new weight, updates m and v.
+__device__ __forceinline__ float adam_update(float p, float& m, float& v, float g, float lr, float beta1, float beta2,
+                                             float eps, float c1, float c2) {
+    m = __fmaf_rn(m, beta1, __fmul_rn(g, __fsub_rn(1.f, beta1)));
+    v = __fmaf_rn(v, beta2, __fmul_rn(__fmul_rn(g, g), __fsub_rn(1.f, beta2)));
+    const float step = __fdiv_rn(__fmul_rn(lr, __fdiv_rn(m, c1)), __fadd_rn(__fsqrt_rn(__fdiv_rn(v, c2)), eps));
+    return __fsub_rn(p, step);
+}
+#endif
+
 }  // namespace nzb

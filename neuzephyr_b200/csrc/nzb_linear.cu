@@ -137,7 +137,7 @@ int nzb_linear_backward(const nzb_linear_desc* d, const float* x, const float* w
         g.b_mn = 1; g.ldb16 = z.Inp;
         g.C = dx; g.ldc = z.In;
         g.out_e[0] = g.out_e[1] = g.red_e[0] = g.red_e[1] = 1;
-        g.accumulate = 1;
+        g.accumulate = d->overwrite_dx ? 0 : 1;
         rc = launch_gemm(g, s);
         if (rc != NZB_OK) return rc;
     }

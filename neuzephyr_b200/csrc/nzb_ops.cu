@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(256) avgpool_fixed_kernel(float* __restrict__ 
 template <int POOL>
 __global__ void __launch_bounds__(256) avgpool_backward_s2_kernel(float* __restrict__ gin,
                                                                   const float* __restrict__ gout, int H, int W, int Ho,
-                                                                  int Wo, int planes) {
+                                                                  int Wo, int planes, int overwrite) {
     constexpr int NH = (POOL - 1) / 2 + 1;      // windows covering rows 2a, 2a+1
     constexpr int NW = (POOL - 1 + 3) / 2 + 1;  // windows covering columns 4b .. 4b+3
     const int W4 = W >> 2, H2 = (H + 1) >> 1, per = H2 * W4;
@@ -311,7 +311,8 @@ __global__ void __launch_bounds__(256) avgpool_backward_s2_kernel(float* __restr
                             if (dh >= h_lo && dh <= h_hi && dw >= w_lo && dw <= w_hi) s[j] += v[dh][dw];
                 }
                 float4* d4 = reinterpret_cast<float4*>(dst + (int64_t)hi * W + wi0);
-                float4 o = *d4;
+                // every input element is visited exactly once: overwriting needs no cleared buffer
+                float4 o = overwrite ? make_float4(0.f, 0.f, 0.f, 0.f) : *d4;
                 o.x += s[0] / full; o.y += s[1] / full; o.z += s[2] / full; o.w += s[3] / full;
                 *d4 = o;
             }
@@ -547,10 +548,8 @@ __global__ void __launch_bounds__(256) adam_kernel(float* __restrict__ data, flo
                                                    float* __restrict__ v, const float* __restrict__ grad, float lr,
                                                    float beta1, float beta2, float eps, float c1, float c2, int64_t n) {
     NZB_GRID_STRIDE(i, n) {
-        const float g = grad[i];
-        const float mt = m[i] * beta1 + g * (1.f - beta1);
-        const float vt = v[i] * beta2 + g * g * (1.f - beta2);
-        data[i] -= lr * (mt / c1) / (sqrtf(vt / c2) + eps);
+        float mt = m[i], vt = v[i];
+        data[i] = adam_update(data[i], mt, vt, grad[i], lr, beta1, beta2, eps, c1, c2);
         m[i] = mt;
         v[i] = vt;
     }
@@ -720,11 +719,24 @@ int nzb_avgpool(float* out, const float* in, int64_t pool, int64_t stride, int64
 
 int nzb_avgpool_backward(float* gin, const float* gout, int64_t pool, int64_t stride, int64_t pad, int64_t batches,
                          int64_t channels, int64_t H_in, int64_t W_in, int64_t H_out, int64_t W_out, void* stream) {
+    return nzb_avgpool_backward_ex(gin, gout, pool, stride, pad, batches, channels, H_in, W_in, H_out, W_out, 0, stream);
+}
+
+int nzb_avgpool_backward_ex(float* gin, const float* gout, int64_t pool, int64_t stride, int64_t pad, int64_t batches,
+                            int64_t channels, int64_t H_in, int64_t W_in, int64_t H_out, int64_t W_out, int overwrite,
+                            void* stream) {
     if (!gin || !gout) return fail(NZB_ERR_BAD_ARG, "null pointer");
     if (pool < 1 || stride < 1) return fail(NZB_ERR_BAD_ARG, "bad window");
     NZB_OPS_PROLOGUE();
     const int64_t total = batches * channels * H_in * W_in;
     if (total == 0) return NZB_OK;
+    // overwrite: the stride-2 kernels below write every element themselves; every other form clears gin
+    // first and then accumulates as usual
+    const bool direct = overwrite && pad == 0 && W_in % 4 == 0 && (reinterpret_cast<uintptr_t>(gin) & 15) == 0 &&
+                        stride == 2 && (pool == 5 || pool == 3 || pool == 2) && H_in * W_in < INT32_MAX &&
+                        batches * channels < INT32_MAX;
+    if (overwrite && !direct) NZB_CUDA_TRY(cudaMemsetAsync(gin, 0, (size_t)total * sizeof(float), s));
+    const int ovw = direct ? 1 : 0;
     if (H_in * W_in < INT32_MAX && batches * channels < INT32_MAX && pool < 65536 && stride < 65536 && pad < 65536) {
         const int64_t per = H_in * W_in, planes = batches * channels;
         int64_t gx = (per + 255) / 256;
@@ -741,11 +753,11 @@ int nzb_avgpool_backward(float* gin, const float* gout, int64_t pool, int64_t st
                 if (g2 > capx) g2 = capx;
                 const dim3 grid2((unsigned)g2, (unsigned)gy);
                 if (pool == 5)
-                    avgpool_backward_s2_kernel<5><<<grid2, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+                    avgpool_backward_s2_kernel<5><<<grid2, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes, ovw);
                 else if (pool == 3)
-                    avgpool_backward_s2_kernel<3><<<grid2, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+                    avgpool_backward_s2_kernel<3><<<grid2, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes, ovw);
                 else
-                    avgpool_backward_s2_kernel<2><<<grid2, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes);
+                    avgpool_backward_s2_kernel<2><<<grid2, 256, 0, s>>>(gin, gout, (int)H_in, (int)W_in, (int)H_out, (int)W_out, (int)planes, ovw);
                 NZB_OPS_EPILOGUE();
             }
             if (stride == 1)

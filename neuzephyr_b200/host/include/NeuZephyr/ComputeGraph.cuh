@@ -39,6 +39,12 @@ public:
     // declares the reference nodes it stands for with addPhantomSteps().
     void update(opt::Optimizer* optimizer, const std::function<void()>& before_step = nullptr) const;
     void stepIntermediateNodes(bool on) { step_intermediates_ = on; }
+    // Marks the gradient buffers that one node alone writes in full -- the output of a non-parameter node
+    // that feeds exactly one consumer of type Conv2d / Linear (as their first input) or AveragePooling --
+    // as overwritten (Tensor::setGradOverwritten): zeroGrad() then skips them and the consumer's backward
+    // stores instead of adding. Same results, one clearing pass and one read of the largest tensors of a
+    // model less per step. Model turns it on for fused models; off by default for hand-built graphs.
+    void overwriteSingleConsumerGradients(bool on);
     // `n` optimizer ticks that belong to gradient-requiring reference nodes which have no node of
     // their own in this graph (a fused node collapses several); they are placed before the next
     // node that is added, or at the end of the list.

@@ -55,11 +55,13 @@ protected:
     Node* Conv2d(Node* input, size_t outChannels, size_t kernelHeight, size_t kernelWidth, size_t stride,
                  size_t padding, bool bias = true, bool perSampleWeights = false, bool fuseRelu = false);
     Node* AvgPool2d(Node* input, size_t poolSize, size_t stride, size_t padding = 0);
+    Node* MaxPool2d(Node* input, size_t poolSize, size_t stride, size_t padding = 0);
     void BCELoss(Node* input, Node* target);
 
 private:
     Node* own(Node* n, bool parameter = false);
     bool fused_ = true;
+    bool gradients_marked_ = false;
     bool grads_synced_ = false;
     bool overlap_sync_ = true;
     std::vector<bool> param_synced_;

@@ -135,11 +135,27 @@ private:
     Tensor::size_type pool_, stride_, pad_;
 };
 
+// MaxPoolingNode (src/Nodes.cu:716-743; kernels src/OperationKernels.cu:1507-1573)
+class MaxPoolingNode : public Node {
+public:
+    MaxPoolingNode(Node* input, Tensor::size_type poolSize, Tensor::size_type stride, Tensor::size_type padding);
+    void forward() override;
+    void backward() override;
+    std::vector<size_t> attributes() const override { return {pool_, stride_, pad_}; }
+
+private:
+    Tensor::size_type pool_, stride_, pad_;
+    std::shared_ptr<Tensor> position_;  // arg-max index of every window, as a float
+};
+
 class SoftmaxNode : public Node {
 public:
     explicit SoftmaxNode(Node* input);
     void forward() override;
     void backward() override;
+    // set by a loss node that computes softmax + loss (and their backward) in one kernel: this node's own
+    // forward / backward then do nothing (its output is still the probabilities, written by the loss node)
+    bool handledByLoss = false;
     // true (default): round the Jacobian and the upstream gradient to fp16 like the reference's
     // tensor-core product in SoftmaxNode::backward (src/Nodes.cu:538-548)
     bool roundLikeReference = true;
@@ -181,6 +197,13 @@ public:
     BinaryCrossEntropyNode(Node* input1, Node* input2);  // prediction, target
     void forward() override;
     void backward() override;
+    // When the prediction comes from a SoftmaxNode, compute softmax + loss in one kernel and their two
+    // backward steps in another (Model::BCELoss turns this on for fused models). Results are those of the
+    // two nodes run one after the other.
+    void fuseWithSoftmax(bool on);
+
+private:
+    calc::SoftmaxNode* softmax_ = nullptr;
 };
 }  // namespace loss
 

@@ -4,6 +4,7 @@
 #pragma once
 #include <memory>
 #include <unordered_map>
+#include <utility>
 #include <vector>
 
 #include "Nodes.cuh"
@@ -17,6 +18,10 @@ public:
     // `n` step() calls the reference would have made on nodes this graph does not step
     // (activations, nodes folded into a fused node): only per-call state advances.
     virtual void skip(int n) { (void)n; }
+    // ComputeGraph::update brackets its loop with these: an optimizer may collect the step() calls in
+    // between and run them as one launch in endBatch() (Adam does). The default runs each step at once.
+    virtual void beginBatch() {}
+    virtual void endBatch() {}
     // Checkpointing (ComputeGraph::save / load): a name, the per-call counter, and per node the state
     // vectors the optimizer keeps (empty when it keeps none for that node).
     virtual const char* name() const { return "Optimizer"; }
@@ -41,6 +46,8 @@ public:
     Adam(float learning_rate, float beta1, float beta2);
     void step(nodes::Node* input) override;
     void skip(int n) override { it_ += n; }
+    void beginBatch() override;
+    void endBatch() override;  // one nzb_adam_multi launch over every tensor stepped since beginBatch()
     const char* name() const override { return "Adam"; }
     long counter() const override { return it_; }
     void setCounter(long it) override { it_ = (int)it; }
@@ -55,6 +62,8 @@ public:
 private:
     float beta1_, beta2_, epsilon_ = 1e-6f;
     int it_ = 0, it_shared_ = 0;
+    bool batching_ = false;
+    std::vector<std::pair<nodes::Node*, int>> batch_;  // (node, time step) collected between begin / endBatch
     std::unordered_map<nodes::Node*, std::unique_ptr<data::Tensor>> m_, v_;
 };
 

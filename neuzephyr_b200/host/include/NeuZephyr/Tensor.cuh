@@ -55,6 +55,11 @@ public:
     void dataInject(const std::initializer_list<value_type>& data, bool grad = false) const;
 
     void zeroGrad() const;
+    // A gradient buffer with exactly one consumer whose backward WRITES it (instead of adding to it) needs
+    // no clearing: zeroGrad() skips it. Set by ComputeGraph for activations of fused models; the writing
+    // node asks gradOverwritten() to choose between "=" and "+=". Results are the same either way.
+    void setGradOverwritten(bool on) { grad_overwritten_ = on; }
+    bool gradOverwritten() const noexcept { return grad_overwritten_; }
     // uniform (0, 1] from a 64-bit seed, as the reference's curand-based randomize in distribution
     // (src/Tensor.cu:298-300); the bit stream differs, so seeded comparisons inject data instead
     void randomize(unsigned long long seed = 0) const;
@@ -84,6 +89,7 @@ private:
     value_type* data_ = nullptr;
     value_type* grad_ = nullptr;
     bool requires_grad_ = false;
+    bool grad_overwritten_ = false;
 };
 
 }  // namespace nz::data

@@ -40,6 +40,18 @@ void iAveragePooling(float* out, float* in, size_t pool, size_t stride, size_t p
                      size_t H_in, size_t W_in, size_t H_out, size_t W_out);
 void iAveragePoolingBackward(float* gin, float* gout, size_t pool, size_t stride, size_t pad, size_t batches,
                              size_t channels, size_t H_in, size_t W_in, size_t H_out, size_t W_out);
+// iMaxPooling / iMaxPoolingBackward (include/NeuZephyr/TensorOperations.cuh; kernels
+// src/OperationKernels.cu:1507-1573): position holds each window's arg-max index as a float
+void iMaxPooling(float* out, float* position, float* in, size_t pool, size_t stride, size_t pad, size_t batches,
+                 size_t channels, size_t H_in, size_t W_in, size_t H_out, size_t W_out);
+void iMaxPoolingBackward(float* gin, float* position, float* gout, size_t pool, size_t stride, size_t pad,
+                         size_t batches, size_t channels, size_t H_in, size_t W_in, size_t H_out, size_t W_out);
+// the softmax + BCE head in one kernel each way (no counterpart in the reference)
+void iSoftmaxBCE(float* probs, float* loss, float* logits, float* target, size_t batches, size_t n);
+void iSoftmaxBCEBackward(float* dlogits, float* probs, float* target, size_t batches, size_t n, bool round_f16);
+// gin = ... instead of gin += ... (for a gradient buffer marked Tensor::gradOverwritten())
+void iAveragePoolingBackwardOverwrite(float* gin, float* gout, size_t pool, size_t stride, size_t pad, size_t batches,
+                                      size_t channels, size_t H_in, size_t W_in, size_t H_out, size_t W_out);
 void iSoftmax(float* out, float* in, size_t batches, size_t n);
 void iSoftmaxBackward(float* gin, float* y, float* gout, size_t batches, size_t n, bool round_f16);
 void iBCE(float* loss, float* predict, float* target, size_t n);

@@ -61,6 +61,24 @@ void ComputeGraph::topologicalSort() {
     if (sorted_nodes_.size() != nodes_.size()) throw std::runtime_error("Graph has cycle");
     sorted_ = true;
 }
+void ComputeGraph::overwriteSingleConsumerGradients(bool on) {
+    std::unordered_map<Node*, std::vector<Node*>> users;
+    for (Node* n : nodes_)
+        for (Node* in : n->inputs) users[in].push_back(n);
+    for (Node* n : nodes_) {
+        bool mark = false;
+        if (on && !n->inputs.empty() && n->output->requiresGrad() && users[n].size() == 1) {
+            Node* u = users[n][0];
+            const bool first = !u->inputs.empty() && u->inputs[0] == n &&
+                               std::count(u->inputs.begin(), u->inputs.end(), n) == 1;
+            mark = first && (u->type == "Conv2d" || u->type == "Linear" || u->type == "AveragePooling");
+        }
+        // an output node shares its input's tensor: never mark that one
+        for (Node* o : outputs_)
+            if (!o->inputs.empty() && o->inputs[0] == n) mark = false;
+        n->output->setGradOverwritten(mark);
+    }
+}
 void ComputeGraph::forward() {
     if (!sorted_) topologicalSort();
     for (Node* n : sorted_nodes_) n->forward();
@@ -77,6 +95,7 @@ void ComputeGraph::zeroGrad() const {
 }
 void ComputeGraph::update(opt::Optimizer* optimizer, const std::function<void()>& before_step) const {
     if (before_step) before_step();
+    optimizer->beginBatch();
     for (size_t i = 0; i < nodes_.size(); i++) {
         Node* n = nodes_[i];
         if (ticks_before_[i]) optimizer->skip(ticks_before_[i]);
@@ -85,6 +104,7 @@ void ComputeGraph::update(opt::Optimizer* optimizer, const std::function<void()>
         else optimizer->skip(1);  // the reference steps this activation (src/ComputeGraph.cu:541-547)
     }
     if (pending_ticks_) optimizer->skip(pending_ticks_);
+    optimizer->endBatch();
 }
 // ---- save / load (src/ComputeGraph.cu:553-811) -------------------------------------------------
 namespace {
@@ -257,6 +277,7 @@ void ComputeGraph::load(const std::string& path, opt::Optimizer* optimizer) {
         else if (r.type == "Img2Col") n = new calc::Img2ColNode(in_node(0), attr(0), attr(1), attr(2), attr(3));
         else if (r.type == "Col2Img") n = new calc::Col2ImgNode(in_node(0), attr(0), attr(1));
         else if (r.type == "AveragePooling") n = new calc::AveragePoolingNode(in_node(0), attr(0), attr(1), attr(2));
+        else if (r.type == "MaxPooling") n = new calc::MaxPoolingNode(in_node(0), attr(0), attr(1), attr(2));
         else if (r.type == "Softmax") n = new calc::SoftmaxNode(in_node(0));
         else if (r.type == "Conv2d")
             n = new calc::Conv2dNode(in_node(0), in_node(1), r.pre.size() > 2 ? in_node(2) : nullptr, attr(0), attr(1),
@@ -336,10 +357,47 @@ void Adam::step(nodes::Node* input) {
     }
     it_++;  // one time step per call, shared by all parameters (src/Optimizer.cu:86-102)
     const int tstep = perCallTimeStep ? it_ : (it_shared_ > 0 ? it_shared_ : 1);
+    if (batching_) {
+        batch_.emplace_back(input, tstep);
+        return;
+    }
     SM::Instance().run({t.data(), m->data(), v->data()}, {t.grad()}, [&](cudaStream_t s) {
         NZB_CHECK(nzb_adam(t.data(), m->data(), v->data(), t.grad(), learning_rate, beta1_, beta2_, epsilon_, tstep,
                            (int64_t)t.size(), s));
     });
+}
+
+void Adam::beginBatch() {
+    batching_ = true;
+    batch_.clear();
+}
+void Adam::endBatch() {
+    batching_ = false;
+    if (batch_.empty()) return;
+    // one launch for all tensors: ordered after every pending use of the tensors it writes (weights and
+    // moments) and after the writers of the gradients it reads (the all-reduce of a data-parallel step)
+    std::vector<nzb_adam_tensor> list(batch_.size());
+    auto& sm = SM::Instance();
+    cudaStream_t s = sm.getStream();
+    for (size_t i = 0; i < batch_.size(); i++) {
+        data::Tensor& t = *batch_[i].first->output;
+        data::Tensor& m = *m_[batch_[i].first];
+        data::Tensor& v = *v_[batch_[i].first];
+        sm.streamWait(t.data(), s, true);
+        sm.streamWait(m.data(), s, true);
+        sm.streamWait(v.data(), s, true);
+        sm.streamWait(t.grad(), s, false);
+        list[i] = nzb_adam_tensor{t.data(), m.data(), v.data(), t.grad(), nullptr, (int64_t)t.size(), batch_[i].second, 0};
+    }
+    NZB_CHECK(nzb_adam_multi(list.data(), (int)list.size(), learning_rate, beta1_, beta2_, epsilon_, s));
+    for (size_t i = 0; i < batch_.size(); i++) {
+        data::Tensor& t = *batch_[i].first->output;
+        sm.recordData(t.data(), s);
+        sm.recordData(m_[batch_[i].first]->data(), s);
+        sm.recordData(v_[batch_[i].first]->data(), s);
+        sm.recordRead(t.grad(), s);
+    }
+    batch_.clear();
 }
 
 std::vector<std::vector<float>> Adam::exportState(nodes::Node* node) const {
@@ -379,6 +437,10 @@ Model::Node* Model::own(Node* n, bool parameter) {
     return n;
 }
 Tensor& Model::forward() {
+    if (fused_ && !gradients_marked_) {
+        computeGraph.overwriteSingleConsumerGradients(true);
+        gradients_marked_ = true;
+    }
     computeGraph.forward();
     return *computeGraph.getOutputs().at(0)->output;
 }
@@ -529,10 +591,15 @@ Model::Node* Model::AvgPool2d(Node* input, size_t pool, size_t stride, size_t pa
     computeGraph.addNode(input);
     return own(new calc::AveragePoolingNode(input, pool, stride, pad));
 }
+Model::Node* Model::MaxPool2d(Node* input, size_t pool, size_t stride, size_t pad) {
+    computeGraph.addNode(input);
+    return own(new calc::MaxPoolingNode(input, pool, stride, pad));
+}
 void Model::BCELoss(Node* input, Node* target) {
     computeGraph.addNode(input);
     Node* expanded = TargetExpand(target, input->output->shape());
     auto* bce = new nodes::loss::BinaryCrossEntropyNode(input, expanded);
+    if (fused_) bce->fuseWithSoftmax(true);
     hiddenNodes.push_back(bce);
     computeGraph.addOutput(bce);
 }

@@ -224,8 +224,35 @@ void AveragePoolingNode::forward() {
 void AveragePoolingNode::backward() {
     if (inputs[0]->output->requiresGrad()) {
         const auto s = inputs[0]->output->shape(), o = output->shape();
-        data::iAveragePoolingBackward(inputs[0]->output->grad(), output->grad(), pool_, stride_, pad_, s.N(), s.C(),
-                                      s.H(), s.W(), o.H(), o.W());
+        if (inputs[0]->output->gradOverwritten())
+            data::iAveragePoolingBackwardOverwrite(inputs[0]->output->grad(), output->grad(), pool_, stride_, pad_, s.N(),
+                                                   s.C(), s.H(), s.W(), o.H(), o.W());
+        else
+            data::iAveragePoolingBackward(inputs[0]->output->grad(), output->grad(), pool_, stride_, pad_, s.N(), s.C(),
+                                          s.H(), s.W(), o.H(), o.W());
+    }
+}
+
+// ---- MaxPooling (src/Nodes.cu:716-743) ----
+MaxPoolingNode::MaxPoolingNode(Node* input, Tensor::size_type pool, Tensor::size_type stride, Tensor::size_type pad)
+    : pool_(pool), stride_(stride), pad_(pad) {
+    const auto s = input->output->shape();
+    const Dimension o(s.N(), s.C(), (s.H() + 2 * pad - pool) / stride + 1, (s.W() + 2 * pad - pool) / stride + 1);
+    inputs = {input};
+    output = std::make_shared<Tensor>(o, input->output->requiresGrad());
+    position_ = std::make_shared<Tensor>(o, false);
+    type = "MaxPooling";
+}
+void MaxPoolingNode::forward() {
+    const auto s = inputs[0]->output->shape(), o = output->shape();
+    data::iMaxPooling(output->data(), position_->data(), inputs[0]->output->data(), pool_, stride_, pad_, s.N(), s.C(),
+                      s.H(), s.W(), o.H(), o.W());
+}
+void MaxPoolingNode::backward() {
+    if (inputs[0]->output->requiresGrad()) {
+        const auto s = inputs[0]->output->shape(), o = output->shape();
+        data::iMaxPoolingBackward(inputs[0]->output->grad(), position_->data(), output->grad(), pool_, stride_, pad_,
+                                  s.N(), s.C(), s.H(), s.W(), o.H(), o.W());
     }
 }
 
@@ -236,10 +263,12 @@ SoftmaxNode::SoftmaxNode(Node* input) {
     type = "Softmax";
 }
 void SoftmaxNode::forward() {
+    if (handledByLoss) return;
     const auto s = output->shape();
     data::iSoftmax(output->data(), inputs[0]->output->data(), s.N() * s.C(), s.H() * s.W());
 }
 void SoftmaxNode::backward() {
+    if (handledByLoss) return;
     if (inputs[0]->output->requiresGrad()) {
         const auto s = output->shape();
         data::iSoftmaxBackward(inputs[0]->output->grad(), output->data(), output->grad(), s.N() * s.C(),
@@ -300,6 +329,7 @@ void Conv2dNode::backward() {
         const bool want_db = inputs.size() > 2 && inputs[2]->output->requiresGrad();
         f.relu = relu_;
         f.bias_mode = want_db ? NZB_BIAS_MATRIX : NZB_BIAS_NONE;
+        f.overwrite_dx = x.gradOverwritten() ? 1 : 0;
         size_t fused_bytes = 0;
         if (nzb_conv2d_backward_workspace_bytes(&f, &fused_bytes) == NZB_OK) {
             float* db = want_db ? inputs[2]->output->grad() : nullptr;
@@ -341,6 +371,7 @@ void Conv2dNode::backward() {
     if (x.requiresGrad()) {
         float* dx = x.grad();
         if (stride_ == 1 && kh_ == kw_ && pad_ <= kh_ - 1) {
+            d.overwrite_dx = x.gradOverwritten() ? 1 : 0;
             SM::Instance().run({dx}, {dy, w.data()}, [&](cudaStream_t s) {
                 void* ws = SM::Instance().scratch(bytes, s);
                 const int rc = nzb_conv2d_backward_data(&d, dy, w.data(), dx, ws, bytes, s);
@@ -348,7 +379,9 @@ void Conv2dNode::backward() {
                 NZB_CHECK(rc);
             });
         } else {
-            // general stride: the reference's composition on library kernels
+            // general stride: the reference's composition on library kernels (accumulates: clear first
+            // if nothing else did)
+            if (x.gradOverwritten()) SM::Instance().memset(dx, 0, x.size() * sizeof(float));
             const auto so = output->shape();
             const size_t K = x.shape().C() * kh_ * kw_, P = so.H() * so.W();
             // dY {N, Cout, Ho, Wo} -> {N, 1, Ho*Wo, Cout}: the channel extent is C(), not the row width
@@ -398,6 +431,7 @@ void LinearNode::backward() {
     const Tensor& w = *inputs[1]->output;
     nzb_linear_desc d{};
     d.batch = x.shape().N(); d.in_features = w.shape().W(); d.out_features = w.shape().H(); d.relu = relu_;
+    d.overwrite_dx = x.gradOverwritten() ? 1 : 0;
     float* dx = x.requiresGrad() ? x.grad() : nullptr;
     float* dw = w.requiresGrad() ? w.grad() : nullptr;
     float* db = (inputs.size() > 2 && inputs[2]->output->requiresGrad()) ? inputs[2]->output->grad() : nullptr;
@@ -421,10 +455,35 @@ BinaryCrossEntropyNode::BinaryCrossEntropyNode(Node* input1, Node* input2) : io:
     inputs.push_back(input2);
     type = "BinaryCrossEntropy";
 }
+void BinaryCrossEntropyNode::fuseWithSoftmax(bool on) {
+    auto* sm = dynamic_cast<calc::SoftmaxNode*>(inputs[0]);
+    if (softmax_) softmax_->handledByLoss = false;
+    softmax_ = nullptr;
+    // the one-kernel head handles vectors of up to 1024 elements
+    if (on && sm && sm->output->shape().H() * sm->output->shape().W() <= 1024) {
+        softmax_ = sm;
+        sm->handledByLoss = true;
+    }
+}
 void BinaryCrossEntropyNode::forward() {
+    if (softmax_) {
+        const auto s = softmax_->output->shape();
+        data::iSoftmaxBCE(softmax_->output->data(), loss_dev_, softmax_->inputs[0]->output->data(),
+                          inputs[1]->output->data(), s.N() * s.C(), s.H() * s.W());
+        return;
+    }
     data::iBCE(loss_dev_, inputs[0]->output->data(), inputs[1]->output->data(), output->size());
 }
 void BinaryCrossEntropyNode::backward() {
+    if (softmax_) {
+        Node* logits = softmax_->inputs[0];
+        if (logits->output->requiresGrad()) {
+            const auto s = softmax_->output->shape();
+            data::iSoftmaxBCEBackward(logits->output->grad(), softmax_->output->data(), inputs[1]->output->data(),
+                                      s.N() * s.C(), s.H() * s.W(), softmax_->roundLikeReference);
+        }
+        return;
+    }
     if (output->requiresGrad())
         data::iBCEBackward(output->grad(), inputs[0]->output->data(), inputs[1]->output->data(), output->size());
 }

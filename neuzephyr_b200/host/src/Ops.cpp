@@ -124,6 +124,34 @@ void iAveragePooling(float* out, float* in, size_t pool, size_t stride, size_t p
         NZB_CHECK(nzb_avgpool(out, in, pool, stride, pad, batches, channels, H, W, Ho, Wo, s));
     });
 }
+void iMaxPooling(float* out, float* position, float* in, size_t pool, size_t stride, size_t pad, size_t batches,
+                 size_t channels, size_t H, size_t W, size_t Ho, size_t Wo) {
+    SM::Instance().run({out, position}, {in}, [&](cudaStream_t s) {
+        NZB_CHECK(nzb_maxpool(out, position, in, pool, stride, pad, batches, channels, H, W, Ho, Wo, s));
+    });
+}
+void iMaxPoolingBackward(float* gin, float* position, float* gout, size_t pool, size_t stride, size_t pad,
+                         size_t batches, size_t channels, size_t H, size_t W, size_t Ho, size_t Wo) {
+    SM::Instance().run({gin}, {position, gout}, [&](cudaStream_t s) {
+        NZB_CHECK(nzb_maxpool_backward(gin, position, gout, pool, stride, pad, batches, channels, H, W, Ho, Wo, s));
+    });
+}
+void iSoftmaxBCE(float* probs, float* loss, float* logits, float* target, size_t batches, size_t n) {
+    SM::Instance().run({probs, loss}, {logits, target}, [&](cudaStream_t s) {
+        NZB_CHECK(nzb_softmax_bce_forward(probs, loss, logits, target, batches, n, s));
+    });
+}
+void iSoftmaxBCEBackward(float* dlogits, float* probs, float* target, size_t batches, size_t n, bool round_f16) {
+    SM::Instance().run({dlogits}, {probs, target}, [&](cudaStream_t s) {
+        NZB_CHECK(nzb_softmax_bce_backward(dlogits, probs, target, batches, n, round_f16 ? 1 : 0, s));
+    });
+}
+void iAveragePoolingBackwardOverwrite(float* gin, float* gout, size_t pool, size_t stride, size_t pad, size_t batches,
+                                      size_t channels, size_t H, size_t W, size_t Ho, size_t Wo) {
+    SM::Instance().run({gin}, {gout}, [&](cudaStream_t s) {
+        NZB_CHECK(nzb_avgpool_backward_ex(gin, gout, pool, stride, pad, batches, channels, H, W, Ho, Wo, 1, s));
+    });
+}
 void iAveragePoolingBackward(float* gin, float* gout, size_t pool, size_t stride, size_t pad, size_t batches,
                              size_t channels, size_t H, size_t W, size_t Ho, size_t Wo) {
     SM::Instance().run({gin}, {gout}, [&](cudaStream_t s) {

@@ -328,7 +328,7 @@ void Tensor::dataInject(const std::initializer_list<value_type>& data, bool grad
     dataInject(data.begin(), data.end(), grad);
 }
 void Tensor::zeroGrad() const {
-    if (requires_grad_) SM::Instance().memset(grad_, 0, size_ * sizeof(value_type));
+    if (requires_grad_ && !grad_overwritten_) SM::Instance().memset(grad_, 0, size_ * sizeof(value_type));
 }
 void Tensor::randomize(unsigned long long seed) const {
     std::mt19937_64 gen(seed);

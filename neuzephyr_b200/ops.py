@@ -224,7 +224,7 @@ def conv2d_backward_bias(dy, x_shape, w_shape, Kh, Kw, stride, pad, dbias):
     return dbias
 
 
-def conv2d_backward(x, w, dy, Kh, Kw, stride, pad, dx=None, dw=None, dbias=None, y=None):
+def conv2d_backward(x, w, dy, Kh, Kw, stride, pad, dx=None, dw=None, dbias=None, y=None, overwrite_dx=False):
     """The whole backward of one layer through nzb_conv2d_backward (dY read once): accumulates into the
     given dx / dw / dbias ({1,1,Ho*Wo,Cout}); y, when given, is the forward output whose sign masks dY
     (a layer with a fused ReLU). Raises for shapes the one-pass form does not take."""
@@ -232,6 +232,7 @@ def conv2d_backward(x, w, dy, Kh, Kw, stride, pad, dx=None, dw=None, dbias=None,
     d = _conv_desc(x.shape, w.shape, Kh, Kw, stride, pad)
     d.bias_mode = C.BIAS_MATRIX if dbias is not None else C.BIAS_NONE
     d.relu = int(y is not None)
+    d.overwrite_dx = int(overwrite_dx)
     n = ctypes.c_size_t(0)
     C.check(C.lib().nzb_conv2d_backward_workspace_bytes(ctypes.byref(d), ctypes.byref(n)))
     ws = _workspace(n.value, x.device)
@@ -263,10 +264,11 @@ def linear_forward(x, w, bias=None, relu=False, out=None):
     return out
 
 
-def linear_backward(x, w, y, dy, dx=None, dw=None, dbias=None, relu=False):
-    """dx += dy' w, dw += dy'^T x, dbias += colsum(dy'), dy' = dy * (y > 0) if relu."""
+def linear_backward(x, w, y, dy, dx=None, dw=None, dbias=None, relu=False, overwrite_dx=False):
+    """dx += dy' w (dx = ... with overwrite_dx), dw += dy'^T x, dbias += colsum(dy'), dy' = dy * (y > 0) if relu."""
     _check_f32_cuda(x, w, y, dy, dx, dw, dbias)
     d = _linear_desc(x.shape[0], x.shape[1], w.shape[0], relu)
+    d.overwrite_dx = int(overwrite_dx)
     ws = _linear_ws(d, x.device)
     C.check(C.lib().nzb_linear_backward(ctypes.byref(d), _ptr(x), _ptr(w), _ptr(y), _ptr(dy), _ptr(dx), _ptr(dw),
                                         _ptr(dbias), _ptr(ws), ws.numel(), _stream()))

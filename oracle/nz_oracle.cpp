@@ -456,6 +456,49 @@ NZO_API void nzo_avgpool_backward(float* gin, const float* gout, i64 pool, i64 s
     }
 }
 
+// Max pooling (MaxPoolingKernel / MaxPoolingBackwardKernel, src/OperationKernels.cu:1507-1573): first
+// maximum in row-major window order (strict >), its window index stored as a float; empty window -> 0.
+NZO_API void nzo_maxpool(float* out, float* position, const float* in, i64 pool, i64 stride, i64 pad, i64 batches,
+                         i64 channels, i64 H_in, i64 W_in, i64 H_out, i64 W_out) {
+#pragma omp parallel for schedule(static)
+    for (i64 bc = 0; bc < batches * channels; bc++)
+        for (i64 h = 0; h < H_out; h++)
+            for (i64 w = 0; w < W_out; w++) {
+                float best = -1e20f;
+                i64 best_i = 0;
+                for (i64 i = 0; i < pool; i++)
+                    for (i64 j = 0; j < pool; j++) {
+                        const i64 hi = h * stride - pad + i, wi = w * stride - pad + j;
+                        if (hi >= 0 && hi < H_in && wi >= 0 && wi < W_in) {
+                            const float v = in[bc * H_in * W_in + hi * W_in + wi];
+                            if (v > best) {
+                                best = v;
+                                best_i = i * pool + j;
+                            }
+                        }
+                    }
+                out[bc * H_out * W_out + h * W_out + w] = best == -1e20f ? 0.f : best;
+                position[bc * H_out * W_out + h * W_out + w] = (float)best_i;
+            }
+}
+// gin += scatter of gout to the recorded maxima (the reference's atomicAdd), summed in double per element
+NZO_API void nzo_maxpool_backward(float* gin, const float* position, const float* gout, i64 pool, i64 stride, i64 pad,
+                                  i64 batches, i64 channels, i64 H_in, i64 W_in, i64 H_out, i64 W_out) {
+#pragma omp parallel for schedule(static)
+    for (i64 bc = 0; bc < batches * channels; bc++) {
+        std::vector<double> acc((size_t)(H_in * W_in), 0.0);
+        for (i64 h = 0; h < H_out; h++)
+            for (i64 w = 0; w < W_out; w++) {
+                const i64 o = bc * H_out * W_out + h * W_out + w;
+                const i64 idx = (i64)position[o];
+                const i64 hi = h * stride - pad + idx / pool, wi = w * stride - pad + idx % pool;
+                if (hi >= 0 && hi < H_in && wi >= 0 && wi < W_in) acc[(size_t)(hi * W_in + wi)] += (double)gout[o];
+            }
+        float* g = gin + bc * H_in * W_in;
+        for (i64 t = 0; t < H_in * W_in; t++) g[t] += (float)acc[(size_t)t];
+    }
+}
+
 // ---------------------------------------------------------------------------
 // Softmax over each {H,W} matrix flattened (n = H*W), no max subtraction
 // (src/OperationKernels.cu:477-523, include/NeuZephyr/TensorOperations.cuh:379-392),

@@ -242,6 +242,28 @@ def avgpool_backward(gout, xshape, pool, stride, pad, gin=None):
     return gin
 
 
+def maxpool(x, pool, stride, pad):
+    """(out, position) of MaxPoolingKernel (OperationKernels.cu:1507-1540)."""
+    x = _f32(x)
+    n, c, h, w = x.shape
+    ho, wo = (h + 2 * pad - pool) // stride + 1, (w + 2 * pad - pool) // stride + 1
+    out = np.empty((n, c, ho, wo), dtype=np.float32)
+    pos = np.empty((n, c, ho, wo), dtype=np.float32)
+    lib().nzo_maxpool(_p(out), _p(pos), _p(x), _i64(pool), _i64(stride), _i64(pad), _i64(n), _i64(c), _i64(h), _i64(w),
+                      _i64(ho), _i64(wo))
+    return out, pos
+
+
+def maxpool_backward(gout, position, xshape, pool, stride, pad, gin=None):
+    gout, position = _f32(gout), _f32(position)
+    n, c, h, w = xshape
+    if gin is None:
+        gin = np.zeros(xshape, dtype=np.float32)
+    lib().nzo_maxpool_backward(_p(gin), _p(position), _p(gout), _i64(pool), _i64(stride), _i64(pad), _i64(n), _i64(c),
+                               _i64(h), _i64(w), _i64(gout.shape[2]), _i64(gout.shape[3]))
+    return gin
+
+
 def softmax(x):
     """Softmax over each {H,W} matrix of an {N,C,H,W} tensor."""
     x = _f32(x)

@@ -145,6 +145,10 @@ def test_conv_backward_one_pass(nz, n, c, h, w, co, k, p, per_sample, relu):
     assert emax(dx.cpu().numpy() - dx0, dx_ref) <= 5e-5
     assert emax(dw.cpu().numpy() - dw0, dw_ref) <= 5e-5
     assert emax(db.cpu().numpy() - db0, db_ref) <= 5e-6
+    # overwrite_dx: dx is written, not added to (whatever it held)
+    dx3 = dev(dx0 * 1e6)
+    nz.conv2d_backward(dev(x), dev(wt), dev(dy), k, k, 1, p, dx=dx3, y=dev(y) if relu else None, overwrite_dx=True)
+    assert emax(dx3.cpu().numpy(), dx_ref) <= 5e-5
     # any subset of the outputs
     dw2 = dev(dw0)
     nz.conv2d_backward(dev(x), dev(wt), dev(dy), k, k, 1, p, dw=dw2, y=dev(y) if relu else None)

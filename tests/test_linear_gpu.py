@@ -47,3 +47,7 @@ def test_linear_forward_backward(B, fin, fout, relu):
     assert emax(dx.cpu().numpy() - dx0, O.gemm_f64(dyp, w, True)) <= 5e-5
     assert emax(dw.cpu().numpy() - dw0, O.gemm_f64(np.ascontiguousarray(dyp.T), x, True)) <= 5e-5
     assert emax(db.cpu().numpy() - db0, dyp.astype(np.float64).sum(axis=0)) <= 5e-5
+    # overwrite_dx: dx is written, not added to (whatever it held)
+    dx2 = dev(dx0 * 1e6)
+    nz.linear_backward(dev(x), dev(w), y, dev(dy), dx2, None, None, relu=relu, overwrite_dx=True)
+    assert emax(dx2.cpu().numpy(), O.gemm_f64(dyp, w, True)) <= 5e-5

@@ -121,6 +121,10 @@ def test_avgpool(L, pool, s, p, h, w):
     assert L.nzb_avgpool_backward(P(gin), P(dev(g)), pool, s, p, n, c, h, w, ho, wo, S()) == 0
     want = O.avgpool_backward(g, x.shape, pool, s, p, gin=g0.copy())
     assert tensor_eq(gin.cpu().numpy(), want, abs_tol=1e-5)
+    # overwrite form: whatever gin held is replaced by the gradient alone
+    gin2 = dev(g0 * 1e6)
+    assert L.nzb_avgpool_backward_ex(P(gin2), P(dev(g)), pool, s, p, n, c, h, w, ho, wo, 1, S()) == 0
+    assert tensor_eq(gin2.cpu().numpy(), O.avgpool_backward(g, x.shape, pool, s, p), abs_tol=1e-5)
 
 
 def test_softmax_forward_backward(L):
@@ -175,3 +179,86 @@ def test_fill_expand_scale(L):
     assert torch.equal(out.view(5, 12), src.expand(5, 12))
     assert L.nzb_scale(P(out), 0.5, 60, S()) == 0
     assert torch.equal(out.view(5, 12), (src * 0.5).expand(5, 12))
+
+
+def test_adam_multi_matches_per_tensor_adam_and_writes_fp16_copies(L):
+    """nzb_adam_multi: one launch over tensors of different sizes, alignments and time steps equals
+    nzb_adam tensor by tensor (bit for bit) and the oracle; the optional fp16 copy is the RN rounding of
+    the updated weights."""
+    from neuzephyr_b200 import _capi as C
+    rng = np.random.default_rng(6)
+    sizes = [10007, 16, 4096 * 3, 1, 70001]
+    ts = [1, 3, 7, 10, 15]
+    base = [torch.empty(n + 3, device="cuda") for n in sizes]  # slices at offset 1 or 3: unaligned tensors
+    offs = [0, 1, 0, 3, 0]
+    data_h = [rng.uniform(-10, 10, n).astype(np.float32) for n in sizes]
+    grad_h = [rng.uniform(-10, 10, n).astype(np.float32) for n in sizes]
+    d = [b[o:o + n] for b, o, n in zip(base, offs, sizes)]
+    for t_, h in zip(d, data_h):
+        t_.copy_(torch.from_numpy(h))
+    m = [torch.zeros(n, device="cuda") for n in sizes]
+    v = [torch.zeros(n, device="cuda") for n in sizes]
+    g = [dev(h) for h in grad_h]
+    shadows = [torch.empty(n, dtype=torch.float16, device="cuda") if i % 2 == 0 else None for i, n in enumerate(sizes)]
+    d2 = [dev(h) for h in data_h]
+    m2 = [torch.zeros(n, device="cuda") for n in sizes]
+    v2 = [torch.zeros(n, device="cuda") for n in sizes]
+    for step in range(2):
+        arr = (C.AdamTensor * len(sizes))()
+        for i, n in enumerate(sizes):
+            arr[i].data, arr[i].m, arr[i].v, arr[i].grad = d[i].data_ptr(), m[i].data_ptr(), v[i].data_ptr(), g[i].data_ptr()
+            arr[i].shadow_f16 = shadows[i].data_ptr() if shadows[i] is not None else None
+            arr[i].n, arr[i].t = n, ts[i] + 20 * step
+        assert L.nzb_adam_multi(arr, len(sizes), 0.01, 0.9, 0.999, 1e-6, S()) == 0
+        for i, n in enumerate(sizes):
+            assert L.nzb_adam(P(d2[i]), P(m2[i]), P(v2[i]), P(g[i]), 0.01, 0.9, 0.999, 1e-6, ts[i] + 20 * step, n, S()) == 0
+    torch.cuda.synchronize()
+    for i, n in enumerate(sizes):
+        assert torch.equal(d[i], d2[i]) and torch.equal(m[i], m2[i]) and torch.equal(v[i], v2[i])
+        if shadows[i] is not None:
+            assert np.array_equal(shadows[i].view(torch.int16).cpu().numpy().view(np.uint16), O.f16_bits(d[i].cpu().numpy()))
+        dh, mh, vh = data_h[i].copy(), np.zeros(n, np.float32), np.zeros(n, np.float32)
+        for step in range(2):
+            O.adam(dh, mh, vh, grad_h[i], 0.01, 0.9, 0.999, 1e-6, ts[i] + 20 * step)
+        assert tensor_eq(d[i].cpu().numpy(), dh, rel_tol=2e-5)
+
+
+def test_softmax_bce_head(L):
+    """The fused head equals softmax -> BCE and BCE backward -> softmax backward (both rounding modes)."""
+    rng = np.random.default_rng(8)
+    for batches, n in ((5, 16), (64, 16), (3, 100), (1000, 7)):
+        x = rng.uniform(-2, 2, (batches, 1, n, 1)).astype(np.float32)
+        t = (rng.uniform(0, 1, x.shape) > 0.5).astype(np.float32)
+        probs = torch.empty(x.shape, device="cuda")
+        loss = torch.full((1,), 0.25, device="cuda")  # the loss scalar accumulates
+        assert L.nzb_softmax_bce_forward(P(probs), P(loss), P(dev(x)), P(dev(t)), batches, n, S()) == 0
+        yo = O.softmax(x)
+        assert np.allclose(probs.cpu().numpy(), yo, rtol=1e-5, atol=1e-7)
+        assert abs(loss.item() - 0.25 - O.bce(yo, t)) < 1e-5
+        dl = torch.empty(x.shape, device="cuda")
+        for rnd in (0, 1):
+            assert L.nzb_softmax_bce_backward(P(dl), P(dev(yo)), P(dev(t)), batches, n, rnd, S()) == 0
+            want = O.softmax_backward(yo, O.bce_backward(yo, t), round_operands=bool(rnd))
+            scale = np.max(np.abs(want))
+            assert np.max(np.abs(dl.cpu().numpy() - want)) <= 1e-5 * scale + 1e-9
+
+
+@pytest.mark.parametrize("pool,s,p,h,w", [(2, 2, 0, 4, 5), (3, 2, 1, 8, 9), (5, 2, 0, 30, 31), (3, 1, 1, 7, 7),
+                                          (4, 3, 2, 13, 11), (2, 2, 0, 64, 64), (3, 3, 0, 9, 12)])
+def test_maxpool(L, pool, s, p, h, w):
+    rng = np.random.default_rng(pool * 11 + h)
+    n, c = 2, 3
+    x = rng.uniform(-1, 1, (n, c, h, w)).astype(np.float32)
+    x[0, 0, :2, :2] = 0.5  # ties: the first maximum in window order must win
+    ho, wo = (h + 2 * p - pool) // s + 1, (w + 2 * p - pool) // s + 1
+    out = torch.empty((n, c, ho, wo), device="cuda")
+    pos = torch.empty((n, c, ho, wo), device="cuda")
+    assert L.nzb_maxpool(P(out), P(pos), P(dev(x)), pool, s, p, n, c, h, w, ho, wo, S()) == 0
+    o_out, o_pos = O.maxpool(x, pool, s, p)
+    assert np.array_equal(out.cpu().numpy(), o_out) and np.array_equal(pos.cpu().numpy(), o_pos)
+    g = rng.uniform(0.1, 0.9, (n, c, ho, wo)).astype(np.float32)
+    g0 = rng.uniform(-1, 1, x.shape).astype(np.float32)
+    gin = dev(g0)
+    assert L.nzb_maxpool_backward(P(gin), P(pos), P(dev(g)), pool, s, p, n, c, h, w, ho, wo, S()) == 0
+    want = O.maxpool_backward(g, o_pos, x.shape, pool, s, p, gin=g0.copy())
+    assert tensor_eq(gin.cpu().numpy(), want, abs_tol=1e-5)
