@@ -52,6 +52,12 @@ public:
     int world() const { return world_; }
     // in-place average over all ranks of n floats at `grad` (device memory)
     void allReduceAverage(float* grad, size_t n);
+    // Sharded form of the same exchange: rank r receives the average of elements [r*n/world, (r+1)*n/world)
+    // in place (ncclReduceScatter; the rest of the buffer keeps this rank's own values), and the inverse,
+    // which fills every rank's buffer from the slices the ranks own (ncclAllGather). n must be a
+    // multiple of the world size. Ordered through the stream manager like allReduceAverage.
+    void reduceScatterAverage(float* grad, size_t n);
+    void allGather(float* data, size_t n);
     // the same collective on a stream the caller orders itself (no StreamManager bookkeeping)
     void allReduceAverageOn(float* grad, size_t n, void* cuda_stream);
     // in-place sum of a small host-visible value (used for reporting the loss)

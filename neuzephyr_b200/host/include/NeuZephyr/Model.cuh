@@ -31,6 +31,17 @@ public:
     // all-reduce each parameter gradient as soon as its last consumer's backward has been queued
     // (default), or all of them in update() / syncGradients()
     void setOverlapGradientSync(bool on) { overlap_sync_ = on; }
+    // Sharded optimizer step for data-parallel runs: each rank receives only its slice of every
+    // averaged gradient (reduce-scatter instead of all-reduce), updates that slice of the weights and
+    // of the optimizer's state, and the updated slices are gathered on all ranks (all-gather) under the
+    // next forward pass. Same bytes on the wire as the all-reduce, but the optimizer's pass over the
+    // parameters shrinks with the number of ranks instead of being repeated on every one. Parameters
+    // whose size is not a multiple of the world size keep the all-reduce. Results are those of the
+    // unsharded step.
+    void setShardedOptimizer(bool on) { shard_optimizer_ = on; }
+    // after syncGradients(): makes every rank hold the complete averaged gradients also when the
+    // optimizer is sharded (for inspection; update() does not need it)
+    void gatherGradients();
     // parameter nodes (weights / biases created by the builders), in creation order
     const std::vector<nodes::Node*>& parameters() const { return params_; }
     graph::ComputeGraph& graph() { return computeGraph; }
@@ -60,6 +71,9 @@ protected:
 
 private:
     Node* own(Node* n, bool parameter = false);
+    bool sharded(size_t param_index) const;
+    void exchangeGradient(size_t param_index);
+    bool shard_optimizer_ = false;
     bool fused_ = true;
     bool gradients_marked_ = false;
     bool grads_synced_ = false;

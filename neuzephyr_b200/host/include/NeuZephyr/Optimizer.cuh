@@ -22,6 +22,21 @@ public:
     // between and run them as one launch in endBatch() (Adam does). The default runs each step at once.
     virtual void beginBatch() {}
     virtual void endBatch() {}
+    // Restricts the steps of `node` to elements [offset, offset + count) of its tensor (count == 0: the
+    // whole tensor again). A data-parallel run with a sharded optimizer gives every rank its own slice.
+    void setSlice(nodes::Node* node, size_t offset, size_t count) {
+        if (count) slices_[node] = {offset, count};
+        else slices_.erase(node);
+    }
+
+protected:
+    std::pair<size_t, size_t> sliceOf(nodes::Node* node) const {
+        auto it = slices_.find(node);
+        return it == slices_.end() ? std::pair<size_t, size_t>{0, node->output->size()} : it->second;
+    }
+    std::unordered_map<nodes::Node*, std::pair<size_t, size_t>> slices_;
+
+public:
     // Checkpointing (ComputeGraph::save / load): a name, the per-call counter, and per node the state
     // vectors the optimizer keeps (empty when it keeps none for that node).
     virtual const char* name() const { return "Optimizer"; }

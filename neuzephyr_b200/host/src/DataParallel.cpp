@@ -151,6 +151,27 @@ void Communicator::allReduceAverage(float* grad, size_t n) {
     SM::Instance().recordData(grad, s);
 }
 
+void Communicator::reduceScatterAverage(float* grad, size_t n) {
+    if (world_ <= 1 || n == 0) return;
+    if (n % (size_t)world_) throw std::invalid_argument("reduceScatterAverage: size is not a multiple of the world size");
+    cudaStream_t s = static_cast<cudaStream_t>(stream_);
+    const size_t chunk = n / (size_t)world_;
+    SM::Instance().streamWait(grad, s, true);
+    NCCL_TRY(ncclReduceScatter(grad, grad + (size_t)rank_ * chunk, chunk, ncclFloat32, ncclAvg,
+                               static_cast<ncclComm_t>(comm_), s));
+    SM::Instance().recordData(grad, s);
+}
+
+void Communicator::allGather(float* data, size_t n) {
+    if (world_ <= 1 || n == 0) return;
+    if (n % (size_t)world_) throw std::invalid_argument("allGather: size is not a multiple of the world size");
+    cudaStream_t s = static_cast<cudaStream_t>(stream_);
+    const size_t chunk = n / (size_t)world_;
+    SM::Instance().streamWait(data, s, true);
+    NCCL_TRY(ncclAllGather(data + (size_t)rank_ * chunk, data, chunk, ncclFloat32, static_cast<ncclComm_t>(comm_), s));
+    SM::Instance().recordData(data, s);
+}
+
 void Communicator::allReduceAverageOn(float* grad, size_t n, void* cuda_stream) {
     if (world_ <= 1 || n == 0) return;
     NCCL_TRY(ncclAllReduce(grad, grad, n, ncclFloat32, ncclAvg, static_cast<ncclComm_t>(comm_),

@@ -361,9 +361,10 @@ void Adam::step(nodes::Node* input) {
         batch_.emplace_back(input, tstep);
         return;
     }
+    const auto sl = sliceOf(input);
     SM::Instance().run({t.data(), m->data(), v->data()}, {t.grad()}, [&](cudaStream_t s) {
-        NZB_CHECK(nzb_adam(t.data(), m->data(), v->data(), t.grad(), learning_rate, beta1_, beta2_, epsilon_, tstep,
-                           (int64_t)t.size(), s));
+        NZB_CHECK(nzb_adam(t.data() + sl.first, m->data() + sl.first, v->data() + sl.first, t.grad() + sl.first,
+                           learning_rate, beta1_, beta2_, epsilon_, tstep, (int64_t)sl.second, s));
     });
 }
 
@@ -387,7 +388,9 @@ void Adam::endBatch() {
         sm.streamWait(m.data(), s, true);
         sm.streamWait(v.data(), s, true);
         sm.streamWait(t.grad(), s, false);
-        list[i] = nzb_adam_tensor{t.data(), m.data(), v.data(), t.grad(), nullptr, (int64_t)t.size(), batch_[i].second, 0};
+        const auto sl = sliceOf(batch_[i].first);
+        list[i] = nzb_adam_tensor{t.data() + sl.first, m.data() + sl.first, v.data() + sl.first, t.grad() + sl.first,
+                                  nullptr, (int64_t)sl.second, batch_[i].second, 0};
     }
     NZB_CHECK(nzb_adam_multi(list.data(), (int)list.size(), learning_rate, beta1_, beta2_, epsilon_, s));
     for (size_t i = 0; i < batch_.size(); i++) {
@@ -465,21 +468,47 @@ void Model::backward() {
         for (Node* in : n->inputs)
             for (size_t i = 0; i < params_.size(); i++)
                 if (params_[i] == in && --remaining[i] == 0) {
-                    comm_->allReduceAverage(in->output->grad(), in->output->size());
+                    exchangeGradient(i);
                     param_synced_[i] = true;
                 }
     });
 }
+bool Model::sharded(size_t i) const {
+    return shard_optimizer_ && comm_ && comm_->world() > 1 && params_[i]->output->size() % (size_t)comm_->world() == 0;
+}
+void Model::exchangeGradient(size_t i) {
+    Tensor& t = *params_[i]->output;
+    // sharded optimizer: this rank only needs the average of the slice it will update
+    if (sharded(i)) comm_->reduceScatterAverage(t.grad(), t.size());
+    else comm_->allReduceAverage(t.grad(), t.size());
+}
 void Model::syncGradients() {
     if (comm_ && comm_->world() > 1 && !grads_synced_)
         for (size_t i = 0; i < params_.size(); i++)
-            if (i >= param_synced_.size() || !param_synced_[i])
-                comm_->allReduceAverage(params_[i]->output->grad(), params_[i]->output->size());
+            if (i >= param_synced_.size() || !param_synced_[i]) exchangeGradient(i);
     grads_synced_ = true;
     param_synced_.assign(params_.size(), true);
 }
+void Model::gatherGradients() {
+    syncGradients();
+    if (!(comm_ && comm_->world() > 1)) return;
+    for (size_t i = 0; i < params_.size(); i++)
+        if (sharded(i)) comm_->allGather(params_[i]->output->grad(), params_[i]->output->size());
+}
 void Model::update(opt::Optimizer* optimizer) {
+    const bool dp = comm_ && comm_->world() > 1;
+    for (size_t i = 0; i < params_.size(); i++) {
+        const size_t n = params_[i]->output->size();
+        if (dp && sharded(i)) optimizer->setSlice(params_[i], (size_t)comm_->rank() * (n / comm_->world()), n / comm_->world());
+        else optimizer->setSlice(params_[i], 0, 0);
+    }
     computeGraph.update(optimizer, [this]() { syncGradients(); });
+    // every rank stepped its own slice of a sharded parameter: collect the updated slices. Queued in
+    // creation order, which is the order the next forward pass needs the parameters in, so the large
+    // ones that come last travel under the first layers' kernels.
+    if (dp)
+        for (size_t i = 0; i < params_.size(); i++)
+            if (sharded(i)) comm_->allGather(params_[i]->output->data(), params_[i]->output->size());
     computeGraph.zeroGrad();
     grads_synced_ = false;
 }

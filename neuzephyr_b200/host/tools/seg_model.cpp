@@ -243,6 +243,9 @@ int main(int argc, char** argv) {
     {
         SegModel model(b, S);
         model.setCommunicator(comm);
+        // NZ_DP_SHARD_OPTIMIZER=0 keeps the replicated optimizer step (all-reduce, every rank updates
+        // every parameter); the default shards it (reduce-scatter, update of 1/world, all-gather)
+        model.setShardedOptimizer(!(getenv("NZ_DP_SHARD_OPTIMIZER") && getenv("NZ_DP_SHARD_OPTIMIZER")[0] == '0'));
         init_params(model, S);
         model.input.dataInject(x.data() + rank * b * xs);
         model.target.dataInject(t.data() + rank * b * 16);
@@ -252,7 +255,7 @@ int main(int argc, char** argv) {
             model.forward();
             const float local_loss = model.getLoss();
             model.backward();
-            model.syncGradients();
+            model.gatherGradients();  // complete averaged gradients on every rank, for the comparison
             std::vector<std::vector<float>> grads;
             for (auto* p : model.parameters()) grads.push_back(p->output->hostGrad());
             model.update(&adam);

@@ -35,12 +35,15 @@ def test_single_process_step_matches_itself():
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_rank_data_parallel_step_matches_full_batch():
-    port = "29533"
+@pytest.mark.parametrize("shard_optimizer", ["1", "0"])
+def test_two_rank_data_parallel_step_matches_full_batch(shard_optimizer):
+    """Both forms of the exchange: all-reduce + replicated Adam, and reduce-scatter + Adam on each rank's
+    slice + all-gather of the updated weights (the default)."""
+    port = "29533" if shard_optimizer == "1" else "29534"
     idf = "/tmp/nz_dp_%s.id" % port
     if os.path.exists(idf):
         os.remove(idf)
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", NZ_DP_SHARD_OPTIMIZER=shard_optimizer)
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                         "--master-addr", "127.0.0.1", "--master-port", port, "--no-python", _tool(), "check", "8",
                         "64"], capture_output=True, text=True, timeout=600, env=env)
