@@ -994,6 +994,44 @@ conv2d_tma_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
     }
 }
 
+// The 8 + KW - 1 values x[w0 - pad .. w0 - pad + 8 + KW - 2] of one image row (zero outside [0, W)).
+// When the row is 16-byte aligned and the eight central values lie inside it, they come as two float4
+// loads and only the KW - 1 halo values as scalars: 4 load instructions instead of 10 for KW = 3, and the
+// vector loads of a warp are contiguous. PAD is a template argument so that every register index is
+// static (the caller switches on the run-time pad).
+template <int KW, int PAD>
+__device__ __forceinline__ void load_shift_window_p(float (&v)[8 + KW - 1], const float* __restrict__ src, int w0,
+                                                    int W, bool row_aligned) {
+    if (row_aligned && w0 + 8 <= W) {
+        const float4 a = __ldg(reinterpret_cast<const float4*>(src + w0));
+        const float4 b = __ldg(reinterpret_cast<const float4*>(src + w0 + 4));
+        const float c[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int j = 0; j < 8 + KW - 1; j++) {
+            if (j >= PAD && j < PAD + 8) {
+                v[j] = c[j - PAD];
+            } else {
+                const int w = w0 + j - PAD;
+                v[j] = (unsigned)w < (unsigned)W ? __ldg(src + w) : 0.f;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int j = 0; j < 8 + KW - 1; j++) {
+            const int w = w0 + j - PAD;
+            v[j] = (unsigned)w < (unsigned)W ? __ldg(src + w) : 0.f;
+        }
+    }
+}
+template <int KW>
+__device__ __forceinline__ void load_shift_window(float (&v)[8 + KW - 1], const float* __restrict__ src, int w0, int pad,
+                                                  int W, bool row_aligned) {
+    if (pad == 0) load_shift_window_p<KW, 0>(v, src, w0, W, row_aligned);
+    else if (pad == 1 && KW > 1) load_shift_window_p<KW, (KW > 1 ? 1 : 0)>(v, src, w0, W, row_aligned);
+    else if (pad == 2 && KW > 2) load_shift_window_p<KW, (KW > 2 ? 2 : 0)>(v, src, w0, W, row_aligned);
+    else load_shift_window_p<KW, KW - 1>(v, src, w0, W, row_aligned);
+}
+
 // Input staging for the TMA im2col mode: Kw shifted fp16 copies, 8 output columns per thread
 // (one 16-byte store per copy). rows = images * C * H of this chunk.
 template <int KW>
@@ -1002,16 +1040,13 @@ __global__ void __launch_bounds__(256) shift_copies_kernel(__half* __restrict__ 
     const int W8 = Wp >> 3;
     const int64_t total = rows * W8;
     const int64_t copy_stride = rows * Wp;
+    const bool aligned = (W & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;  // every row starts on 16 bytes
     for (int64_t u = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; u < total; u += (int64_t)gridDim.x * blockDim.x) {
         const int64_t row = u / W8;
         const int w0 = (int)(u - row * W8) * 8;
         const float* src = x + row * W;
         float v[8 + KW - 1];
-#pragma unroll
-        for (int j = 0; j < 8 + KW - 1; j++) {
-            const int w = w0 + j - pad;
-            v[j] = (unsigned)w < (unsigned)W ? __ldg(src + w) : 0.f;
-        }
+        load_shift_window<KW>(v, src, w0, pad, W, aligned);
 #pragma unroll
         for (int kw = 0; kw < KW; kw++) {
             uint4 o;
@@ -1041,6 +1076,8 @@ __global__ void __launch_bounds__(256) dy_prepare_kernel(__half* __restrict__ xs
     const int segs = (Wp + PX - 1) / PX, cblks = (Cout + CT - 1) / CT;
     const int co_l = threadIdx.x / UNITS, w8 = threadIdx.x % UNITS;
     const int64_t copy_stride = (int64_t)n * Cout * Ho * Wp;
+    const bool aligned = (Wo & 3) == 0 && (reinterpret_cast<uintptr_t>(dy) & 15) == 0;
+    const bool aligned_mask = (Wo & 3) == 0 && (reinterpret_cast<uintptr_t>(ymask) & 15) == 0;
     for (int64_t blk = blockIdx.x; blk < (int64_t)cblks * Ho * segs; blk += gridDim.x) {
         const int seg = (int)(blk % segs);
         const int ho = (int)((blk / segs) % Ho);
@@ -1055,12 +1092,13 @@ __global__ void __launch_bounds__(256) dy_prepare_kernel(__half* __restrict__ xs
                 const float* src = dy + row * Wo;
                 const float* msk = ymask ? ymask + row * Wo : nullptr;
                 float v[8 + KW - 1];
+                load_shift_window<KW>(v, src, w0, pad, Wo, aligned);
+                if (msk) {
+                    float mv[8 + KW - 1];
+                    load_shift_window<KW>(mv, msk, w0, pad, Wo, aligned_mask);
 #pragma unroll
-                for (int j = 0; j < 8 + KW - 1; j++) {
-                    const int w = w0 + j - pad;
-                    float g = (unsigned)w < (unsigned)Wo ? __ldg(src + w) : 0.f;
-                    if (msk && (unsigned)w < (unsigned)Wo && !(__ldg(msk + w) > 0.f)) g = 0.f;
-                    v[j] = g;
+                    for (int j = 0; j < 8 + KW - 1; j++)
+                        if (!(mv[j] > 0.f)) v[j] = 0.f;  // outside the row both are zero already
                 }
 #pragma unroll
                 for (int kw = 0; kw < KW; kw++) {
@@ -1074,8 +1112,13 @@ __global__ void __launch_bounds__(256) dy_prepare_kernel(__half* __restrict__ xs
                     *reinterpret_cast<uint4*>(xs + kw * copy_stride + row * Wp + w0) = o;
                 }
                 if (dbias) {
+                    // the unshifted values v[pad .. pad + 7] (pad <= KW - 1), with static register indices
 #pragma unroll
-                    for (int j = 0; j < 8; j++) acc[j] += v[j + pad];  // pad <= KW - 1: the unshifted values
+                    for (int pp = 0; pp < KW; pp++)
+                        if (pp == pad) {
+#pragma unroll
+                            for (int j = 0; j < 8; j++) acc[j] += v[j + pp];
+                        }
                 }
             }
         }
