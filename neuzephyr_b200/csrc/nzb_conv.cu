@@ -738,6 +738,28 @@ conv2d_rows_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid
 // CTA = 192 threads: warp 0 TMA (two image boxes + one weight box per stage), warp 1 MMA,
 // warps 2-5 epilogue straight into NCHW. Narrow channel tiles leave room for two CTAs per SM.
 // ---------------------------------------------------------------------------
+// internal bias mode of the TMA kernel: the {Ho*Wo, Cout} bias matrix transposed to {Cout, Ho*Wo}
+constexpr int kBiasMatrixT = 4;
+
+// out[c][r] = in[r][c] for an R x C fp32 matrix (the bias matrix, once per forward call)
+__global__ void __launch_bounds__(256) transpose_f32_kernel(float* __restrict__ out, const float* __restrict__ in,
+                                                            int64_t R, int64_t C) {
+    __shared__ float tile[32][33];
+    const int64_t tiles_c = (C + 31) / 32, tiles = ((R + 31) / 32) * tiles_c;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int64_t t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int64_t r0 = (t / tiles_c) * 32, c0 = (t % tiles_c) * 32;
+#pragma unroll
+        for (int i = ty; i < 32; i += 8)
+            if (r0 + i < R && c0 + tx < C) tile[i][tx] = __ldg(in + (r0 + i) * C + c0 + tx);
+        __syncthreads();
+#pragma unroll
+        for (int i = ty; i < 32; i += 8)
+            if (c0 + i < C && r0 + tx < R) out[(c0 + i) * R + r0 + tx] = tile[tx][i];
+        __syncthreads();
+    }
+}
+
 struct ConvTmaParams {
     float* Y;
     const float* bias;
@@ -937,6 +959,13 @@ conv2d_tma_tcgen05_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
 #pragma unroll
                             for (int j = 0; j < Cfg::CHUNK; j++) add[j] = co0 + j < p.Cout ? __ldg(bp + j) : 0.f;
                         }
+                    } else if (p.bias_mode == kBiasMatrixT) {
+                        // the bias matrix transposed to [channel][pixel] by the launcher: lanes are
+                        // consecutive pixels, so every load is one contiguous 128-byte request
+                        const float* bp = p.bias + static_cast<int64_t>(co0) * p.HoWo + (pix_ok ? pix : pix0);
+#pragma unroll
+                        for (int j = 0; j < Cfg::CHUNK; j++)
+                            add[j] = (whole || co0 + j < p.Cout) ? __ldg(bp + static_cast<int64_t>(j) * p.HoWo) : 0.f;
                     } else if (p.bias_mode == NZB_BIAS_ROW) {
 #pragma unroll
                         for (int j = 0; j < Cfg::CHUNK; j++) add[j] = __ldg(p.bias + min(co0 + j, p.Cout - 1));
@@ -1770,6 +1799,7 @@ struct ConvTmaRun {
     int64_t layerC, layerCout;  // the layer's own channel counts (weight tensor extents)
     int32_t w_per_sample, bias_mode, accumulate, relu, flip;
     const __half* staged;  // shifted copies of exactly these N images, already written (skips the staging pass)
+    float* bias_t;         // scratch of Ho*Wo*R floats for the transposed bias matrix (null: read it as stored)
 };
 
 template <class Cfg>
@@ -1815,6 +1845,16 @@ static int run_conv_tma_cfg(const ConvTmaRun& r, const TmaPlan& pl, void* ws, co
     p.tiles_n = (p.Cout + Cfg::BN - 1) / Cfg::BN;
     p.w_per_sample = r.w_per_sample;
     p.bias_mode = r.bias ? r.bias_mode : NZB_BIAS_NONE;
+    if (p.bias_mode == NZB_BIAS_MATRIX && r.bias_t && r.N >= 4) {  // pays once several images reuse it
+        // [pixel][channel] as the reference stores it -> [channel][pixel], which the epilogue (lanes =
+        // pixels) reads contiguously; 2 x Ho*Wo*Cout*4 bytes of traffic once per call
+        const int64_t tiles = ((r.Ho * r.Wo + 31) / 32) * ((r.R + 31) / 32);
+        const int64_t cap = (int64_t)ds.sm_count * 16;
+        transpose_f32_kernel<<<(unsigned)(tiles < cap ? tiles : cap), 256, 0, stream>>>(r.bias_t, r.bias, r.Ho * r.Wo, r.R);
+        NZB_CUDA_TRY(cudaGetLastError());
+        p.bias = r.bias_t;
+        p.bias_mode = kBiasMatrixT;
+    }
     p.relu = r.relu;
     p.stage_tx = (uint32_t)(2 * 64 * r.Kh * 16 * 2 + Cfg::B_BYTES);
     p.status = ds.status_dev;
@@ -2086,7 +2126,9 @@ int nzb_conv2d_workspace_bytes(const nzb_conv_desc* d, size_t* bytes_out) {
     if (g > m) m = g;
     // TMA im2col mode: staged weights + the shifted fp16 copies of a chunk of images
     const TmaPlan tf = tma_plan(d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, Ho, Wo, wN);
-    if (tf.ok && tf.w_bytes + tf.nchunk * tf.per_image > m) m = tf.w_bytes + tf.nchunk * tf.per_image;
+    // (+ the forward's transposed copy of the {Ho*Wo, Cout} bias matrix)
+    const int64_t bias_t_bytes = round_up(Ho * Wo * d->Cout * 4, 256);
+    if (tf.ok && tf.w_bytes + tf.nchunk * tf.per_image + bias_t_bytes > m) m = tf.w_bytes + tf.nchunk * tf.per_image + bias_t_bytes;
     const TmaPlan tb = tma_plan(d->N, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W, wN);
     if (tb.ok && tb.w_bytes + tb.nchunk * tb.per_image > m) m = tb.w_bytes + tb.nchunk * tb.per_image;
     const WgradPlan tg = wgrad_plan(d, Ho, Wo);
@@ -2112,8 +2154,10 @@ int nzb_conv2d_forward(const nzb_conv_desc* d, const float* x, const float* w, c
     {
         const TmaPlan tp = tma_plan(d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, Ho, Wo, wN);
         if (tp.ok) {
+            float* bias_t = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(workspace) + tp.w_bytes + tp.nchunk * tp.per_image);
             ConvTmaRun r{x, y, bias, w, d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->pad, Ho, Wo, d->C, d->Cout,
-                         d->weights_per_sample ? 1 : 0, d->bias_mode, d->accumulate ? 1 : 0, d->relu ? 1 : 0, 0, nullptr};
+                         d->weights_per_sample ? 1 : 0, d->bias_mode, d->accumulate ? 1 : 0, d->relu ? 1 : 0, 0, nullptr,
+                         bias_t};
             return run_conv_tma(r, tp, workspace, s);
         }
     }
