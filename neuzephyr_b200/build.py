@@ -12,7 +12,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libnzb.so")
-SOURCES = ["nzb_api.cu", "nzb_cast.cu", "nzb_gemm.cu", "nzb_static.cu", "nzb_selftest.cu", "nzb_matmul32.cu", "nzb_host_gemm.cu", "nzb_ops.cu", "nzb_train_ops.cu", "nzb_conv.cu", "nzb_linear.cu"]
+SOURCES = ["nzb_api.cu", "nzb_cast.cu", "nzb_gemm.cu", "nzb_static.cu", "nzb_selftest.cu", "nzb_matmul32.cu", "nzb_host_gemm.cu", "nzb_ops.cu", "nzb_train_ops.cu", "nzb_conv.cu", "nzb_conv_nhwc.cu", "nzb_linear.cu"]
 HEADERS = ["nzb_internal.h", "nzb_ptx.cuh", os.path.join("..", "..", "include", "nzb.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

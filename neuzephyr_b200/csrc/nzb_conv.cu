@@ -2126,6 +2126,8 @@ int nzb_conv2d_workspace_bytes(const nzb_conv_desc* d, size_t* bytes_out) {
     if (g > m) m = g;
     // TMA im2col mode: staged weights + the shifted fp16 copies of a chunk of images
     const TmaPlan tf = tma_plan(d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, Ho, Wo, wN);
+    const NhwcPlan nf = nhwc_plan(d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, Ho, Wo, wN);
+    if (nf.ok && nf.w_bytes + nf.nchunk * nf.per_image + nf.bias_bytes > m) m = nf.w_bytes + nf.nchunk * nf.per_image + nf.bias_bytes;
     // (+ the forward's transposed copy of the {Ho*Wo, Cout} bias matrix)
     const int64_t bias_t_bytes = round_up(Ho * Wo * d->Cout * 4, 256);
     if (tf.ok && tf.w_bytes + tf.nchunk * tf.per_image + bias_t_bytes > m) m = tf.w_bytes + tf.nchunk * tf.per_image + bias_t_bytes;
@@ -2151,6 +2153,14 @@ int nzb_conv2d_forward(const nzb_conv_desc* d, const float* x, const float* w, c
     if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(NZB_ERR_WORKSPACE, "workspace must be 256-byte aligned");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int64_t wN = d->weights_per_sample ? d->N : 1;
+    {
+        const NhwcPlan np = nhwc_plan(d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, Ho, Wo, wN);
+        if (np.ok) {
+            ConvNhwcRun r{x, y, bias, w, d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->pad, Ho, Wo, d->C, d->Cout,
+                          d->bias_mode, d->accumulate ? 1 : 0, d->relu ? 1 : 0, 0};
+            return run_conv_nhwc(r, np, workspace, s);
+        }
+    }
     {
         const TmaPlan tp = tma_plan(d->N, d->C, d->H, d->W, d->Cout, d->Kh, d->Kw, d->stride, Ho, Wo, wN);
         if (tp.ok) {

@@ -46,6 +46,33 @@ inline int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 // the first use both set the attribute, which is harmless.
 int ensure_dynamic_smem(std::atomic<uint64_t>& done, const void* kernel, int bytes);
 
+// Channels-last convolution (nzb_conv_nhwc.cu): stride 1, shared weights, 16 / 32 / 64k input channels.
+struct NhwcPlan {
+    bool ok;
+    int Cb;             // channels per operand row block: 16, 32 or 64
+    int BN;             // output channels per tile
+    int stages;         // input rows the shared-memory ring holds
+    int64_t w_bytes;    // staged weights
+    int64_t per_image;  // channels-last fp16 copy of one image
+    int64_t nchunk;     // images staged and convolved per pass
+    int64_t bias_bytes; // transposed copy of a {Ho*Wo, R} bias matrix
+};
+// Cin, Hin, Win: the tensor the taps slide over; R: output channels; wN: weight sets (1 = shared).
+NhwcPlan nhwc_plan(int64_t N, int64_t Cin, int64_t Hin, int64_t Win, int64_t R, int64_t Kh, int64_t Kw, int64_t stride,
+                   int64_t Ho, int64_t Wo, int64_t wN);
+// Y {N, R, Ho, Wo} (op)= conv(X {N, Cin, Hin, Win}, w); flip selects the backward-data form of the weights
+// (w is always the layer's {1, 1, C*Kh*Kw, Cout} tensor). ws holds w_bytes + nchunk * per_image + bias_bytes.
+struct ConvNhwcRun {
+    const float* X;
+    float* Y;
+    const float* bias;
+    const float* w;
+    int64_t N, Cin, Hin, Win, R, Kh, Kw, pad, Ho, Wo;
+    int64_t layerC, layerCout;  // the layer's own channel counts (weight tensor extents)
+    int32_t bias_mode, accumulate, relu, flip;
+};
+int run_conv_nhwc(const ConvNhwcRun& r, const NhwcPlan& pl, void* ws, cudaStream_t stream);
+
 // fp16 operand copy layout: rows x Kp halves, Kp = K rounded up to one 128-byte line.
 constexpr int64_t kOperandKAlign = 64;
 

@@ -182,12 +182,13 @@ def _conv_ws(d, device):
     return _workspace(n.value, device)
 
 
-def conv2d_forward(x, w, bias, Kh, Kw, stride, pad, relu=False, bias_mode=None, out=None):
-    """y = conv(x, w) (+ bias) (ReLU); x {N,C,H,W}, w {wN,1,C*Kh*Kw,Cout}, bias {1,1,Ho*Wo,Cout} or [Cout]."""
+def conv2d_forward(x, w, bias, Kh, Kw, stride, pad, relu=False, bias_mode=None, out=None, accumulate=False):
+    """y = conv(x, w) (+ bias) (ReLU); x {N,C,H,W}, w {wN,1,C*Kh*Kw,Cout}, bias {1,1,Ho*Wo,Cout} or [Cout].
+    accumulate=True adds the result (before ReLU) to the values already in `out`."""
     _check_f32_cuda(x, w, bias, out)
     if bias_mode is None:
         bias_mode = C.BIAS_NONE if bias is None else (C.BIAS_ROW if bias.dim() == 1 else C.BIAS_MATRIX)
-    d = _conv_desc(x.shape, w.shape, Kh, Kw, stride, pad, bias_mode, relu)
+    d = _conv_desc(x.shape, w.shape, Kh, Kw, stride, pad, bias_mode, relu, accumulate)
     Ho, Wo = (d.H + 2 * pad - Kh) // stride + 1, (d.W + 2 * pad - Kw) // stride + 1
     if out is None:
         out = torch.empty((d.N, d.Cout, Ho, Wo), dtype=torch.float32, device=x.device)

@@ -55,6 +55,12 @@ CASES = [
     (1, 6, 8, 70, 33, 2, 1, 1, False),
     (1, 20, 9, 60, 65, 4, 1, 2, False),
     (1, 3, 5, 300, 16, 3, 1, 2, False),
+    # stride 1, shared weights, 64 input channels, 65..128 output channels, rows of 64+ pixels: the forward pass
+    # runs from one channels-last fp16 copy (tap shifts are operand-row offsets); segments of 128 + a remainder,
+    # pads 0 .. K - 1, 1x1
+    (2, 64, 9, 200, 100, 3, 1, 0, False),
+    (3, 64, 5, 64, 128, 1, 1, 0, False),
+    (2, 64, 12, 130, 96, 3, 1, 2, False),
 ]
 
 
@@ -78,6 +84,55 @@ def test_conv_forward(nz, n, c, h, w, co, k, s, p, per_sample):
     y3 = nz.conv2d_forward(dev(x), dev(wt), dev(bvec), k, k, s, p).cpu().numpy()
     ref3 = O.conv2d_forward(x, wt, None, k, k, s, p, True).astype(np.float64) + bvec[None, :, None, None]
     assert emax(y3, ref3) <= TOL
+
+
+# The channels-last kernel handles every swizzle width (16 / 32 / 64-channel operand rows), several channel
+# blocks and narrow channel tiles; by default it is chosen only where it is the faster one. NZB_CONV_NHWC=2
+# (read once per process) selects it wherever it can run.
+NHWC_CASES = [
+    (2, 16, 12, 130, 16, 3, 1, 1, False),
+    (2, 32, 9, 150, 40, 3, 1, 0, False),
+    (1, 128, 7, 129, 70, 5, 1, 2, False),
+    (3, 64, 5, 64, 130, 1, 1, 0, False),
+    (1, 16, 11, 200, 16, 3, 1, 2, False),
+    (2, 64, 10, 96, 64, 3, 1, 1, False),
+    (1, 64, 6, 224, 128, 3, 1, 1, False),
+]
+
+
+def test_conv_forward_channels_last_everywhere():
+    import subprocess
+    import sys
+    if os.environ.get("NZB_CONV_NHWC") == "2":
+        pytest.skip("already running with the channels-last kernel everywhere")
+    code = (
+        "import sys, numpy as np, torch\n"
+        "sys.path.insert(0, %r)\n"
+        "import neuzephyr_b200 as nz\n"
+        "from oracle import nz_oracle as O\n"
+        "from tests.test_conv_gpu import NHWC_CASES, dev, emax, TOL\n"
+        "for (n, c, h, w, co, k, s, p, _) in NHWC_CASES:\n"
+        "    rng = np.random.default_rng(n * 100 + c * 10 + co)\n"
+        "    x = rng.normal(0, 1, (n, c, h, w)).astype(np.float32)\n"
+        "    wt = (rng.normal(0, 1, (1, 1, c * k * k, co)) * np.sqrt(2.0 / (c * k * k))).astype(np.float32)\n"
+        "    ho, wo = O.conv_out_hw(h, w, k, k, s, p)\n"
+        "    bias = rng.normal(0, 1, (1, 1, ho * wo, co)).astype(np.float32)\n"
+        "    y = nz.conv2d_forward(dev(x), dev(wt), dev(bias), k, k, s, p, relu=True).cpu().numpy()\n"
+        "    torch.cuda.synchronize()\n"
+        "    assert nz.device_status() == 0\n"
+        "    e = emax(y, O.conv2d_forward(x, wt, bias, k, k, s, p, True, relu=True))\n"
+        "    assert e <= TOL, (n, c, h, w, co, k, p, e)\n"
+        "    y0 = rng.normal(0, 1, y.shape).astype(np.float32)\n"
+        "    ya = dev(y0)\n"
+        "    nz.conv2d_forward(dev(x), dev(wt), None, k, k, s, p, out=ya, accumulate=True)\n"
+        "    e = emax(ya.cpu().numpy() - y0, O.conv2d_forward(x, wt, None, k, k, s, p, True))\n"
+        "    assert e <= 5e-5, ('accumulate', n, c, h, w, co, k, p, e)\n"
+        "print('ok')\n"
+    ) % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NZB_CONV_NHWC="2")
+    r = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and "ok" in r.stdout, r.stdout + r.stderr
 
 
 @pytest.mark.parametrize("n,c,h,w,co,k,s,p,per_sample", [cs for cs in CASES if cs[6] == 1])
