@@ -313,7 +313,7 @@ def run_ours(args):
                 out["roofline"]["conv2d_forward"] = {
                     "bound": "hbm", "achieved": conv["forward_hbm_gbs_algorithmic_per_gpu"], "peak": hbm, "unit": "GB/s",
                     "frac": conv["forward_hbm_gbs_algorithmic_per_gpu"] / hbm, "peak_source": "of measured (copy)",
-                    "kernel": "conv2d_tma_tcgen05_kernel (+ staging)", "ms": conv["forward_ms"],
+                    "kernel": "conv2d_nhwc_tcgen05_kernel (+ nchw_to_nhwc_half_kernel staging, bias transpose)", "ms": conv["forward_ms"],
                     "algorithmic_bytes": conv["forward_algorithmic_bytes"],
                     "tensor_tflops": conv["forward_tflops_per_gpu"], "img_per_s": conv["forward_img_per_s"]}
                 out["roofline"]["conv2d_forward_backward"] = {
