@@ -1434,6 +1434,221 @@ conv2d_wgrad_tma_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_co
 }
 
 // ---------------------------------------------------------------------------
+// Weight gradient with the tap columns stacked along N (3x3 .. 3-wide kernels, up to 64 output channels).
+//
+// A tcgen05.mma costs about the same whatever its N, and the kernel above issues 8 instructions of N = BN per
+// 128 pixels FOR EACH tap column, each time against another shifted copy of x. Substituting u = wo + kw - pad,
+//   dW[(ci,kh),kw][co] = sum_{ho,u} x[ci][ho+kh-pad][u] * dY[co][ho][u - kw + pad],
+// the shift moves to dY, and the Kw shifted copies of dY already exist (the data gradient reads them: copy kw'
+// holds dY shifted by kw' - (K-1-pad), so tap column kw reads copy K-1-kw). One instruction then multiplies
+// the UNSHIFTED x rows (16 channels x Kh rows) by all Kw copies at once: B has Kw*BN rows (copy, channel),
+// the accumulator Kw*BN columns. A third of the instructions, and x is staged once instead of Kw times.
+// ---------------------------------------------------------------------------
+template <int BN_, int STAGES_, int MINB_>
+struct WgradStackCfg {
+    static constexpr int BN = BN_, STAGES = STAGES_, MIN_BLOCKS = MINB_, NS = 3;
+    static constexpr int BNN = NS * BN;             // accumulator columns: (copy, channel)
+    static constexpr int A_BYTES = 2 * 8192;        // two 64-pixel halves of up to 64 k rows (16 channels x Kh)
+    static constexpr int B_HALF = BNN * 128;        // one 64-pixel half of NS * BN rows
+    static constexpr int STAGE_BYTES = A_BYTES + 2 * B_HALF;
+    static constexpr int BAR_BYTES = 256;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+    static constexpr int TMEM_COLS = BNN <= 64 ? 64 : BNN <= 128 ? 128 : 256;
+    static constexpr int THREADS = 6 * 32;
+    static_assert(STAGE_BYTES % 1024 == 0 && B_HALF % 1024 == 0, "operand tiles must stay 1024-byte aligned");
+    static_assert(BNN % 16 == 0 && BNN <= 256, "instruction N");
+    static_assert((SMEM_BYTES + 1024) * MINB_ <= 233472, "exceeds the 228 KB shared memory of an sm_100 SM");
+    static_assert(TMEM_COLS * MINB_ <= 512, "exceeds the tensor memory of an SM");
+};
+
+template <class Cfg>
+__global__ void __launch_bounds__(Cfg::THREADS, Cfg::MIN_BLOCKS)
+conv2d_wgrad_stacked_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDY,
+                            const WgradParams p) {
+    using namespace ptx;
+    constexpr int BN = Cfg::BN, STAGES = Cfg::STAGES, BNN = Cfg::BNN;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* tfull = bars + 2 * STAGES;
+    uint64_t* tempty = bars + 2 * STAGES + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmX);
+        prefetch_tensormap(&tmDY);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(tfull, 1);
+        mbar_init(tempty, 4);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // item -> (tile, group, split); tile -> (cb, nt). p.segs counts 128-column blocks of the INPUT width.
+    auto item_range = [&](uint32_t item, int32_t& cb, int32_t& nt, int32_t& group, uint32_t& kk0, uint32_t& kk1) {
+        const uint32_t split = item % (uint32_t)p.splits;
+        uint32_t r = item / (uint32_t)p.splits;
+        group = (int32_t)(r % (uint32_t)p.groups);
+        r /= (uint32_t)p.groups;
+        nt = (int32_t)(r % (uint32_t)p.tiles_n);
+        cb = (int32_t)(r / (uint32_t)p.tiles_n);
+        kk0 = (uint32_t)(p.kb_per_group * split / p.splits);
+        kk1 = (uint32_t)(p.kb_per_group * (split + 1) / p.splits);
+    };
+
+    if (warp == 0) {
+        // ---------------- TMA ----------------
+        uint32_t it = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x) {
+            int32_t cb, nt, group;
+            uint32_t kk0, kk1;
+            item_range((uint32_t)item, cb, nt, group, kk0, kk1);
+            const uint32_t per_img = (uint32_t)(p.Ho * p.segs);
+            int32_t img = (int32_t)(kk0 / per_img);
+            uint32_t rem = kk0 - (uint32_t)img * per_img;
+            int32_t ho = (int32_t)(rem / (uint32_t)p.segs), seg = (int32_t)(rem % (uint32_t)p.segs);
+            img += p.w_per_sample ? group : 0;
+            for (uint32_t kk = kk0; kk < kk1; kk++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&empty[s], ph ^ 1, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
+                    uint8_t* sa = smem + s * Cfg::STAGE_BYTES;
+                    uint8_t* sb = sa + Cfg::A_BYTES;
+                    const int32_t w0 = seg * 128;
+                    mbar_arrive_expect_tx(&full[s], p.stage_tx);
+                    tma_load_4d(sa, &tmX, w0, ho - p.pad, cb * 16, img, &full[s]);
+                    tma_load_4d(sa + 8192, &tmX, w0 + 64, ho - p.pad, cb * 16, img, &full[s]);
+                    tma_load_5d(sb, &tmDY, w0, ho, nt * BN, img, 0, &full[s]);
+                    tma_load_5d(sb + Cfg::B_HALF, &tmDY, w0 + 64, ho, nt * BN, img, 0, &full[s]);
+                }
+                __syncwarp();
+                if (++seg == p.segs) {
+                    seg = 0;
+                    if (++ho == p.Ho) {
+                        ho = 0;
+                        img++;
+                    }
+                }
+            }
+        }
+        if (!ok && lane == 0) {
+            const long long t0 = clock64();
+            const uint32_t first = it > (uint32_t)STAGES ? it - STAGES : 0;
+            for (uint32_t j = first; j < it; j++)
+                while (!mbar_try_wait(&full[j % STAGES], (j / STAGES) & 1))
+                    if (clock64() - t0 > kWaitCycleLimit) break;
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA: 8 steps of 16 pixels per k block, N = NS * BN ----------------
+        constexpr uint32_t idesc = make_idesc_f16_f32(128, BNN);
+        uint32_t it = 0, icount = 0;
+        bool ok = true;
+        for (int64_t item = blockIdx.x; item < p.total_items && ok; item += gridDim.x, icount++) {
+            int32_t cb, nt, group;
+            uint32_t kk0, kk1;
+            item_range((uint32_t)item, cb, nt, group, kk0, kk1);
+            if (!mbar_wait_warp(tempty, (icount & 1) ^ 1, abort_flag)) break;
+            tc_fence_after();
+            for (uint32_t kk = kk0; kk < kk1; kk++, it++) {
+                const uint32_t s = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_warp(&full[s], ph, abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t sa = smem_u32(smem + s * Cfg::STAGE_BYTES);
+                const uint64_t da0 = make_sw128_kmajor_desc(sa), da1 = make_sw128_kmajor_desc(sa + 8192);
+                const uint64_t db0 = make_sw128_kmajor_desc(sa + Cfg::A_BYTES);
+                const uint64_t db1 = make_sw128_kmajor_desc(sa + Cfg::A_BYTES + Cfg::B_HALF);
+                if (elect_one()) {
+                    mma_f16_ss(tmem_base, da0, db0, idesc, kk > kk0 ? 1u : 0u);
+                    mma_f16_ss(tmem_base, da0 + 2, db0 + 2, idesc, 1u);
+                    mma_f16_ss(tmem_base, da0 + 4, db0 + 4, idesc, 1u);
+                    mma_f16_ss(tmem_base, da0 + 6, db0 + 6, idesc, 1u);
+                    mma_f16_ss(tmem_base, da1, db1, idesc, 1u);
+                    mma_f16_ss(tmem_base, da1 + 2, db1 + 2, idesc, 1u);
+                    mma_f16_ss(tmem_base, da1 + 4, db1 + 4, idesc, 1u);
+                    mma_f16_ss(tmem_base, da1 + 6, db1 + 6, idesc, 1u);
+                    mma_commit(&empty[s]);
+                }
+                __syncwarp();
+            }
+            if (ok && elect_one()) mma_commit(tfull);
+            __syncwarp();
+        }
+    } else {
+        // ---------------- epilogue: lane = k row (channel, kh); columns = (copy, channel out) ----------------
+        const int q = warp & 3;
+        uint32_t icount = 0;
+        for (int64_t item = blockIdx.x; item < p.total_items; item += gridDim.x, icount++) {
+            int32_t cb, nt, group;
+            uint32_t kk0, kk1;
+            item_range((uint32_t)item, cb, nt, group, kk0, kk1);
+            if (!mbar_wait_relaxed(tfull, icount & 1, abort_flag)) break;
+            tc_fence_after();
+            const int32_t m = q * 32 + lane;
+            const int32_t ci = m / p.Kh, kh = m - ci * p.Kh;
+            const int32_t c = cb * 16 + ci;
+            const bool row_ok = kk1 > kk0 && ci < 16 && c < p.C;
+            const int64_t K = (int64_t)p.C * p.Kh * p.Kw;
+            float* row = p.dW + (p.w_per_sample ? (int64_t)(p.img0 + group) * K * p.Cout : 0) +
+                         (int64_t)(c * p.Kh + kh) * p.Kw * p.Cout + nt * BN;
+            if (q * 32 < 16 * p.Kh) {  // warp-uniform: quarters past the last k row hold nothing
+#pragma unroll 1
+                for (int c0 = 0; c0 < BNN; c0 += 16) {
+                    const int32_t copy = c0 / BN, co0 = c0 - copy * BN;
+                    if (nt * BN + co0 >= p.Cout) continue;
+                    uint32_t v[16];
+                    tmem_ld_32x16(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + c0, v);
+                    tmem_ld_wait();
+                    if (row_ok) {
+                        float* dst = row + (int64_t)(p.Kw - 1 - copy) * p.Cout + co0;  // copy kw' serves tap column K-1-kw'
+#pragma unroll
+                        for (int j = 0; j < 16; j++)
+                            if (nt * BN + co0 + j < p.Cout) atomicAdd(dst + j, __uint_as_float(v[j]));
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty);
+        }
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag) {
+        *p.status = NZB_ERR_DEVICE_TIMEOUT;
+        __threadfence_system();
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Weight staging for backward-data: W2[c][co*Kh*Kw + kh'*Kw + kw'] =
 //   half(W[wb][(c*Kh + (Kh-1-kh'))*Kw + (Kw-1-kw')][co])  -- the flipped-tap kernel whose
 // forward convolution over dY is the gradient with respect to the input.
@@ -2046,6 +2261,89 @@ static int run_wgrad_tma(const nzb_conv_desc* d, const WgradPlan& pl, const floa
 }
 
 // ---- whole backward of one layer on shared staging ------------------------------------------------
+// Weight gradient from ONE unshifted fp16 copy of x (pitch x_wp, a multiple of 64 covering the input width)
+// and the Kw = 3 shifted copies of dY the data gradient uses (pitch dy_wp), for d->N images.
+template <class Cfg>
+static int run_wgrad_stacked_cfg(const nzb_conv_desc* d, const __half* x16, int64_t x_wp, const __half* dys, int64_t dy_wp,
+                                 float* dw, int64_t Ho, int32_t img0, const DeviceState& ds, cudaStream_t stream) {
+    EncodeTiledFn enc;
+    int rc = get_encode_tiled(&enc);
+    if (rc != NZB_OK) return rc;
+    static std::atomic<uint64_t> smem_set{0};
+    {
+        const int rc_attr = ensure_dynamic_smem(smem_set, reinterpret_cast<const void*>(conv2d_wgrad_stacked_kernel<Cfg>), Cfg::SMEM_BYTES);
+        if (rc_attr != NZB_OK) return rc_attr;
+    }
+    const int64_t n = d->N;
+    WgradParams p{};
+    p.dW = dw;
+    p.C = (int32_t)d->C; p.Cout = (int32_t)d->Cout; p.Kh = (int32_t)d->Kh; p.Kw = (int32_t)d->Kw; p.pad = (int32_t)d->pad;
+    p.Ho = (int32_t)Ho; p.segs = (int32_t)((d->W + 127) / 128);
+    p.cbw = 16;
+    p.cblks = (int32_t)((d->C + 15) / 16);
+    p.tiles_n = (int32_t)((d->Cout + Cfg::BN - 1) / Cfg::BN);
+    p.tiles = p.cblks * p.tiles_n;
+    p.w_per_sample = d->weights_per_sample ? 1 : 0;
+    p.stage_tx = (uint32_t)(2 * 64 * d->Kh * 16 * 2 + 2 * Cfg::B_HALF);
+    p.status = ds.status_dev;
+    CUtensorMap tmX, tmDY;
+    {
+        const cuuint64_t row_b = (cuuint64_t)x_wp * 2;
+        cuuint64_t dims[4] = {(cuuint64_t)x_wp, (cuuint64_t)d->H, (cuuint64_t)d->C, (cuuint64_t)n};
+        cuuint64_t strides[3] = {row_b, row_b * d->H, row_b * d->H * d->C};
+        cuuint32_t box[4] = {64, (cuuint32_t)d->Kh, 16, 1};
+        cuuint32_t estr[4] = {1, 1, 1, 1};
+        CUresult cr = enc(&tmX, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4, const_cast<__half*>(x16), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (x copy) failed with CUresult %d", (int)cr);
+        const cuuint64_t row_b2 = (cuuint64_t)dy_wp * 2;
+        cuuint64_t dims2[5] = {(cuuint64_t)dy_wp, (cuuint64_t)Ho, (cuuint64_t)d->Cout, (cuuint64_t)n, (cuuint64_t)d->Kw};
+        cuuint64_t strides2[4] = {row_b2, row_b2 * Ho, row_b2 * Ho * d->Cout, row_b2 * Ho * d->Cout * n};
+        cuuint32_t box2[5] = {64, 1, (cuuint32_t)Cfg::BN, 1, (cuuint32_t)Cfg::NS};
+        cuuint32_t estr2[5] = {1, 1, 1, 1, 1};
+        cr = enc(&tmDY, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 5, const_cast<__half*>(dys), dims2, strides2, box2, estr2,
+                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (cr != CUDA_SUCCESS) return fail(NZB_ERR_CUDA, "cuTensorMapEncodeTiled (dY copies) failed with CUresult %d", (int)cr);
+    }
+    p.img0 = img0;
+    p.groups = p.w_per_sample ? (int32_t)n : 1;
+    p.imgs_per_group = p.w_per_sample ? 1 : (int32_t)n;
+    p.kb_per_group = (int64_t)p.imgs_per_group * Ho * p.segs;
+    if (p.kb_per_group > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "contraction length exceeds 2^31 blocks");
+    int64_t splits = (int64_t)ds.sm_count * Cfg::MIN_BLOCKS / ((int64_t)p.tiles * p.groups);
+    if (splits < 1) splits = 1;
+    if (splits > p.kb_per_group) splits = p.kb_per_group;
+    p.splits = (int32_t)splits;
+    p.total_items = (int64_t)p.tiles * p.groups * p.splits;
+    if (p.total_items > INT32_MAX) return fail(NZB_ERR_UNSUPPORTED, "more than 2^31 work items");
+    const int64_t cap = (int64_t)ds.sm_count * Cfg::MIN_BLOCKS;
+    const int64_t grid = p.total_items < cap ? p.total_items : cap;
+    conv2d_wgrad_stacked_kernel<Cfg><<<(unsigned)grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmX, tmDY, p);
+    NZB_CUDA_TRY(cudaGetLastError());
+    return NZB_OK;
+}
+
+// The stacked form pays where instructions are narrow: three tap columns, at most 64 output channels.
+static bool wgrad_stacked_ok(const nzb_conv_desc* d) {
+    static const bool enabled = [] {
+        const char* e = getenv("NZB_WGRAD_STACKED");
+        return e && e[0] == '1';
+    }();
+    return enabled && d->Kw == 3 && d->Kh <= 4 && d->Cout <= 64 && d->stride == 1;
+}
+
+static int run_wgrad_stacked(const nzb_conv_desc* d, const __half* x16, int64_t x_wp, const __half* dys, int64_t dy_wp,
+                             float* dw, int64_t Ho, int32_t img0, cudaStream_t stream) {
+    DeviceState* ds;
+    int rc = get_device_state(&ds);
+    if (rc != NZB_OK) return rc;
+    if (d->Cout > 32) return run_wgrad_stacked_cfg<WgradStackCfg<64, 3, 1>>(d, x16, x_wp, dys, dy_wp, dw, Ho, img0, *ds, stream);
+    if (d->Cout > 16) return run_wgrad_stacked_cfg<WgradStackCfg<32, 4, 1>>(d, x16, x_wp, dys, dy_wp, dw, Ho, img0, *ds, stream);
+    return run_wgrad_stacked_cfg<WgradStackCfg<16, 3, 2>>(d, x16, x_wp, dys, dy_wp, dw, Ho, img0, *ds, stream);
+}
+
 struct BackwardPlan {
     bool ok;
     TmaPlan dx;      // data-gradient plan for one chunk (N = nchunk)
@@ -2323,7 +2621,8 @@ int nzb_conv2d_backward(const nzb_conv_desc* d, const float* x, const float* w, 
         const float* w_c = (w && d->weights_per_sample) ? w + img0 * K * d->Cout : w;
         {
             // one pass over dY: mask, the Kw shifted copies, bias gradient
-            const int only_kw = dx ? -1 : (int)padb;  // without a data gradient only the unshifted copy is needed
+            // without a data gradient only the unshifted copy is needed, unless the weight gradient takes all of them
+            const int only_kw = (dx || (dw && wgrad_stacked_ok(d))) ? -1 : (int)padb;
             const bool narrow = d->Cout <= 16;
             const int64_t blocks_all = narrow ? ((d->Cout + 15) / 16) * Ho * ((b.wp_dy + 127) / 128)
                                               : ((d->Cout + 31) / 32) * Ho * (b.wp_dy / 64);
@@ -2346,7 +2645,17 @@ int nzb_conv2d_backward(const nzb_conv_desc* d, const float* x, const float* w, 
         }
         nzb_conv_desc dc = *d;
         dc.N = n;
-        if (dw) {
+        if (dw && wgrad_stacked_ok(d)) {
+            // one unshifted copy of x over its whole width; the tap shifts are in the dY copies
+            const int64_t rows = n * d->C * d->H, x_wp = round_up(d->W, 64);
+            int64_t blocks = (rows * (x_wp / 8) + 255) / 256;
+            if (blocks > (int64_t)ds->sm_count * 32) blocks = (int64_t)ds->sm_count * 32;
+            shift_copies_kernel<1><<<(unsigned)blocks, 256, 0, s>>>(XSx, x_c, rows, (int)d->W, (int)x_wp, 0);
+            NZB_CUDA_TRY(cudaGetLastError());
+            float* dw_c = dw + (d->weights_per_sample ? img0 * K * d->Cout : 0);
+            rc = run_wgrad_stacked(&dc, XSx, x_wp, XSdy, b.wp_dy, dw_c, Ho, (int32_t)0, s);
+            if (rc != NZB_OK) return rc;
+        } else if (dw) {
             const int64_t rows = n * d->C * d->H;
             int64_t blocks = (rows * (b.wg.Wp / 8) + 255) / 256;
             if (blocks > (int64_t)ds->sm_count * 32) blocks = (int64_t)ds->sm_count * 32;

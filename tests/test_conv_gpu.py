@@ -177,7 +177,10 @@ def test_conv_backward_weight(nz, n, c, h, w, co, k, s, p, per_sample):
 @pytest.mark.parametrize("n,c,h,w,co,k,p,per_sample,relu", [
     (2, 16, 20, 48, 16, 3, 1, False, True), (3, 16, 7, 256, 16, 3, 1, True, False), (1, 64, 6, 224, 128, 3, 1, False, True),
     (2, 40, 9, 35, 20, 3, 0, False, False), (1, 6, 8, 70, 33, 2, 1, False, True), (1, 20, 9, 60, 65, 4, 2, True, True),
-    (2, 3, 5, 300, 16, 3, 2, False, False)])
+    (2, 3, 5, 300, 16, 3, 2, False, False),
+    # 3-wide kernels with up to 64 output channels: the weight gradient stacks the tap columns along N
+    # (channel tiles of 64 and 32, several 16-channel blocks of x, per-sample weights, every pad)
+    (2, 24, 11, 130, 40, 3, 1, False, True), (2, 16, 9, 200, 24, 3, 0, True, False), (1, 70, 6, 64, 64, 3, 2, False, True)])
 def test_conv_backward_one_pass(nz, n, c, h, w, co, k, p, per_sample, relu):
     """nzb_conv2d_backward (dY read once: mask, fp16 copies, bias gradient; then both tensor-core kernels on
     the shared copies) against the oracle's backward of Conv2d (+ReLU)."""
