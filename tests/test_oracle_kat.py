@@ -189,6 +189,44 @@ def test_avgpool(pool, s, p):
     assert tensor_eq(O.avgpool_backward(g, (n, c, h, w), pool, s, p), ref)
 
 
+@pytest.mark.parametrize("pool,s,p", [(2, 2, 0), (3, 2, 1), (3, 1, 0)])
+def test_maxpool(pool, s, p):
+    """NodeBasic.MaxPoolingForward / MaxPoolingBackward (test/Test.cpp:3460-3617): the expected values are the
+    test's own host loops (first strict maximum of the window wins, an empty window gives 0, the gradient goes
+    to the position of the maximum), restated here on seeded inputs of the test's shape and a larger one."""
+    rng = np.random.default_rng(8)
+    for (n, c, h, w) in ((2, 3, 4, 5), (2, 2, 9, 11)):
+        x = rng.uniform(0.1, 0.9, (n, c, h, w)).astype(np.float32)
+        ho, wo = (h + 2 * p - pool) // s + 1, (w + 2 * p - pool) // s + 1
+        want = np.zeros((n, c, ho, wo), np.float32)
+        idx = np.zeros((n, c, ho, wo), np.int64)
+        for i in range(n):
+            for j in range(c):
+                for k in range(ho):
+                    for l in range(wo):
+                        best, bi = -1e20, 0
+                        for r in range(pool):
+                            for t in range(pool):
+                                hi, wi = k * s - p + r, l * s - p + t
+                                if 0 <= hi < h and 0 <= wi < w and x[i, j, hi, wi] > best:
+                                    best, bi = x[i, j, hi, wi], r * pool + t
+                        want[i, j, k, l] = 0.0 if best == -1e20 else best
+                        idx[i, j, k, l] = bi
+        out, pos = O.maxpool(x, pool, s, p)
+        assert np.array_equal(out, want)
+        assert np.array_equal(pos.astype(np.int64), idx)
+        g = rng.uniform(0.1, 0.9, (n, c, ho, wo)).astype(np.float32)
+        ref = np.zeros((n, c, h, w), np.float64)
+        for i in range(n):
+            for j in range(c):
+                for k in range(ho):
+                    for l in range(wo):
+                        hi, wi = k * s - p + idx[i, j, k, l] // pool, l * s - p + idx[i, j, k, l] % pool
+                        if 0 <= hi < h and 0 <= wi < w:
+                            ref[i, j, hi, wi] += g[i, j, k, l]
+        assert tensor_eq(O.maxpool_backward(g, pos, (n, c, h, w), pool, s, p), ref)
+
+
 def test_softmax_and_jacobian():
     """NodeBasic.SoftmaxForward, TensorBasic.SoftmaxJacobianTest, NodeBasic.SoftmaxBackwardRow (test/Test.cpp:1735-1870)."""
     rng = np.random.default_rng(7)
