@@ -2329,7 +2329,7 @@ static int run_wgrad_stacked_cfg(const nzb_conv_desc* d, const __half* x16, int6
 static bool wgrad_stacked_ok(const nzb_conv_desc* d) {
     static const bool enabled = [] {
         const char* e = getenv("NZB_WGRAD_STACKED");
-        return e && e[0] == '1';
+        return !(e && e[0] == '0');
     }();
     return enabled && d->Kw == 3 && d->Kh <= 4 && d->Cout <= 64 && d->stride == 1;
 }
@@ -2359,7 +2359,9 @@ static BackwardPlan backward_plan(const nzb_conv_desc* d, int64_t Ho, int64_t Wo
     b.wg = wgrad_plan(d, Ho, Wo);
     b.ok = b.wg.ok && d->Kh == d->Kw && d->pad <= d->Kh - 1 && d->W >= 32 &&
            (d->bias_mode == NZB_BIAS_MATRIX || d->bias_mode == NZB_BIAS_NONE);
-    b.wp_dy = round_up(d->W, 64);
+    // wide enough for the data gradient's rows (W) and for every column of dY itself (Wo > W when pad > (K-1)/2:
+    // the bias gradient and the unshifted copy need them all)
+    b.wp_dy = round_up(d->W > Wo ? d->W : Wo, 64);
     b.x_bytes = round_up(d->Kw * d->C * d->H * b.wg.Wp * 2, 256);
     b.dy_bytes = round_up(d->Kw * d->Cout * Ho * b.wp_dy * 2, 256);
     const int64_t budget = stage_budget(int64_t(3) << 29);
@@ -2369,6 +2371,7 @@ static BackwardPlan backward_plan(const nzb_conv_desc* d, int64_t Ho, int64_t Wo
     if (d->N > 0) n = (d->N + (d->N + n - 1) / n - 1) / ((d->N + n - 1) / n);
     b.nchunk = n;
     b.dx = tma_plan(n, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W, wN1 ? n : 1);
+    b.dx.Wp = b.wp_dy;
     b.ok = b.ok && b.dx.ok;
     b.total = b.dx.w_bytes + n * (b.x_bytes + b.dy_bytes);
     return b;
@@ -2675,6 +2678,7 @@ int nzb_conv2d_backward(const nzb_conv_desc* d, const float* x, const float* w, 
         if (dx) {
             TmaPlan pl = tma_plan(n, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, d->stride, d->H, d->W,
                                   d->weights_per_sample ? n : 1);
+            pl.Wp = b.wp_dy;  // the pitch the copies were written with
             ConvTmaRun r{dy_c, dx + img0 * d->C * d->H * d->W, nullptr, w_c, n, d->Cout, Ho, Wo, d->C, d->Kh, d->Kw, padb,
                          d->H, d->W, d->C, d->Cout, d->weights_per_sample ? 1 : 0, NZB_BIAS_NONE,
                          d->overwrite_dx ? 0 : 1, 0, 1, XSdy};
