@@ -55,6 +55,12 @@ CASES = [
     (1, 6, 8, 70, 33, 2, 1, 1, False),
     (1, 20, 9, 60, 65, 4, 1, 2, False),
     (1, 3, 5, 300, 16, 3, 1, 2, False),
+    # 3x3, pad 1, at most 64 output channels, rows of 32+ pixels: the three tap columns are stacked along N and
+    # recombined in the epilogue (tiles of 112 output pixels: remainders of 1 and 26, several 16-channel blocks,
+    # channel tiles of 16 / 32 / 64)
+    (2, 40, 9, 250, 20, 3, 1, 1, False),
+    (1, 24, 6, 113, 64, 3, 1, 1, False),
+    (2, 16, 5, 112, 48, 3, 1, 1, True),
     # stride 1, shared weights, 64 input channels, 65..128 output channels, rows of 64+ pixels: the forward pass
     # runs from one channels-last fp16 copy (tap shifts are operand-row offsets); segments of 128 + a remainder,
     # pads 0 .. K - 1, 1x1
