@@ -507,6 +507,57 @@ TEST(Model, FusedEqualsNodeByNodeOneAdamStep) {
     }
 }
 
+// The fused Conv2dNode takes its composed fallback (img2col + GEMM + col2img through the library's node-level
+// entry points) for strides other than 1 and non-square kernels. With more output columns than output channels
+// a shape mix-up in that fallback's backward would read past dY; the fused graph must agree with the
+// node-by-node composition on the output, the loss and every gradient, the input's included.
+class StridedModel : public Model {
+public:
+    InputNode input, target;
+    Node* out = nullptr;
+    StridedModel(size_t batch, size_t hw, bool fused) : input({batch, 3, hw, hw}, true), target({batch, 1, 4, 1}) {
+        setFused(fused);
+        computeGraph.addInput(&input);
+        computeGraph.addInput(&target);
+        auto x = Conv2d(&input, 8, 3, 2, 2, 1);  // 3x2 kernel, stride 2, pad 1: 8 channels, 12 x 13 outputs
+        x = Linear(x, 4);
+        out = Softmax(x);
+        BCELoss(out, &target);
+    }
+};
+
+TEST(Model, FusedFallbackStride2NonSquareEqualsNodeByNode) {
+    const size_t batch = 2, hw = 24;
+    StridedModel a(batch, hw, true), b(batch, hw, false);
+    auto x = uniform(batch * 3 * hw * hw, -1, 1, 50);
+    std::vector<float> tg(batch * 4);
+    std::mt19937 gen(51);
+    for (auto& v : tg) v = (gen() & 1) ? 1.f : 0.f;
+    a.input.dataInject(x.begin(), x.end());
+    b.input.dataInject(x.begin(), x.end());
+    a.target.dataInject(tg.begin(), tg.end());
+    b.target.dataInject(tg.begin(), tg.end());
+    auto pa = a.parameters(), pb = b.parameters();
+    EXPECT_EQ(pa.size(), pb.size());
+    for (size_t i = 0; i < pa.size() && i < pb.size(); i++) {
+        EXPECT_EQ(pa[i]->output->size(), pb[i]->output->size());
+        auto w = uniform(pa[i]->output->size(), -0.2f, 0.2f, 60 + (unsigned)i);
+        pa[i]->dataInject(w.begin(), w.end());
+        pb[i]->dataInject(w.begin(), w.end());
+    }
+    a.graph().zeroGrad();
+    b.graph().zeroGrad();
+    a.forward();
+    b.forward();
+    EXPECT_TRUE(close_vec(a.out->output->hostData(), b.out->output->hostData(), 1e-5, 1e-3));
+    EXPECT_NEAR(a.getLoss(), b.getLoss(), 1e-4);
+    a.backward();
+    b.backward();
+    for (size_t i = 0; i < pa.size() && i < pb.size(); i++)
+        EXPECT_TRUE(close_vec(pa[i]->output->hostGrad(), pb[i]->output->hostGrad(), 2e-5, 2e-2));
+    EXPECT_TRUE(close_vec(a.input.output->hostGrad(), b.input.output->hostGrad(), 2e-5, 2e-2));
+}
+
 TEST(Model, LossDecreasesOverSteps) {
     SegModel m(4, 16, true);
     auto x = uniform(4 * 3 * 16 * 16, -1, 1, 40);
