@@ -40,6 +40,65 @@ __global__ void __launch_bounds__(256) bias_grad_rows_kernel(float* __restrict__
     }
 }
 
+// dW[o][j] += sum_b dY'[b][o] * X[b][j] for a layer with few outputs and a short batch (the contraction): a
+// 16 x In weight gradient with a contraction of 8 .. 256 is a poor fit for 128-row tensor-core tiles (the GEMM
+// kernel ran it at 15 % of the DRAM rate, one k block per tile), and it is bound by reading X once. A thread owns
+// four consecutive input features and 16 outputs; dY' (masked, rounded to fp16 like every operand) sits in shared
+// memory and is read as broadcasts; X is read as fp32 float4, rounded to fp16 in registers (no staged copy),
+// products of two fp16 values are exact in fp32 and are accumulated with fp32 FMAs.
+template <int BMAX>
+__global__ void __launch_bounds__(256) linear_wgrad_small_kernel(float* __restrict__ dw, const float* __restrict__ dy,
+                                                                 const float* __restrict__ mask,
+                                                                 const float* __restrict__ x, int B, int64_t In, int Out) {
+    __shared__ __align__(16) float sdy[BMAX][16];
+    const int o0 = blockIdx.y * 16;
+    for (int i = threadIdx.x; i < B * 16; i += 256) {
+        const int b = i >> 4, o = o0 + (i & 15);
+        float g = 0.f;
+        if (o < Out) {
+            g = __ldg(dy + (int64_t)b * Out + o);
+            if (mask && !(__ldg(mask + (int64_t)b * Out + o) > 0.f)) g = 0.f;
+        }
+        sdy[b][i & 15] = __half2float(__float2half_rn(g));
+    }
+    __syncthreads();
+    const int64_t groups = In >> 2;
+    for (int64_t gidx = blockIdx.x * 256ll + threadIdx.x; gidx < groups; gidx += gridDim.x * 256ll) {
+        const float* xp = x + gidx * 4;
+        float acc[16][4];
+#pragma unroll
+        for (int o = 0; o < 16; o++) acc[o][0] = acc[o][1] = acc[o][2] = acc[o][3] = 0.f;
+#pragma unroll 4
+        for (int b = 0; b < B; b++) {
+            const float4 xv = __ldg(reinterpret_cast<const float4*>(xp + (int64_t)b * In));
+            const float x0 = __half2float(__float2half_rn(xv.x)), x1 = __half2float(__float2half_rn(xv.y)),
+                        x2 = __half2float(__float2half_rn(xv.z)), x3 = __half2float(__float2half_rn(xv.w));
+            const float4* d4 = reinterpret_cast<const float4*>(&sdy[b][0]);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const float4 dv = d4[q];
+                const float dd[4] = {dv.x, dv.y, dv.z, dv.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    acc[q * 4 + i][0] = fmaf(dd[i], x0, acc[q * 4 + i][0]);
+                    acc[q * 4 + i][1] = fmaf(dd[i], x1, acc[q * 4 + i][1]);
+                    acc[q * 4 + i][2] = fmaf(dd[i], x2, acc[q * 4 + i][2]);
+                    acc[q * 4 + i][3] = fmaf(dd[i], x3, acc[q * 4 + i][3]);
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 0; o < 16; o++) {
+            if (o0 + o < Out) {
+                float4* dst = reinterpret_cast<float4*>(dw + (int64_t)(o0 + o) * In + gidx * 4);
+                float4 w4 = *dst;
+                w4.x += acc[o][0]; w4.y += acc[o][1]; w4.z += acc[o][2]; w4.w += acc[o][3];
+                *dst = w4;
+            }
+        }
+    }
+}
+
 struct LinearSizes {
     int64_t B, In, Out, Inp, Outp, Bp;
     size_t x16, w16, total_fwd;           // forward: X [B][Inp], W [Out][Inp]
@@ -141,7 +200,19 @@ int nzb_linear_backward(const nzb_linear_desc* d, const float* x, const float* w
         rc = launch_gemm(g, s);
         if (rc != NZB_OK) return rc;
     }
-    if (dw) {
+    if (dw && z.Out <= 32 && z.B <= 256 && z.In % 4 == 0 && z.In >= 4096 &&
+        ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dw)) & 15) == 0) {
+        // few outputs, short contraction, long rows: bound by reading X once (see linear_wgrad_small_kernel)
+        int64_t blocks = (z.In / 4 + 255) / 256;
+        const int64_t cap = (int64_t)ds->sm_count * 8;
+        if (blocks > cap) blocks = cap;
+        const dim3 grid((unsigned)blocks, (unsigned)((z.Out + 15) / 16));
+        if (z.B <= 64)
+            linear_wgrad_small_kernel<64><<<grid, 256, 0, s>>>(dw, dy, mask, x, (int)z.B, z.In, (int)z.Out);
+        else
+            linear_wgrad_small_kernel<256><<<grid, 256, 0, s>>>(dw, dy, mask, x, (int)z.B, z.In, (int)z.Out);
+        NZB_CUDA_TRY(cudaGetLastError());
+    } else if (dw) {
         // dW[Out x In] += dY'^T[Out x B] * X[B x In]: both operands as stored, contraction along rows
         rc = launch_cast_masked(ds->sm_count, x, nullptr, x16, z.B, z.In, z.In, z.Inp, 0, 1, 1, 0, 0, s);
         if (rc != NZB_OK) return rc;

@@ -22,7 +22,10 @@ def emax(x, ref):
 
 
 @pytest.mark.parametrize("B,fin,fout,relu", [(8, 30, 16, True), (200, 130, 70, True), (64, 4100, 16, False),
-                                             (300, 256, 512, True), (1, 50, 3, False)])
+                                             (300, 256, 512, True), (1, 50, 3, False),
+                                             # few outputs, long rows: the weight gradient's direct kernel
+                                             # (two output tiles, the 256-row variant, the ReLU mask, one output)
+                                             (100, 8192, 24, True), (7, 4096, 1, False)])
 def test_linear_forward_backward(B, fin, fout, relu):
     import neuzephyr_b200 as nz
     rng = np.random.default_rng(B + fin + fout)
