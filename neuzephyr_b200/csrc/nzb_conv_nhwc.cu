@@ -25,7 +25,10 @@
 // and the epilogue's global loads and stores share that data path; the 36 instructions of a 3x3, 64-channel
 // tile take 3 900 clocks against 2 300 of tensor work. Converting the fp32 input inside the kernel
 // (converter warps writing the swizzled rows) was measured slower than the separate staging pass for
-// that reason (0.56 against 0.53 ms), and loading the bias one chunk ahead did not help either.
+// that reason (0.56 against 0.53 ms), and loading the bias one chunk ahead did not help either. With
+// 16-channel inputs an operand row is 32 bytes and a tap is a single K = 16 instruction; the SM then retires
+// one instruction per 113 clocks even at N = 16 (one per 40 with 128-byte rows), so narrow layers stay on the
+// shifted-copies kernel, whose operand tiles have the pixels contiguous whatever the channel count.
 #include "nzb_internal.h"
 #include "nzb_ptx.cuh"
 
