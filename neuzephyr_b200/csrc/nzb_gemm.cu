@@ -923,8 +923,7 @@ static int launch_pair(const GemmLaunch& g, GemmParams& p, const DeviceState& ds
     if (rc != NZB_OK) return rc;
     p.tiles_m = (int32_t)((g.M + 255) / 256);
     p.tiles_n = (int32_t)((g.N + 255) / 256);
-    static const int group_m_env = [] { const char* e = getenv("NZB_GEMM_GROUP_M"); return e ? atoi(e) : 0; }();
-    p.group_m = group_m_env > 0 ? group_m_env : 8;
+    p.group_m = 8;  // groups of 4 and 16 tile rows were measured slower (L2 fit)
     p.splits = 1;
     p.total_tiles = (int64_t)p.tiles_m * p.tiles_n * p.out_e0 * p.out_e1;
     static std::atomic<uint64_t> smem_set[2];  // per kernel instantiation, one bit per device
