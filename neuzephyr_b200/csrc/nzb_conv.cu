@@ -2060,7 +2060,7 @@ static int run_conv_tma_cfg(const ConvTmaRun& r, const TmaPlan& pl, void* ws, co
     p.tiles_n = (p.Cout + Cfg::BN - 1) / Cfg::BN;
     p.w_per_sample = r.w_per_sample;
     p.bias_mode = r.bias ? r.bias_mode : NZB_BIAS_NONE;
-    if (p.bias_mode == NZB_BIAS_MATRIX && r.bias_t && r.N >= 4 && r.R > 32) {  // pays once several images reuse it; narrow rows are read whole by one lane anyway
+    if (p.bias_mode == NZB_BIAS_MATRIX && r.bias_t && r.N >= 4 && r.R > 64) {  // pays once several images reuse it; up to 64 channels a lane reading its pixel's row as stored measured faster
         // [pixel][channel] as the reference stores it -> [channel][pixel], which the epilogue (lanes =
         // pixels) reads contiguously; 2 x Ho*Wo*Cout*4 bytes of traffic once per call
         const int64_t tiles = ((r.Ho * r.Wo + 31) / 32) * ((r.R + 31) / 32);
