@@ -2,12 +2,17 @@
 
     python -m neuzephyr_b200 info
     python -m neuzephyr_b200 gemm M N K [--staged] [--iters 10] [--warmup 3]
-    python -m neuzephyr_b200 conv N C H W Cout K pad [--backward] [--no-bias] [--iters 5] [--warmup 2]
+    python -m neuzephyr_b200 conv N C H W Cout K pad [--backward] [--no-bias] [--counters] [--iters 5] [--warmup 2]
 
 `gemm` times nzb_gemm (fp32 in / out, uniform[-1,1]); with --staged the GEMM kernel alone on operands
 that are already fp16 (nzb_gemm_f16). `conv` times nzb_conv2d_forward (+ untied bias matrix + ReLU) or,
 with --backward, nzb_conv2d_backward_data, on N(0,1) tensors with Kaiming-normal weights, stride 1.
 Times are CUDA-event averages over --iters calls after --warmup calls. Needs a B200.
+
+--counters prints, after the timed calls, the clock64() counters of the channels-last convolution kernel:
+clocks per CTA and call that each role spent waiting or working. They exist only in a library built with
+    NZB_EXTRA_NVCC_FLAGS=-DNZB_NHWC_PROFILE python -m neuzephyr_b200.build --force
+(rebuild without the variable afterwards: the instrumented kernel is a few percent slower).
 """
 import argparse
 import json
@@ -45,6 +50,7 @@ def main():
     c.add_argument("dims", type=int, nargs=7, metavar=("N", "C", "H", "W", "Cout", "K", "pad"))
     c.add_argument("--backward", action="store_true")
     c.add_argument("--no-bias", action="store_true")
+    c.add_argument("--counters", action="store_true")
     c.add_argument("--iters", type=int, default=5)
     c.add_argument("--warmup", type=int, default=2)
     args = ap.parse_args()
@@ -79,9 +85,27 @@ def main():
         ms = _time(lambda: nz.conv2d_backward_data(dy, w, x.shape, k, k, 1, p, dx), args.iters, args.warmup)
     else:
         ms = _time(lambda: nz.conv2d_forward(x, w, bias, k, k, 1, p, relu=True, out=y), args.iters, args.warmup)
-    print(json.dumps({"op": "conv", "dims": args.dims, "backward": args.backward, "ms": ms,
-                      "tflops": 2.0 * N * Ho * Wo * Co * C * k * k / ms / 1e9, "img_per_s": N / ms * 1e3,
-                      "status": nz.device_status()}), flush=True)
+    line = {"op": "conv", "dims": args.dims, "backward": args.backward, "ms": ms,
+            "tflops": 2.0 * N * Ho * Wo * Co * C * k * k / ms / 1e9, "img_per_s": N / ms * 1e3,
+            "status": nz.device_status()}
+    if args.counters:
+        import ctypes
+        lib = _capi.lib()
+        if not hasattr(lib, "nzb_debug_nhwc_counters"):
+            line["counters"] = "not in this build (see --help)"
+        else:
+            out = (ctypes.c_ulonglong * 16)()
+            lib.nzb_debug_nhwc_counters(out, 1)  # drop what the timing loop accumulated
+            calls = max(args.iters, 1)
+            for _ in range(calls):
+                nz.conv2d_forward(x, w, bias, k, k, 1, p, relu=True, out=y)
+            lib.nzb_debug_nhwc_counters(out, 1)
+            ctas = torch.cuda.get_device_properties(0).multi_processor_count
+            names = ["tma_wait_empty", "mma_wait_tempty", "mma_wait_full", "mma_issue_and_commit", "epilogue_wait_tfull",
+                     "epilogue_work", "kernel", "mma_issue"]
+            line["counters"] = {n: int(out[i] // (ctas * calls)) for i, n in enumerate(names)}
+            line["counters_unit"] = "clocks per CTA and call (one CTA per SM; MMA figures are the first of the two issuing warps)"
+    print(json.dumps(line), flush=True)
 
 
 if __name__ == "__main__":

@@ -16,7 +16,7 @@ SOURCES = ["nzb_api.cu", "nzb_cast.cu", "nzb_gemm.cu", "nzb_static.cu", "nzb_sel
 HEADERS = ["nzb_internal.h", "nzb_ptx.cuh", os.path.join("..", "..", "include", "nzb.h")]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-         "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"]
+         "-Xcompiler", "-fPIC,-fvisibility=hidden", "-shared"] + os.environ.get("NZB_EXTRA_NVCC_FLAGS", "").split()
 
 
 OBJ_DIR = os.path.join(HERE, "build")  # per-source objects, so that editing one file recompiles one file
